@@ -1,0 +1,243 @@
+"""ctypes binding of the CPU oracle (oracle/libsfb_oracle.so) and of the reference's own
+CPU operators (oracle/_ref/libsfb_ref.so).  Test infrastructure: only tests/, the smoke
+check and the CPU-baseline leg of bench.py import this module."""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORACLE_DIR = os.path.join(ROOT, "oracle")
+
+MASK_ALL, MASK_CAUSAL_DIAG, MASK_CAUSAL_ALL, MASK_LOCAL = 0, 1, 2, 3
+
+_u8p = C.POINTER(C.c_uint8)
+_u32p = C.POINTER(C.c_uint32)
+_f32p = C.POINTER(C.c_float)
+
+
+def build_oracle():
+    """Compile the oracle (and the reference operators when the reference tree exists)."""
+    subprocess.run(["make", "-s", "-C", ORACLE_DIR], check=True)
+
+
+def _ptr(a, t):
+    return None if a is None else a.ctypes.data_as(t)
+
+
+_lib = None
+_ref = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = os.path.join(ORACLE_DIR, "libsfb_oracle.so")
+        if not os.path.exists(path):
+            build_oracle()
+        _lib = C.CDLL(path)
+        _lib.orc_hash64.restype = C.c_uint64
+        _lib.orc_hash64.argtypes = [C.c_uint64]
+        _lib.orc_to_bhalf.restype = C.c_uint16
+        _lib.orc_to_bhalf.argtypes = [C.c_float]
+        _lib.orc_from_bhalf.restype = C.c_float
+        _lib.orc_from_bhalf.argtypes = [C.c_uint16]
+        _lib.orc_num_threads.restype = C.c_int
+    return _lib
+
+
+def ref():
+    """The reference's own CPU operators; None when oracle/_ref was never built."""
+    global _ref
+    if _ref is None:
+        path = os.path.join(ORACLE_DIR, "_ref", "libsfb_ref.so")
+        if not os.path.exists(path):
+            return None
+        _ref = C.CDLL(path)
+        _ref.ref_num_threads.restype = C.c_int
+    return _ref
+
+
+# ---------------------------------------------------------------- layouts
+def layout(kind, heads, nb, **kw):
+    out = np.zeros((heads, nb, nb), dtype=np.uint8)
+    p = _ptr(out, _u8p)
+    L = lib()
+    if kind == "full":
+        L.orc_layout_full(p, C.c_uint32(heads), C.c_uint32(nb), C.c_int(kw.get("causal", 0)))
+    elif kind == "fixed":
+        L.orc_layout_fixed(p, C.c_uint32(heads), C.c_uint32(nb), C.c_uint32(kw.get("stride", 4)),
+                           C.c_int(kw.get("causal", 0)))
+    elif kind == "stride":
+        L.orc_layout_stride(p, C.c_uint32(heads), C.c_uint32(nb), C.c_uint32(kw.get("band", 4)),
+                            C.c_uint32(kw.get("every", 8)), C.c_int(kw.get("causal", 0)))
+    elif kind == "sawtooth":
+        L.orc_layout_stride_sawtooth(p, C.c_uint32(heads), C.c_uint32(nb), C.c_uint32(kw["chunks"]))
+    elif kind == "local":
+        L.orc_layout_local(p, C.c_uint32(heads), C.c_uint32(nb), C.c_uint32(kw.get("left", 8)),
+                           C.c_uint32(kw.get("right", 8)))
+    elif kind == "bigbird":
+        L.orc_layout_bigbird(p, C.c_uint32(heads), C.c_uint32(nb), C.c_uint32(kw.get("window", 1)),
+                             C.c_uint32(kw.get("g_first", 1)), C.c_uint32(kw.get("g_last", 1)),
+                             C.c_uint32(kw.get("nrand", 3)), C.c_uint64(kw.get("seed", 1234)))
+    else:
+        raise ValueError(kind)
+    return out
+
+
+def lut_count(lay):
+    heads, nb, _ = lay.shape
+    blocks = C.c_uint32(0)
+    rc = lib().orc_lut_count(_ptr(lay, _u8p), C.c_uint32(heads), C.c_uint32(nb), C.byref(blocks))
+    if rc != 0:
+        raise ValueError("heads have different block counts")
+    return blocks.value
+
+
+def lut_build(lay):
+    """-> dict(nt, nn, rblk, nn_max, blocks) with uint32 arrays shaped [heads, n, 2]."""
+    lay = np.ascontiguousarray(lay, dtype=np.uint8)
+    heads, nb, _ = lay.shape
+    blocks = lut_count(lay)
+    nt = np.zeros((heads, blocks, 2), np.uint32)
+    nn = np.zeros((heads, nb + blocks, 2), np.uint32)
+    rb = np.zeros((heads, blocks, 2), np.uint32)
+    mx = C.c_uint32(0)
+    rc = lib().orc_lut_build(_ptr(lay, _u8p), C.c_uint32(heads), C.c_uint32(nb), C.c_uint32(blocks),
+                             _ptr(nt, _u32p), _ptr(nn, _u32p), _ptr(rb, _u32p), C.byref(mx))
+    assert rc == 0
+    return dict(nt=nt, nn=nn, rblk=rb, nn_max=mx.value, blocks=blocks)
+
+
+_WORD = {8: np.uint8, 16: np.uint16, 32: np.uint32, 64: np.uint64}
+
+
+def mask_pack(nt, bs, pred, ctx=0):
+    """-> (mask_np [heads, blocks, bs], mask_t [heads, bs, blocks]) of bs-bit words."""
+    heads, blocks, _ = nt.shape
+    wt = _WORD[bs]
+    m_np = np.zeros((heads, blocks, bs), wt)
+    m_t = np.zeros((heads, bs, blocks), wt)
+    lib().orc_mask_pack(_ptr(nt, _u32p), C.c_uint32(heads), C.c_uint32(blocks), C.c_uint32(bs),
+                        C.c_int(pred), C.c_uint32(ctx), m_np.ctypes.data_as(C.c_void_p),
+                        m_t.ctypes.data_as(C.c_void_p))
+    return m_np, m_t
+
+
+# ---------------------------------------------------------------- arithmetic
+def attention(q, k, v, luts, bs, scale, mask_np=None, eps=1e-6, round_s_bf16=False,
+              want=("s", "p", "o")):
+    """q,k,v float32 [B,L,H,d]; returns dict with the requested of s,p [B,H,blocks,bs,bs], o [B,L,H,d]."""
+    q = np.ascontiguousarray(q, np.float32)
+    k = np.ascontiguousarray(k, np.float32)
+    v = np.ascontiguousarray(v, np.float32)
+    B, L, H, d = q.shape
+    nb = L // bs
+    nt, nn = luts["nt"], luts["nn"]
+    blocks = luts["blocks"]
+    lut_heads = nt.shape[0]
+    mask_heads = 1 if mask_np is None else mask_np.shape[0]
+    s = np.zeros((B, H, blocks, bs, bs), np.float32) if "s" in want else None
+    p = np.zeros((B, H, blocks, bs, bs), np.float32) if "p" in want else None
+    o = np.zeros((B, L, H, d), np.float32) if "o" in want else None
+    lib().orc_attention(_ptr(q, _f32p), _ptr(k, _f32p), _ptr(v, _f32p), _ptr(nt, _u32p), _ptr(nn, _u32p),
+                        None if mask_np is None else mask_np.ctypes.data_as(C.c_void_p),
+                        C.c_uint32(B), C.c_uint32(H), C.c_uint32(nb), C.c_uint32(bs), C.c_uint32(d),
+                        C.c_uint32(blocks), C.c_uint32(lut_heads), C.c_uint32(mask_heads),
+                        C.c_float(scale), C.c_float(eps), C.c_int(int(round_s_bf16)),
+                        _ptr(s, _f32p), _ptr(p, _f32p), _ptr(o, _f32p))
+    return dict(s=s, p=p, o=o)
+
+
+def bias_residual_layernorm(x, bias, resid, gain, beta):
+    x = np.ascontiguousarray(x, np.float32)
+    m, hidden = x.shape
+    out = np.zeros_like(x)
+    summed = np.zeros_like(x)
+    mean = np.zeros(m, np.float32)
+    rstd = np.zeros(m, np.float32)
+    f = lambda a: None if a is None else _ptr(np.ascontiguousarray(a, np.float32), _f32p)
+    keep = [np.ascontiguousarray(a, np.float32) if a is not None else None for a in (bias, resid, gain, beta)]
+    lib().orc_bias_residual_layernorm(_ptr(out, _f32p), _ptr(summed, _f32p), _ptr(mean, _f32p),
+                                      _ptr(rstd, _f32p), _ptr(x, _f32p), _ptr(keep[0], _f32p),
+                                      _ptr(keep[1], _f32p), _ptr(keep[2], _f32p), _ptr(keep[3], _f32p),
+                                      C.c_uint32(m), C.c_uint32(hidden))
+    return out, summed, mean, rstd
+
+
+def magicu64(d):
+    mg, sh = C.c_uint32(0), C.c_uint32(0)
+    lib().orc_magicu64(C.c_uint32(d), C.byref(mg), C.byref(sh))
+    return mg.value, sh.value
+
+
+def fill_normal(shape, seed, stddev=1.0):
+    out = np.empty(shape, np.float32)
+    lib().orc_fill_normal(_ptr(out, _f32p), C.c_size_t(out.size), C.c_uint64(seed), C.c_float(stddev))
+    return out
+
+
+def to_bhalf(a):
+    """fp32 array -> uint16 bf16 bits with the reference's rounding."""
+    a = np.ascontiguousarray(a, np.float32)
+    L = lib()
+    return np.fromiter((L.orc_to_bhalf(C.c_float(float(x))) for x in a.ravel()), np.uint16, a.size).reshape(a.shape)
+
+
+def from_bhalf(bits):
+    return (np.asarray(bits, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+# ---------------------------------------------------------------- reference CPU path
+def ref_dense_causal_attention(q, k, v, scale):
+    """The reference's own CPU attention (transformer_inference_part.cpp:219-224 order):
+    transpose to [B,H,L,d], multiheadmatmulNT, softmax, multiheadmatmulNN, transpose back.
+    Returns (scores [B,H,L,L], probs [B,H,L,L], o [B,L,H,d])."""
+    R = ref()
+    assert R is not None, "oracle/_ref/libsfb_ref.so not built"
+    B, L, H, d = q.shape
+    tq, tk, tv = (np.zeros((B, H, L, d), np.float32) for _ in range(3))
+    for src, dst in ((q, tq), (k, tk), (v, tv)):
+        src = np.ascontiguousarray(src, np.float32)
+        R.ref_transpose_0123to0213(_ptr(src, _f32p), _ptr(dst, _f32p), C.c_int(B), C.c_int(L), C.c_int(H), C.c_int(d))
+    s = np.zeros((B, H, L, L), np.float32)
+    p = np.zeros((B, H, L, L), np.float32)
+    R.ref_multiheadmatmulNT(_ptr(s, _f32p), _ptr(tq, _f32p), _ptr(tk, _f32p), C.c_int(B), C.c_int(H), C.c_int(L), C.c_int(d), C.c_int(L))
+    R.ref_softmax(_ptr(p, _f32p), _ptr(s, _f32p), C.c_float(scale), C.c_int(L), C.c_int(B), C.c_int(H))
+    to = np.zeros((B, H, L, d), np.float32)
+    R.ref_multiheadmatmulNN(_ptr(to, _f32p), _ptr(p, _f32p), _ptr(tv, _f32p), C.c_int(B), C.c_int(H), C.c_int(L), C.c_int(L), C.c_int(d))
+    o = np.zeros((B, L, H, d), np.float32)
+    R.ref_transpose_0123to0213(_ptr(to, _f32p), _ptr(o, _f32p), C.c_int(B), C.c_int(H), C.c_int(L), C.c_int(d))
+    return s, p, o
+
+
+def ref_bias_residual_layernorm(x, bias, resid, gain, beta):
+    R = ref()
+    assert R is not None
+    x = np.ascontiguousarray(x, np.float32)
+    m, hidden = x.shape
+    t = np.zeros_like(x)
+    R.ref_bias(_ptr(t, _f32p), _ptr(x, _f32p), _ptr(np.ascontiguousarray(bias, np.float32), _f32p), C.c_int(hidden), C.c_int(m))
+    t2 = np.zeros_like(x)
+    resid = np.ascontiguousarray(resid, np.float32)
+    R.ref_tensor_add_tensor(_ptr(t2, _f32p), _ptr(resid, _f32p), _ptr(t, _f32p), C.c_int(1), C.c_int(m), C.c_int(hidden))
+    out = np.zeros_like(x)
+    mean = np.zeros(m, np.float32)
+    rstd = np.zeros(m, np.float32)
+    g = np.ascontiguousarray(gain, np.float32)
+    b = np.ascontiguousarray(beta, np.float32)
+    R.ref_layernorm(_ptr(out, _f32p), _ptr(mean, _f32p), _ptr(rstd, _f32p), _ptr(t2, _f32p), _ptr(g, _f32p), _ptr(b, _f32p), C.c_int(1), C.c_int(m), C.c_int(hidden))
+    return out, t2, mean, rstd
+
+
+def blocks_to_dense(blk, nt, nb, bs):
+    """[B,H,blocks,bs,bs] block tensor -> dense [B,H,L,L] (zeros elsewhere)."""
+    B, H, blocks, _, _ = blk.shape
+    out = np.zeros((B, H, nb * bs, nb * bs), blk.dtype)
+    for h in range(H):
+        lut = nt[h if nt.shape[0] > 1 else 0]
+        for kk in range(blocks):
+            i, j = int(lut[kk, 0]), int(lut[kk, 1])
+            out[:, h, i * bs:(i + 1) * bs, j * bs:(j + 1) * bs] = blk[:, h, kk]
+    return out

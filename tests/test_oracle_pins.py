@@ -1,0 +1,160 @@
+"""Pins the CPU oracle to the reference: (1) the LUT / mask arrays that the reference's own
+test programs upload (tests/golden/ref_uploads.npz, made by tests/golden/make_golden.py),
+(2) outputs of the reference's own CPU operators (tests/golden/ref_cpu_attention.npz), and
+(3) the all-ones known answer of the reference test programs (fixed_fusion_test.cu:263-268,
+test.cu:382-386: every score equals d, every probability 1/#kept)."""
+import os
+
+import numpy as np
+import pytest
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _layout_from_nt(nt, nb):
+    lay = np.zeros((1, nb, nb), np.uint8)
+    lay[0, nt[:, 0], nt[:, 1]] = 1
+    return lay
+
+
+# program -> (nb, bs, generator or None, mask predicate, ctx)
+CASES = {
+    "stride_fusion_test": (32, 32, ("sawtooth", dict(chunks=1)), "causal_all", 0),
+    "local_fusion_test": (32, 32, ("local", dict(left=1, right=0)), "local", 32),
+    "no_fusion_test": (10, 32, ("full", dict(causal=1)), "causal_diag", 0),
+    "big_bird_fusion_test": (10, 32, None, None, 0),
+}
+
+
+@pytest.mark.parametrize("prog", sorted(CASES))
+def test_lut_and_mask_match_reference_uploads(oracle, prog):
+    g = np.load(os.path.join(GOLD, "ref_uploads.npz"))
+    nb, bs, gen, pred, ctx = CASES[prog]
+    nt_ref = g[prog + "/nt_lut"].reshape(-1, 2)
+    lay = _layout_from_nt(nt_ref, nb)
+    if gen is not None:
+        assert np.array_equal(oracle.layout(gen[0], 1, nb, **gen[1]), lay)
+    luts = oracle.lut_build(lay)
+    assert np.array_equal(luts["nt"][0], nt_ref)
+    assert np.array_equal(luts["nn"][0], g[prog + "/nn_lut"].reshape(-1, 2))
+    if prog + "/rblk_lut" in g:
+        assert np.array_equal(luts["rblk"][0], g[prog + "/rblk_lut"].reshape(-1, 2))
+    if pred is not None:
+        code = dict(causal_all=oracle.MASK_CAUSAL_ALL, causal_diag=oracle.MASK_CAUSAL_DIAG,
+                    local=oracle.MASK_LOCAL)[pred]
+        m_np, m_t = oracle.mask_pack(luts["nt"], bs, code, ctx)
+        assert np.array_equal(m_np.ravel(), g[prog + "/mask_np"])
+        assert np.array_equal(m_t.ravel(), g[prog + "/mask_t"])
+
+
+@pytest.mark.parametrize("prog", sorted(CASES))
+def test_nn_max_matches_reference_softmax_launch(oracle, prog):
+    """The reference sizes the softmax CTA from nn_max (blocksparse.h:665-680): threads =
+    ceil(nn_max*bs/256)*32, shared = threads*4/16*8 bytes; grid = (L, B, H)."""
+    g = np.load(os.path.join(GOLD, "ref_uploads.npz"))
+    nb, bs, _, _, _ = CASES[prog]
+    luts = oracle.lut_build(_layout_from_nt(g[prog + "/nt_lut"].reshape(-1, 2), nb))
+    line = [l for l in g[prog + "/launches"] if "bst_masked_softmax" in l][0].split()
+    grid_x, threads, smem = int(line[1]), int(line[4]), int(line[7])
+    want_threads = -(-luts["nn_max"] * bs // 256) * 32
+    assert grid_x == nb * bs
+    assert threads == want_threads
+    assert smem == (want_threads * 4 >> 4) * 8
+    sddmm = [l for l in g[prog + "/launches"] if "bst_sgemm_32x32x64_nt" in l][0].split()
+    assert int(sddmm[1]) == luts["blocks"]
+
+
+def test_attention_matches_reference_cpu_operators(oracle):
+    g = np.load(os.path.join(GOLD, "ref_cpu_attention.npz"))
+    B, L, H, d = (int(x) for x in g["attn/shape"])
+    sq, sk, sv = (int(x) for x in g["attn/seeds"])
+    bs = 32
+    nb = L // bs
+    q, k, v = (oracle.fill_normal((B, L, H, d), s) for s in (sq, sk, sv))
+    luts = oracle.lut_build(oracle.layout("full", 1, nb, causal=1))
+    m_np, _ = oracle.mask_pack(luts["nt"], bs, oracle.MASK_CAUSAL_DIAG)
+    r = oracle.attention(q, k, v, luts, bs, np.float32(1.0 / np.sqrt(d)), mask_np=m_np)
+    tri = np.tril(np.ones((L, L), bool))
+    s = oracle.blocks_to_dense(r["s"], luts["nt"], nb, bs)
+    p = oracle.blocks_to_dense(r["p"], luts["nt"], nb, bs)
+    # bit-exact: same operation order as matmul.h / ewops.h
+    assert np.array_equal(np.where(tri, s, 0), g["attn/s"])
+    assert np.array_equal(p, g["attn/p"])
+    assert np.array_equal(r["o"], g["attn/o"])
+
+
+def test_attention_matches_live_reference_when_built(oracle):
+    if oracle.ref() is None:
+        pytest.skip("oracle/_ref not built on this machine")
+    B, L, H, d, bs = 1, 128, 2, 32, 64
+    q, k, v = (oracle.fill_normal((B, L, H, d), s) for s in (5, 6, 7))
+    luts = oracle.lut_build(oracle.layout("full", 1, L // bs, causal=1))
+    m_np, _ = oracle.mask_pack(luts["nt"], bs, oracle.MASK_CAUSAL_DIAG)
+    r = oracle.attention(q, k, v, luts, bs, 0.25, mask_np=m_np)
+    s, p, o = oracle.ref_dense_causal_attention(q, k, v, 0.25)
+    assert np.array_equal(oracle.blocks_to_dense(r["p"], luts["nt"], L // bs, bs), p)
+    assert np.array_equal(r["o"], o)
+
+
+def test_layernorm_matches_reference_cpu_operators(oracle):
+    g = np.load(os.path.join(GOLD, "ref_cpu_attention.npz"))
+    m, hidden = (int(x) for x in g["ln/shape"])
+    sx, sr, sb, sg, sbe = (int(x) for x in g["ln/seeds"])
+    x = oracle.fill_normal((m, hidden), sx)
+    r = oracle.fill_normal((m, hidden), sr)
+    b = oracle.fill_normal((hidden,), sb, 0.02)
+    gain = 1.0 + oracle.fill_normal((hidden,), sg, 0.1)
+    beta = oracle.fill_normal((hidden,), sbe, 0.1)
+    y, summed, mean, rstd = oracle.bias_residual_layernorm(x, b, r, gain, beta)
+    assert np.array_equal(summed, g["ln/sum"])
+    assert np.array_equal(mean, g["ln/mean"])
+    assert np.array_equal(rstd, g["ln/rstd"])
+    assert np.array_equal(y, g["ln/y"])
+
+
+@pytest.mark.parametrize("kind,kw,H", [("fixed", dict(stride=4), 4), ("local", dict(left=1, right=0), 1),
+                                         ("bigbird", dict(nrand=3), 1)])
+def test_all_ones_known_answer(oracle, kind, kw, H):
+    B, L, d, bs = 1, 256, 128, 32
+    nb = L // bs
+    luts = oracle.lut_build(oracle.layout(kind, H, nb, **kw))
+    ones = np.ones((B, L, H, d), np.float32)
+    r = oracle.attention(ones, ones, ones, luts, bs, np.float32(1 / np.sqrt(d)), eps=0.0)
+    assert np.all(r["s"] == d)
+    for h in range(H):
+        nn = luts["nn"][h]
+        for i in range(nb):
+            cnt = int(nn[i, 1])
+            for e in range(cnt):
+                blk = int(nn[int(nn[i, 0]) + e, 0])
+                np.testing.assert_allclose(r["p"][0, h, blk], 1.0 / (cnt * bs), rtol=1e-6)
+    np.testing.assert_allclose(r["o"], 1.0, rtol=1e-5)
+
+
+def test_layout_block_counts():
+    """Block counts of the five benchmark configurations."""
+    import oracle_lib as O
+    assert O.lut_build(O.layout("fixed", 4, 16, stride=4))["blocks"] == 112
+    st = O.lut_build(O.layout("stride", 1, 64, band=4, every=8))
+    assert (st["blocks"], st["nn_max"]) == (730, 12)
+    lo = O.lut_build(O.layout("local", 1, 256, left=8, right=8))
+    assert (lo["blocks"], lo["nn_max"]) == (4280, 17)
+    fu = O.lut_build(O.layout("full", 1, 16))
+    assert (fu["blocks"], fu["nn_max"]) == (256, 16)
+    bb = O.lut_build(O.layout("bigbird", 1, 64, window=1, g_first=1, g_last=1, nrand=3, seed=1236))
+    assert bb["nn_max"] == 64 and 560 <= bb["blocks"] <= 620
+
+
+def test_magicu64_divides(oracle):
+    for d in (1, 2, 3, 4, 5, 7, 8, 12):
+        magic, shift = oracle.magicu64(d)
+        for n in (0, 1, d - 1, d, 5 * d + 3, 1000, 65535):
+            got = n >> shift if magic == 1 else ((n * magic) >> 32) >> shift
+            assert got == n // d
+
+
+def test_to_bhalf_rounds_half_away(oracle):
+    below = np.nextafter(np.float32(1.00390625), np.float32(0))
+    v = np.array([1.0, 1.00390625, below, 1.0117188, -1.00390625, 0.0, 3.0e38], np.float32)
+    bits = oracle.to_bhalf(v)
+    assert list(bits[:5]) == [0x3F80, 0x3F81, 0x3F80, 0x3F82, 0xBF81]
