@@ -1,0 +1,162 @@
+/*
+ * libsfbert_b200.so -- C ABI of the B200 (sm_100a) block-sparse attention path.
+ *
+ * Every entry point takes plain pointers and sizes.  Unless a comment says otherwise all
+ * pointers are DEVICE pointers owned by the caller, nothing is allocated or freed, the
+ * work is queued on `stream` (a cudaStream_t / CUstream) and the call returns without
+ * synchronising.  Return value: 0 on success, non-zero on a rejected argument or a failed
+ * launch; sfb_last_error() then holds a message (thread local).  No entry point has a CPU
+ * fallback.
+ *
+ * Each declaration names the interface of the reference (HeyHaoh/SF-Bert) it replaces.
+ * Parameter names follow the reference, including its misleading ones:
+ *   head_dim  = number of heads H          state_dim = size of one head d
+ *   batch_dim = B                          ctx_blks_* = sequence length / block_size
+ *   blocks    = non-zero blocks of ONE head's layout
+ *   lut_heads = 1 (one LUT for all heads) or H;  lut_dim = per-head LUT stride in uint2
+ * Tensors Q, K, V, O are [B, L, H, d] (no head transpose, transformer_attention_optimize.cu:719-748);
+ * S and P are [B, H, blocks, block_size, block_size], row-major inside a block.
+ */
+#ifndef SFBERT_B200_H
+#define SFBERT_B200_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *sfb_stream_t;
+
+/* element types of operand buffers */
+enum { SFB_F32 = 0, SFB_BF16 = 1, SFB_F16 = 2 };
+
+/* layout kinds for sfb_layout_generate */
+enum {
+    SFB_LAYOUT_FULL = 0,     /* p0 unused                                   (no_fusion_test.cu:47-63)       */
+    SFB_LAYOUT_FIXED = 1,    /* p0 = stride                                 (fixed_fusion_test.cu:52-107)   */
+    SFB_LAYOUT_STRIDE = 2,   /* p0 = band, p1 = every                       (BERT-base stride config)       */
+    SFB_LAYOUT_SAWTOOTH = 3, /* p0 = chunks                                 (stride_fusion_test.cu:57-70)   */
+    SFB_LAYOUT_LOCAL = 4,    /* p0 = left, p1 = right                       (local_fusion_test.cu:46-66)    */
+    SFB_LAYOUT_BIGBIRD = 5   /* p0 = window, p1 = g_first, p2 = g_last, p3 = nrand (big_bird_fusion_test.cu:50-99) */
+};
+
+/* element-mask predicates for sfb_mask_pack */
+enum { SFB_MASK_ALL = 0, SFB_MASK_CAUSAL_DIAG = 1, SFB_MASK_CAUSAL_ALL = 2, SFB_MASK_LOCAL = 3 };
+
+/* block-sparse matmul variants (gpu_types.h:135-137) */
+enum { SFB_NT_OP = 0, SFB_NN_OP = 1, SFB_TN_OP = 2 };
+
+/* message of the last failed call on this thread ("" if none) */
+const char *sfb_last_error(void);
+int sfb_version(void);
+
+/* ---- layout -> LUT ------------------------------------------------------------------ */
+
+/* Writes a block layout, uint8 [heads][nb][nb] (1 = kept), into device memory.
+ * Replaces the inline layout loops of the reference test programs (see the enum). */
+int sfb_layout_generate(sfb_stream_t stream, uint8_t *layout, uint32_t heads, uint32_t nb,
+                        int kind, uint32_t p0, uint32_t p1, uint32_t p2, uint32_t p3,
+                        int causal, uint64_t seed);
+
+/* Counts the kept blocks: head_blocks[h] (device, uint32 [heads]).  The caller reads it
+ * back to size the LUTs; every head must have the same count (blocksparse.h:442 has one
+ * per-head stride).  Replaces stride_fusion_test.cu:57-70 (the counting half). */
+int sfb_lut_count(sfb_stream_t stream, const uint8_t *layout, uint32_t heads, uint32_t nb,
+                  uint32_t *head_blocks);
+
+/* Builds, in device memory,
+ *   nt_lut   uint2 [heads][blocks]       (x = row block, y = column block), row-major scan order
+ *   nn_lut   uint2 [heads][nb + blocks]  header (x = offset, y = count), then (x = block id, y = column)
+ *   rblk_lut uint2 [heads][blocks]       (x = block id, y = row block)            (may be NULL)
+ *   nn_max   uint32 [1]                  longest row over all heads               (may be NULL)
+ * Replaces stride_fusion_test.cu:77-134,215-223 / fixed_fusion_test.cu:126-187,296-312.
+ * A head whose count differs from `blocks` makes status[0] non-zero (uint32 [1], may be NULL)
+ * and that head's LUTs are left untouched. */
+int sfb_lut_build(sfb_stream_t stream, const uint8_t *layout, uint32_t heads, uint32_t nb,
+                  uint32_t blocks, void *nt_lut, void *nn_lut, void *rblk_lut,
+                  uint32_t *nn_max, uint32_t *status);
+
+/* Packs element masks: bit c of word r of block k = keep(r, c).
+ *   mask_np [heads][blocks][block_size]  (the fused kernels' order, fusion_blocksparse.h:690)
+ *   mask_t  [heads][block_size][blocks]  (the unfused softmax's order, blocksparse.h:482)
+ * Words are uint32 for block_size 32 and uint64 for 64 (blocksparse.h:688).  Either may be NULL.
+ * Replaces stride_fusion_test.cu:142-187, no_fusion_test.cu:124-171, local_fusion_test.cu:146-202. */
+int sfb_mask_pack(sfb_stream_t stream, const void *nt_lut, uint32_t heads, uint32_t blocks,
+                  uint32_t block_size, int pred, uint32_t ctx, void *mask_np, void *mask_t);
+
+/* Host-only: magic-number division constants.  Replaces magicu64 (blocksparse.h:1016-1043). */
+void sfb_magicu64(uint32_t d, uint32_t *magic, uint32_t *shift);
+
+/* ---- unfused operators ---------------------------------------------------------------- */
+
+/* SDDMM: S[b,h,k] = Q[b, rows of block x, h, :] . K[b, rows of block y, h, :]^T for (x,y) = lut[k],
+ * unscaled.  Replaces bst_sgemm_nt (blocksparse.h:425-456, openai_blocksparse.h:202-233; c_dtype
+ * SFB_BF16) and bst_sgemm_nt_float (blocksparse.h:202-233; c_dtype SFB_F32).  ab_dtype is the type
+ * of a and b (the reference has SFB_F32 only).  block_size 32 or 64. */
+int sfb_bst_sgemm_nt(sfb_stream_t stream, const void *lut, const void *a, const void *b, void *c,
+                     int ab_dtype, int c_dtype, uint32_t block_size, uint32_t blocks,
+                     uint32_t batch_dim, uint32_t ctx_blks_a, uint32_t ctx_blks_b,
+                     uint32_t head_dim, uint32_t state_dim, uint32_t lut_heads, uint32_t lut_dim);
+
+/* P = softmax over the concatenated blocks of every query row of scale*S, with the optional
+ * transposed bit mask (NULL = keep all).  lut is the nn_lut; lut_dim its per-head stride
+ * (blocks + ctx_blks).  x is bf16 (x_dtype SFB_BF16) as in the reference, or SFB_F32.
+ * Replaces BlocksparseMaskedSoftmax<T,V> (blocksparse.h:649-722). */
+int sfb_masked_softmax(sfb_stream_t stream, const void *lut, const void *mask, const void *x, void *y,
+                       int x_dtype, int y_dtype, uint32_t block_size, uint32_t blocks,
+                       uint32_t batch_dim, uint32_t head_dim, uint32_t ctx_blks,
+                       uint32_t lut_heads, uint32_t lut_dim, uint32_t max_lut,
+                       uint32_t mask_heads, float scale);
+
+/* SpMM: O[b, rows of block-row i, h, :] = sum over the row's blocks k of P[b,h,k] . V[b, rows of
+ * column block of k, h, :].  op must be SFB_NN_OP.  magic/shift are accepted and ignored.
+ * Replaces bst_sgemm_xn (blocksparse.h:965-1014) for the forward (NN) case. */
+int sfb_bst_sgemm_xn(sfb_stream_t stream, const void *lut, const void *a, const void *b, void *c,
+                     int a_dtype, int bc_dtype, uint32_t block_size, uint32_t blocks,
+                     uint32_t batch_dim, uint32_t ctx_blks_b, uint32_t ctx_blks_c,
+                     uint32_t head_dim, uint32_t state_dim, uint32_t lut_heads, uint32_t lut_dim,
+                     uint32_t op, uint32_t magic, uint32_t shift, uint32_t max_lut);
+
+/* ---- fused, synchronisation-free operators -------------------------------------------- */
+
+/* SDDMM + masked softmax in one launch: each CTA owns a block-row, so there are no flags, no
+ * Max/Sum scratch and no waiting between CTAs.  mask is mask_np order (NULL = keep all);
+ * lut_dim is the nt_lut stride (`blocks`), the nn_lut stride is lut_dim + ctx_blks_a as in
+ * fusion_blocksparse.h:1245.  Replaces fusion_attention1 (fusion_blocksparse.h:400-455),
+ * fusion_attention2 (:1212-1268), fusion_attention_full (:1636-1694), fusion_attention_local
+ * (:2030-2086) and fusion_attention2_64 (:2456-2514). */
+int sfb_fused_sddmm_softmax(sfb_stream_t stream, const void *nn_lut, const void *a, const void *b,
+                            const void *mask, void *y, int ab_dtype, int y_dtype,
+                            uint32_t block_size, uint32_t blocks, uint32_t batch_dim,
+                            uint32_t ctx_blks_a, uint32_t ctx_blks_b, uint32_t head_dim,
+                            uint32_t state_dim, uint32_t lut_heads, uint32_t lut_dim,
+                            uint32_t mask_heads, float scale);
+
+/* SDDMM + softmax + SpMM in one launch: O = softmax(scale * Q K^T on the kept blocks) V with S
+ * and P never leaving the chip.  dtype is the type of q, k, v and o.  Replaces fusion_attention
+ * (fusion_blocksparse.h:2990-3050), whose kernel the reference left unfinished. */
+int sfb_fused_attention(sfb_stream_t stream, const void *nn_lut, const void *q, const void *k,
+                        const void *v, void *o, const void *mask, int dtype,
+                        uint32_t block_size, uint32_t blocks, uint32_t batch_dim,
+                        uint32_t ctx_blks, uint32_t head_dim, uint32_t state_dim,
+                        uint32_t lut_heads, uint32_t lut_dim, uint32_t mask_heads,
+                        float scale, uint32_t max_lut);
+
+/* ---- epilogue -------------------------------------------------------------------------- */
+
+/* out = LayerNorm(resid + (x + bias)) * gain + beta over rows of `hidden` elements; also writes
+ * the pre-norm sum (sum_out), mean and rstd when those are not NULL.  bias and resid may be NULL.
+ * dtype is the type of x, resid, out and sum_out; bias, gain, beta, mean, rstd are fp32.
+ * Replaces tensor_add_vector_gpu + tensor_add_tensor_gpu + layernorm_gpu
+ * (cuda_kernels.h:459-469, :449-457, :334-372; call site transformer_attention_optimize.cu:763-771). */
+int sfb_bias_residual_layernorm(sfb_stream_t stream, void *out, void *sum_out, float *mean,
+                                float *rstd, const void *x, const float *bias, const void *resid,
+                                const float *gain, const float *beta, uint32_t m, uint32_t hidden,
+                                int dtype);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

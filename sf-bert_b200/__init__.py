@@ -1,0 +1,207 @@
+"""Python host side of libsfbert_b200.so: a ctypes binding of the C ABI (include/sfbert_b200.h)
+plus thin helpers that mirror the reference's operator surface (blocksparse.h,
+fusion_blocksparse.h) on torch tensors.  torch is used for device memory and streams only;
+every operator below runs a hand-written sm_100a kernel from the shared library, and the import
+fails loudly when the library is missing -- there is no fallback."""
+import ctypes as C
+import math
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsfbert_b200.so")
+
+F32, BF16, F16 = 0, 1, 2
+LAYOUT_FULL, LAYOUT_FIXED, LAYOUT_STRIDE, LAYOUT_SAWTOOTH, LAYOUT_LOCAL, LAYOUT_BIGBIRD = range(6)
+MASK_ALL, MASK_CAUSAL_DIAG, MASK_CAUSAL_ALL, MASK_LOCAL = range(4)
+NT_OP, NN_OP, TN_OP = 0, 1, 2
+
+# every symbol include/sfbert_b200.h declares
+SYMBOLS = [
+    "sfb_last_error", "sfb_version", "sfb_layout_generate", "sfb_lut_count", "sfb_lut_build", "sfb_mask_pack",
+    "sfb_magicu64", "sfb_bst_sgemm_nt", "sfb_masked_softmax", "sfb_bst_sgemm_xn", "sfb_fused_sddmm_softmax",
+    "sfb_fused_attention", "sfb_bias_residual_layernorm",
+]
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError("%s is missing: build it with `make -C %s/csrc` (needs nvcc, sm_100a)" % (LIB_PATH, _HERE))
+lib = C.CDLL(LIB_PATH)
+lib.sfb_last_error.restype = C.c_char_p
+for _name in SYMBOLS:
+    getattr(lib, _name)
+
+_u32, _i32, _u64, _f32, _vp = C.c_uint32, C.c_int, C.c_uint64, C.c_float, C.c_void_p
+lib.sfb_layout_generate.argtypes = [_vp, _vp, _u32, _u32, _i32, _u32, _u32, _u32, _u32, _i32, _u64]
+lib.sfb_lut_count.argtypes = [_vp, _vp, _u32, _u32, _vp]
+lib.sfb_lut_build.argtypes = [_vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp]
+lib.sfb_mask_pack.argtypes = [_vp, _vp, _u32, _u32, _u32, _i32, _u32, _vp, _vp]
+lib.sfb_magicu64.argtypes = [_u32, C.POINTER(_u32), C.POINTER(_u32)]
+lib.sfb_magicu64.restype = None
+lib.sfb_bst_sgemm_nt.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 9
+lib.sfb_masked_softmax.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 9 + [_f32]
+lib.sfb_bst_sgemm_xn.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 13
+lib.sfb_fused_sddmm_softmax.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 10 + [_f32]
+lib.sfb_fused_attention.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32] + [_u32] * 8 + [_f32, _u32]
+lib.sfb_bias_residual_layernorm.argtypes = [_vp] * 10 + [_u32, _u32, _i32]
+
+
+class SfbError(RuntimeError):
+    pass
+
+
+def _check(rc):
+    if rc != 0:
+        raise SfbError(lib.sfb_last_error().decode())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+_DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+
+
+def dtype_tag(t):
+    return _DT[t.dtype]
+
+
+def magicu64(d):
+    """magicu64 of blocksparse.h:1016-1043."""
+    m, s = _u32(0), _u32(0)
+    lib.sfb_magicu64(d, C.byref(m), C.byref(s))
+    return m.value, s.value
+
+
+class BlockLayout:
+    """A block layout and its look-up tables in device memory (what the reference's test programs
+    build on the host and upload, stride_fusion_test.cu:48-227)."""
+
+    def __init__(self, layout, block_size):
+        assert layout.dtype == torch.uint8 and layout.dim() == 3 and layout.is_cuda
+        self.layout = layout.contiguous()
+        self.heads, self.nb, _ = layout.shape
+        self.block_size = block_size
+        dev = layout.device
+        counts = torch.zeros(self.heads, dtype=torch.int32, device=dev)
+        _check(lib.sfb_lut_count(_stream(), _p(self.layout), self.heads, self.nb, _p(counts)))
+        counts = counts.cpu()  # the one host read: sizes the tables
+        if int(counts.min()) != int(counts.max()):
+            raise SfbError("heads have different block counts: %s" % counts.tolist())
+        self.blocks = int(counts[0])
+        self.nt_lut = torch.zeros(self.heads, self.blocks, 2, dtype=torch.int32, device=dev)
+        self.nn_lut = torch.zeros(self.heads, self.nb + self.blocks, 2, dtype=torch.int32, device=dev)
+        self.rblk_lut = torch.zeros(self.heads, self.blocks, 2, dtype=torch.int32, device=dev)
+        nn_max = torch.zeros(1, dtype=torch.int32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        _check(lib.sfb_lut_build(_stream(), _p(self.layout), self.heads, self.nb, self.blocks, _p(self.nt_lut),
+                                 _p(self.nn_lut), _p(self.rblk_lut), _p(nn_max), _p(status)))
+        if int(status.item()) != 0:
+            raise SfbError("sfb_lut_build: block count mismatch")
+        self.nn_max = int(nn_max.item())
+        self.mask_np = None
+        self.mask_t = None
+
+    @classmethod
+    def generate(cls, kind, heads, nb, block_size, p0=0, p1=0, p2=0, p3=0, causal=0, seed=0, device="cuda"):
+        lay = torch.empty(heads, nb, nb, dtype=torch.uint8, device=device)
+        _check(lib.sfb_layout_generate(_stream(), _p(lay), heads, nb, kind, p0, p1, p2, p3, causal, seed))
+        return cls(lay, block_size)
+
+    def pack_mask(self, pred, ctx=0):
+        wt = torch.int32 if self.block_size == 32 else torch.int64
+        dev = self.layout.device
+        self.mask_np = torch.zeros(self.heads, self.blocks, self.block_size, dtype=wt, device=dev)
+        self.mask_t = torch.zeros(self.heads, self.block_size, self.blocks, dtype=wt, device=dev)
+        _check(lib.sfb_mask_pack(_stream(), _p(self.nt_lut), self.heads, self.blocks, self.block_size, pred, ctx,
+                                 _p(self.mask_np), _p(self.mask_t)))
+        return self
+
+    @property
+    def nt_lut_dim(self):
+        return self.blocks
+
+    @property
+    def nn_lut_dim(self):
+        return self.blocks + self.nb
+
+
+def _dims(q, lay):
+    B, L, H, d = q.shape
+    assert L == lay.nb * lay.block_size, "sequence length does not match the layout"
+    assert lay.heads in (1, H)
+    return B, L, H, d
+
+
+def bst_sgemm_nt(q, k, lay, out_dtype=torch.bfloat16):
+    """S = Q.K^T on the kept blocks, unscaled (bst_sgemm_nt / bst_sgemm_nt_float, blocksparse.h:425,202)."""
+    B, L, H, d = _dims(q, lay)
+    s = torch.empty(B, H, lay.blocks, lay.block_size, lay.block_size, dtype=out_dtype, device=q.device)
+    _check(lib.sfb_bst_sgemm_nt(_stream(), _p(lay.nt_lut), _p(q), _p(k), _p(s), dtype_tag(q), _DT[out_dtype],
+                                lay.block_size, lay.blocks, B, lay.nb, lay.nb, H, d, lay.heads, lay.nt_lut_dim))
+    return s
+
+
+def masked_softmax(s, lay, scale, out_dtype=torch.bfloat16, use_mask=False):
+    """BlocksparseMaskedSoftmax<T,V> (blocksparse.h:649-722)."""
+    B, H = s.shape[:2]
+    y = torch.empty(s.shape, dtype=out_dtype, device=s.device)
+    mask = lay.mask_t if use_mask else None
+    _check(lib.sfb_masked_softmax(_stream(), _p(lay.nn_lut), _p(mask), _p(s), _p(y), dtype_tag(s), _DT[out_dtype],
+                                  lay.block_size, lay.blocks, B, H, lay.nb, lay.heads, lay.nn_lut_dim, lay.nn_max,
+                                  lay.heads, scale))
+    return y
+
+
+def bst_sgemm_xn(p, v, lay):
+    """O = P.V over each block-row (bst_sgemm_xn with NN_OP, blocksparse.h:965-1014)."""
+    B, L, H, d = _dims(v, lay)
+    o = torch.empty_like(v)
+    magic, shift = magicu64((d + 63) // 64)
+    _check(lib.sfb_bst_sgemm_xn(_stream(), _p(lay.nn_lut), _p(p), _p(v), _p(o), dtype_tag(p), dtype_tag(v), lay.block_size,
+                                lay.blocks, B, lay.nb, lay.nb, H, d, lay.heads, lay.nn_lut_dim, NN_OP, magic, shift,
+                                lay.nn_max))
+    return o
+
+
+def fused_sddmm_softmax(q, k, lay, scale, out_dtype=torch.float32, use_mask=False):
+    """P = softmax(scale * Q.K^T) in one launch (fusion_attention1/2/_full/_local/2_64,
+    fusion_blocksparse.h:400,1212,1636,2030,2456)."""
+    B, L, H, d = _dims(q, lay)
+    y = torch.empty(B, H, lay.blocks, lay.block_size, lay.block_size, dtype=out_dtype, device=q.device)
+    mask = lay.mask_np if use_mask else None
+    _check(lib.sfb_fused_sddmm_softmax(_stream(), _p(lay.nn_lut), _p(q), _p(k), _p(mask), _p(y), dtype_tag(q),
+                                       _DT[out_dtype], lay.block_size, lay.blocks, B, lay.nb, lay.nb, H, d, lay.heads,
+                                       lay.nt_lut_dim, lay.heads, scale))
+    return y
+
+
+def fused_attention(q, k, v, lay, scale=None, use_mask=False, out=None):
+    """O = softmax(scale * Q.K^T on the kept blocks).V in one launch (fusion_attention,
+    fusion_blocksparse.h:2990-3050)."""
+    B, L, H, d = _dims(q, lay)
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    o = torch.empty_like(q) if out is None else out
+    mask = lay.mask_np if use_mask else None
+    _check(lib.sfb_fused_attention(_stream(), _p(lay.nn_lut), _p(q), _p(k), _p(v), _p(o), _p(mask), dtype_tag(q),
+                                   lay.block_size, lay.blocks, B, lay.nb, H, d, lay.heads, lay.nt_lut_dim, lay.heads,
+                                   scale, lay.nn_max))
+    return o
+
+
+def bias_residual_layernorm(x, bias, resid, gain, beta, want_sum=False):
+    """LayerNorm(resid + (x + bias)) (tensor_add_vector_gpu + tensor_add_tensor_gpu + layernorm_gpu,
+    cuda_kernels.h:459,449,334).  Returns (out, sum or None, mean, rstd)."""
+    m, hidden = x.shape
+    out = torch.empty_like(x)
+    summed = torch.empty_like(x) if want_sum else None
+    mean = torch.empty(m, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(m, dtype=torch.float32, device=x.device)
+    _check(lib.sfb_bias_residual_layernorm(_stream(), _p(out), _p(summed), _p(mean), _p(rstd), _p(x), _p(bias), _p(resid),
+                                           _p(gain), _p(beta), m, hidden, dtype_tag(x)))
+    return out, summed, mean, rstd

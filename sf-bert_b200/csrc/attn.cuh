@@ -1,0 +1,25 @@
+// Internal interface between the C ABI (ops.cu) and the kernel files.
+#pragma once
+#include "common.cuh"
+
+namespace sfb {
+
+struct AttnDims {
+    uint32_t B, H, d, nb_a, nb_b, blocks;
+    uint32_t lut_stride;   // uint2 per head in the LUT handed to the kernel (0 = shared by all heads)
+    uint32_t mask_stride;  // words per head in the mask (0 = shared)
+};
+
+// CUDA-core kernels (attn_simt.cu)
+int simt_sddmm_nt(cudaStream_t s, const void *lut, const void *a, const void *b, void *c, int ab_dtype, int c_dtype,
+                  uint32_t bs, const AttnDims &p);
+int simt_softmax(cudaStream_t s, const void *lut, const void *mask, const void *x, void *y, int x_dtype, int y_dtype,
+                 uint32_t bs, const AttnDims &p, float scale);
+int simt_spmm_nn(cudaStream_t s, const void *lut, const void *a, const void *b, void *c, int a_dtype, int bc_dtype,
+                 uint32_t bs, const AttnDims &p);
+int simt_fused_sddmm_softmax(cudaStream_t s, const void *nn_lut, const void *a, const void *b, const void *mask, void *y,
+                             int ab_dtype, int y_dtype, uint32_t bs, const AttnDims &p, float scale);
+int simt_fused_attention(cudaStream_t s, const void *nn_lut, const void *q, const void *k, const void *v, void *o,
+                         const void *mask, int dtype, uint32_t bs, const AttnDims &p, float scale);
+
+}  // namespace sfb

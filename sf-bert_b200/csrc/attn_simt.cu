@@ -1,0 +1,575 @@
+// FP32-arithmetic (CUDA-core) kernels of the block-sparse attention path: SDDMM, masked softmax,
+// SpMM and the two block-row-owned fusions.  They serve fp32 operands (1e-5 parity with the CPU
+// reference cannot be met on tensor cores) and every shape the tcgen05 kernels do not cover.
+//
+// Thread layout shared by all matmul kernels: 256 threads as a 16x16 grid; thread (ty,tx) owns
+// rows ty+16m and columns tx+16n of a tile, so the 16 lanes of a half-warp own one set of rows
+// and row reductions are four shuffles.
+#include "attn.cuh"
+#include <float.h>
+#include <math.h>
+
+namespace sfb {
+
+#define LOG2E_F 1.4426950408889634f
+
+
+template <int BS>
+struct MaskWord { typedef uint32_t type; };
+template <>
+struct MaskWord<64> { typedef uint64_t type; };
+
+// loads rows [row0, row0+BS) x columns [k0, k0+KC) of a [*, HD] row-major operand into smem as
+// dst[k][r] (k-major, row stride BS+1), zero beyond d
+template <int DT, int BS, int KC>
+__device__ __forceinline__ void load_tile_kmajor(float (*dst)[BS + 1], const void *src, size_t base, size_t HD,
+                                                 uint32_t k0, uint32_t d)
+{
+    for (uint32_t e = threadIdx.x; e < BS * KC; e += 256) {
+        uint32_t r = e / KC, k = e % KC;
+        float v = 0.f;
+        if (k0 + k < d) v = Elem<DT>::load(src, base + (size_t)r * HD + k0 + k);
+        dst[k][r] = v;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// SDDMM: one CTA per non-zero block
+template <int BS, int AB_DT, int C_DT>
+__global__ void __launch_bounds__(256) sddmm_nt_kernel(const uint2 *__restrict__ lut, const void *__restrict__ A,
+                                                      const void *__restrict__ Bm, void *__restrict__ C, AttnDims p)
+{
+    constexpr int KC = 32, T = BS / 16;
+    __shared__ float As[KC][BS + 1];
+    __shared__ float Bs[KC][BS + 1];
+    const uint32_t bid = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
+    const uint2 e = lut[(size_t)h * p.lut_stride + bid];
+    const size_t HD = (size_t)p.H * p.d;
+    const size_t baseA = ((size_t)b * p.nb_a * BS + (size_t)e.x * BS) * HD + (size_t)h * p.d;
+    const size_t baseB = ((size_t)b * p.nb_b * BS + (size_t)e.y * BS) * HD + (size_t)h * p.d;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+
+    float acc[T][T];
+#pragma unroll
+    for (int m = 0; m < T; m++)
+#pragma unroll
+        for (int n = 0; n < T; n++) acc[m][n] = 0.f;
+
+    for (uint32_t k0 = 0; k0 < p.d; k0 += KC) {
+        load_tile_kmajor<AB_DT, BS, KC>(As, A, baseA, HD, k0, p.d);
+        load_tile_kmajor<AB_DT, BS, KC>(Bs, Bm, baseB, HD, k0, p.d);
+        __syncthreads();
+#pragma unroll 8
+        for (int k = 0; k < KC; k++) {
+            float a[T], bb[T];
+#pragma unroll
+            for (int m = 0; m < T; m++) a[m] = As[k][ty + 16 * m];
+#pragma unroll
+            for (int n = 0; n < T; n++) bb[n] = Bs[k][tx + 16 * n];
+#pragma unroll
+            for (int m = 0; m < T; m++)
+#pragma unroll
+                for (int n = 0; n < T; n++) acc[m][n] = fmaf(a[m], bb[n], acc[m][n]);
+        }
+        __syncthreads();
+    }
+    const size_t baseC = (((size_t)b * p.H + h) * p.blocks + bid) * BS * BS;
+#pragma unroll
+    for (int m = 0; m < T; m++)
+#pragma unroll
+        for (int n = 0; n < T; n++) Elem<C_DT>::store(C, baseC + (size_t)(ty + 16 * m) * BS + tx + 16 * n, acc[m][n]);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Masked softmax: one CTA per block-row.  A lane owns 8 consecutive keys of one query row of one
+// block (16 bytes of bf16), so a warp reads 512 contiguous bytes per block; the lanes of a row
+// (BS/8 of them) combine with shuffles.  Pass 1 keeps a running max / sum over the row's blocks,
+// pass 2 re-reads the scores (L2 hits) and writes the probabilities.
+template <int X_DT>
+__device__ __forceinline__ void load8(float (&v)[8], const void *x, size_t idx)
+{
+    if (X_DT == SFB_F32) {
+        const float4 *p = (const float4 *)((const float *)x + idx);
+        float4 a = __ldg(p), b = __ldg(p + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+        uint4 u = __ldg((const uint4 *)((const uint16_t *)x + idx));
+        uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (X_DT == SFB_BF16) {
+                v[2 * i] = __uint_as_float(w[i] << 16);
+                v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            } else {
+                __half2 hh = *reinterpret_cast<__half2 *>(&w[i]);
+                float2 f = __half22float2(hh);
+                v[2 * i] = f.x;
+                v[2 * i + 1] = f.y;
+            }
+        }
+    }
+}
+
+template <int Y_DT>
+__device__ __forceinline__ void store8(void *y, size_t idx, const float (&v)[8])
+{
+    if (Y_DT == SFB_F32) {
+        float4 *p = (float4 *)((float *)y + idx);
+        p[0] = make_float4(v[0], v[1], v[2], v[3]);
+        p[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (Y_DT == SFB_BF16) {
+                w[i] = (uint32_t)to_bhalf_bits(v[2 * i]) | ((uint32_t)to_bhalf_bits(v[2 * i + 1]) << 16);
+            } else {
+                __half2 hh = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+                w[i] = *reinterpret_cast<uint32_t *>(&hh);
+            }
+        }
+        *(uint4 *)((uint16_t *)y + idx) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+template <int BS, int X_DT, int Y_DT>
+__global__ void __launch_bounds__(BS * BS / 8) softmax_kernel(const uint2 *__restrict__ lut,
+                                                        const typename MaskWord<BS>::type *__restrict__ mask,
+                                                        const void *__restrict__ X, void *__restrict__ Y, AttnDims p,
+                                                        float scale_log2e)
+{
+    typedef typename MaskWord<BS>::type W;
+    constexpr int LPR = BS / 8;  // lanes per query row
+    const uint32_t i = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
+    const uint2 *nn = lut + (size_t)h * p.lut_stride;
+    const uint2 head = nn[i];
+    const uint32_t off = head.x, cnt = head.y;
+    if (cnt == 0) return;
+    const uint32_t r = threadIdx.x / LPR;        // query row inside the block
+    const uint32_t c0 = (threadIdx.x % LPR) * 8;  // first key of this lane
+    const size_t base = ((size_t)b * p.H + h) * p.blocks * BS * BS + (size_t)r * BS + c0;
+    const W *mrow = mask ? mask + (size_t)h * p.mask_stride + (size_t)r * p.blocks : nullptr;
+
+    float mx = -INFINITY, sum = 0.f;
+    for (uint32_t e = 0; e < cnt; e++) {
+        const uint32_t blk = nn[off + e].x;
+        float v[8];
+        load8<X_DT>(v, X, base + (size_t)blk * BS * BS);
+        uint32_t bits = 0xffu;
+        if (mrow) bits = (uint32_t)((__ldg(mrow + blk) >> c0) & 0xffu);
+        float bm = -INFINITY;
+#pragma unroll
+        for (int t = 0; t < 8; t++) {
+            v[t] = ((bits >> t) & 1u) ? v[t] * scale_log2e : -INFINITY;
+            bm = fmaxf(bm, v[t]);
+        }
+        if (bm > mx) {
+            sum *= exp2f(mx - bm);  // exp2f(-inf) = 0 on the first kept element
+            mx = bm;
+        }
+        if (mx > -INFINITY) {
+#pragma unroll
+            for (int t = 0; t < 8; t++) sum += exp2f(v[t] - mx);
+        }
+    }
+    // combine the lanes of one query row
+    float rmx = mx;
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) rmx = fmaxf(rmx, __shfl_xor_sync(0xffffffffu, rmx, o));
+    float rsum = (mx > -INFINITY) ? sum * exp2f(mx - rmx) : 0.f;
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, o);
+    const float inv = rsum > 0.f ? 1.f / rsum : 0.f;
+
+    for (uint32_t e = 0; e < cnt; e++) {
+        const uint32_t blk = nn[off + e].x;
+        float v[8];
+        load8<X_DT>(v, X, base + (size_t)blk * BS * BS);
+        uint32_t bits = 0xffu;
+        if (mrow) bits = (uint32_t)((__ldg(mrow + blk) >> c0) & 0xffu);
+#pragma unroll
+        for (int t = 0; t < 8; t++)
+            v[t] = (((bits >> t) & 1u) && inv > 0.f) ? exp2f(v[t] * scale_log2e - rmx) * inv : 0.f;
+        store8<Y_DT>(Y, base + (size_t)blk * BS * BS, v);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// SpMM (NN): one CTA per (block-row, 64-wide slice of d)
+template <int BS, int A_DT, int BC_DT>
+__global__ void __launch_bounds__(256) spmm_nn_kernel(const uint2 *__restrict__ lut, const void *__restrict__ Pm,
+                                                     const void *__restrict__ V, void *__restrict__ O, AttnDims p)
+{
+    constexpr int TM = BS / 16, TN = 4;
+    __shared__ float Ps[BS][BS + 16];
+    __shared__ float Vs[BS][64];
+    const uint32_t nslice = (p.d + 63) / 64;
+    const uint32_t i = blockIdx.x / nslice, n0 = (blockIdx.x % nslice) * 64;
+    const uint32_t b = blockIdx.y, h = blockIdx.z;
+    const uint2 *nn = lut + (size_t)h * p.lut_stride;
+    const uint2 head = nn[i];
+    const size_t HD = (size_t)p.H * p.d;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+
+    float acc[TM][TN];
+#pragma unroll
+    for (int m = 0; m < TM; m++)
+#pragma unroll
+        for (int n = 0; n < TN; n++) acc[m][n] = 0.f;
+
+    for (uint32_t e = 0; e < head.y; e++) {
+        const uint2 ent = nn[head.x + e];
+        const size_t baseP = (((size_t)b * p.H + h) * p.blocks + ent.x) * BS * BS;
+        const size_t baseV = ((size_t)b * p.nb_b * BS + (size_t)ent.y * BS) * HD + (size_t)h * p.d + n0;
+        for (uint32_t t = threadIdx.x; t < BS * BS; t += 256) Ps[t / BS][t % BS] = Elem<A_DT>::load(Pm, baseP + t);
+        for (uint32_t t = threadIdx.x; t < BS * 64; t += 256) {
+            uint32_t c = t / 64, n = t % 64;
+            Vs[c][n] = (n0 + n < p.d) ? Elem<BC_DT>::load(V, baseV + (size_t)c * HD + n) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int c = 0; c < BS; c++) {
+            float a[TM], bb[TN];
+#pragma unroll
+            for (int m = 0; m < TM; m++) a[m] = Ps[ty + 16 * m][c];
+#pragma unroll
+            for (int n = 0; n < TN; n++) bb[n] = Vs[c][tx + 16 * n];
+#pragma unroll
+            for (int m = 0; m < TM; m++)
+#pragma unroll
+                for (int n = 0; n < TN; n++) acc[m][n] = fmaf(a[m], bb[n], acc[m][n]);
+        }
+        __syncthreads();
+    }
+    // rows without blocks are written as zeros (blocksparse.h:949-962)
+    const size_t baseO = ((size_t)b * p.nb_a * BS + (size_t)i * BS) * HD + (size_t)h * p.d + n0;
+#pragma unroll
+    for (int m = 0; m < TM; m++)
+#pragma unroll
+        for (int n = 0; n < TN; n++)
+            if (n0 + tx + 16 * n < p.d) Elem<BC_DT>::store(O, baseO + (size_t)(ty + 16 * m) * HD + tx + 16 * n, acc[m][n]);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Block-row-owned fusions.  Dynamic smem: Qs[DMAX][BS+1] | Ks[DMAX][BS+1] | (attention only)
+// Vs[BS][DMAX] | Ps[BS][BS+16].
+template <int BS>
+__device__ __forceinline__ void score_tile(float (&s)[BS / 16][BS / 16], const float (*Qs)[BS + 1],
+                                           const float (*Ks)[BS + 1], uint32_t d, int tx, int ty)
+{
+    constexpr int T = BS / 16;
+#pragma unroll
+    for (int m = 0; m < T; m++)
+#pragma unroll
+        for (int n = 0; n < T; n++) s[m][n] = 0.f;
+#pragma unroll 4
+    for (uint32_t k = 0; k < d; k++) {
+        float a[T], bb[T];
+#pragma unroll
+        for (int m = 0; m < T; m++) a[m] = Qs[k][ty + 16 * m];
+#pragma unroll
+        for (int n = 0; n < T; n++) bb[n] = Ks[k][tx + 16 * n];
+#pragma unroll
+        for (int m = 0; m < T; m++)
+#pragma unroll
+            for (int n = 0; n < T; n++) s[m][n] = fmaf(a[m], bb[n], s[m][n]);
+    }
+}
+
+__device__ __forceinline__ float half_warp_max(float v)
+{
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float half_warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// SDDMM + softmax, probabilities out.  Pass 1 stores the raw scores (in the output type) into Y and
+// tracks the row max / sum; pass 2 lets every thread turn the scores it wrote itself into
+// probabilities, so no thread ever reads another thread's global writes.
+template <int BS, int DMAX, int AB_DT, int Y_DT>
+__global__ void __launch_bounds__(256) fused_sddmm_softmax_kernel(const uint2 *__restrict__ lut, const void *__restrict__ A,
+                                                                 const void *__restrict__ Bm,
+                                                                 const typename MaskWord<BS>::type *__restrict__ mask,
+                                                                 void *__restrict__ Y, AttnDims p, float scale_log2e)
+{
+    typedef typename MaskWord<BS>::type W;
+    constexpr int T = BS / 16;
+    extern __shared__ float smem[];
+    float (*Qs)[BS + 1] = (float (*)[BS + 1])smem;
+    float (*Ks)[BS + 1] = (float (*)[BS + 1])(smem + DMAX * (BS + 1));
+    const uint32_t i = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
+    const uint2 *nn = lut + (size_t)h * p.lut_stride;
+    const uint2 head = nn[i];
+    if (head.y == 0) return;
+    const size_t HD = (size_t)p.H * p.d;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const W *mh = mask ? mask + (size_t)h * p.mask_stride : nullptr;
+
+    for (uint32_t k0 = 0; k0 < p.d; k0 += 32)
+        load_tile_kmajor<AB_DT, BS, 32>(Qs + k0, A, ((size_t)b * p.nb_a * BS + (size_t)i * BS) * HD + (size_t)h * p.d, HD, k0, p.d);
+
+    float mx[T], sum[T];
+#pragma unroll
+    for (int m = 0; m < T; m++) { mx[m] = -INFINITY; sum[m] = 0.f; }
+
+    for (uint32_t e = 0; e < head.y; e++) {
+        const uint2 ent = nn[head.x + e];
+        __syncthreads();
+        for (uint32_t k0 = 0; k0 < p.d; k0 += 32)
+            load_tile_kmajor<AB_DT, BS, 32>(Ks + k0, Bm, ((size_t)b * p.nb_b * BS + (size_t)ent.y * BS) * HD + (size_t)h * p.d, HD, k0, p.d);
+        __syncthreads();
+        float s[T][T];
+        score_tile<BS>(s, Qs, Ks, p.d, tx, ty);
+        const size_t baseY = (((size_t)b * p.H + h) * p.blocks + ent.x) * BS * BS;
+#pragma unroll
+        for (int m = 0; m < T; m++) {
+            const uint32_t r = ty + 16 * m;
+            const W w = mh ? __ldg(mh + (size_t)ent.x * BS + r) : ~(W)0;
+            float bm = -INFINITY, t[T];
+#pragma unroll
+            for (int n = 0; n < T; n++) {
+                const uint32_t c = tx + 16 * n;
+                // the stored (possibly 16-bit) score is what pass 2 will read: use it for the statistics too
+                Elem<Y_DT>::store(Y, baseY + (size_t)r * BS + c, s[m][n]);
+                float sv = Elem<Y_DT>::round(s[m][n]);
+                t[n] = ((w >> c) & 1) ? sv * scale_log2e : -INFINITY;
+                bm = fmaxf(bm, t[n]);
+            }
+            bm = half_warp_max(bm);
+            if (bm > mx[m]) {
+                sum[m] *= exp2f(mx[m] - bm);
+                mx[m] = bm;
+            }
+            float ps = 0.f;
+            if (mx[m] > -INFINITY) {
+#pragma unroll
+                for (int n = 0; n < T; n++) ps += exp2f(t[n] - mx[m]);
+            }
+            sum[m] += half_warp_sum(ps);
+        }
+    }
+    for (uint32_t e = 0; e < head.y; e++) {
+        const uint2 ent = nn[head.x + e];
+        const size_t baseY = (((size_t)b * p.H + h) * p.blocks + ent.x) * BS * BS;
+#pragma unroll
+        for (int m = 0; m < T; m++) {
+            const uint32_t r = ty + 16 * m;
+            const W w = mh ? __ldg(mh + (size_t)ent.x * BS + r) : ~(W)0;
+            const float inv = sum[m] > 0.f ? 1.f / sum[m] : 0.f;
+#pragma unroll
+            for (int n = 0; n < T; n++) {
+                const uint32_t c = tx + 16 * n;
+                float sv = Elem<Y_DT>::load(Y, baseY + (size_t)r * BS + c);
+                float pv = (((w >> c) & 1) && inv > 0.f) ? exp2f(sv * scale_log2e - mx[m]) * inv : 0.f;
+                Elem<Y_DT>::store(Y, baseY + (size_t)r * BS + c, pv);
+            }
+        }
+    }
+}
+
+// SDDMM + softmax + SpMM with an online softmax; S and P never leave the SM.
+template <int BS, int DMAX, int DT>
+__global__ void __launch_bounds__(256) fused_attention_kernel(const uint2 *__restrict__ lut, const void *__restrict__ Q,
+                                                             const void *__restrict__ K, const void *__restrict__ V,
+                                                             void *__restrict__ O,
+                                                             const typename MaskWord<BS>::type *__restrict__ mask,
+                                                             AttnDims p, float scale_log2e)
+{
+    typedef typename MaskWord<BS>::type W;
+    constexpr int T = BS / 16, TD = DMAX / 16;
+    extern __shared__ float smem[];
+    float (*Qs)[BS + 1] = (float (*)[BS + 1])smem;
+    float (*Ks)[BS + 1] = (float (*)[BS + 1])(smem + DMAX * (BS + 1));
+    float (*Vs)[DMAX] = (float (*)[DMAX])(smem + 2 * DMAX * (BS + 1));
+    float (*Ps)[BS + 16] = (float (*)[BS + 16])(smem + 2 * DMAX * (BS + 1) + BS * DMAX);
+    const uint32_t i = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
+    const uint2 *nn = lut + (size_t)h * p.lut_stride;
+    const uint2 head = nn[i];
+    const size_t HD = (size_t)p.H * p.d;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const W *mh = mask ? mask + (size_t)h * p.mask_stride : nullptr;
+
+    if (head.y)
+        for (uint32_t k0 = 0; k0 < p.d; k0 += 32)
+            load_tile_kmajor<DT, BS, 32>(Qs + k0, Q, ((size_t)b * p.nb_a * BS + (size_t)i * BS) * HD + (size_t)h * p.d, HD, k0, p.d);
+
+    float mx[T], sum[T], acc[T][TD];
+#pragma unroll
+    for (int m = 0; m < T; m++) {
+        mx[m] = -INFINITY;
+        sum[m] = 0.f;
+#pragma unroll
+        for (int n = 0; n < TD; n++) acc[m][n] = 0.f;
+    }
+
+    for (uint32_t e = 0; e < head.y; e++) {
+        const uint2 ent = nn[head.x + e];
+        const size_t baseKV = ((size_t)b * p.nb_b * BS + (size_t)ent.y * BS) * HD + (size_t)h * p.d;
+        __syncthreads();
+        for (uint32_t k0 = 0; k0 < p.d; k0 += 32) load_tile_kmajor<DT, BS, 32>(Ks + k0, K, baseKV, HD, k0, p.d);
+        for (uint32_t t = threadIdx.x; t < BS * DMAX; t += 256) {
+            uint32_t c = t / DMAX, n = t % DMAX;
+            Vs[c][n] = n < p.d ? Elem<DT>::load(V, baseKV + (size_t)c * HD + n) : 0.f;
+        }
+        __syncthreads();
+        float s[T][T];
+        score_tile<BS>(s, Qs, Ks, p.d, tx, ty);
+#pragma unroll
+        for (int m = 0; m < T; m++) {
+            const uint32_t r = ty + 16 * m;
+            const W w = mh ? __ldg(mh + (size_t)ent.x * BS + r) : ~(W)0;
+            float bm = -INFINITY;
+#pragma unroll
+            for (int n = 0; n < T; n++) {
+                const uint32_t c = tx + 16 * n;
+                s[m][n] = ((w >> c) & 1) ? s[m][n] * scale_log2e : -INFINITY;
+                bm = fmaxf(bm, s[m][n]);
+            }
+            bm = half_warp_max(bm);
+            float alpha = 1.f;
+            if (bm > mx[m]) {
+                alpha = exp2f(mx[m] - bm);
+                mx[m] = bm;
+            }
+            float ps = 0.f;
+#pragma unroll
+            for (int n = 0; n < T; n++) {
+                float pv = mx[m] > -INFINITY ? exp2f(s[m][n] - mx[m]) : 0.f;
+                Ps[r][tx + 16 * n] = pv;
+                ps += pv;
+            }
+            sum[m] = sum[m] * alpha + half_warp_sum(ps);
+#pragma unroll
+            for (int n = 0; n < TD; n++) acc[m][n] *= alpha;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int c = 0; c < BS; c++) {
+            float a[T], bb[TD];
+#pragma unroll
+            for (int m = 0; m < T; m++) a[m] = Ps[ty + 16 * m][c];
+#pragma unroll
+            for (int n = 0; n < TD; n++) bb[n] = Vs[c][tx + 16 * n];
+#pragma unroll
+            for (int m = 0; m < T; m++)
+#pragma unroll
+                for (int n = 0; n < TD; n++) acc[m][n] = fmaf(a[m], bb[n], acc[m][n]);
+        }
+    }
+    const size_t baseO = ((size_t)b * p.nb_a * BS + (size_t)i * BS) * HD + (size_t)h * p.d;
+#pragma unroll
+    for (int m = 0; m < T; m++) {
+        const float inv = sum[m] > 0.f ? 1.f / sum[m] : 0.f;
+#pragma unroll
+        for (int n = 0; n < TD; n++)
+            if ((uint32_t)(tx + 16 * n) < p.d)
+                Elem<DT>::store(O, baseO + (size_t)(ty + 16 * m) * HD + tx + 16 * n, acc[m][n] * inv);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host-side dispatch
+#define DISPATCH_BS(bs, ...)            \
+    if (bs == 32) { constexpr int BS = 32; __VA_ARGS__ } else { constexpr int BS = 64; __VA_ARGS__ }
+#define DISPATCH_DT(dt, NAME, ...)                                         \
+    if (dt == SFB_F32) { constexpr int NAME = SFB_F32; __VA_ARGS__ }        \
+    else if (dt == SFB_BF16) { constexpr int NAME = SFB_BF16; __VA_ARGS__ } \
+    else { constexpr int NAME = SFB_F16; __VA_ARGS__ }
+
+int simt_sddmm_nt(cudaStream_t s, const void *lut, const void *a, const void *b, void *c, int ab_dtype, int c_dtype,
+                  uint32_t bs, const AttnDims &p)
+{
+    dim3 grid(p.blocks, p.B, p.H);
+    DISPATCH_BS(bs, DISPATCH_DT(ab_dtype, AB, {
+        if (c_dtype == SFB_F32) sddmm_nt_kernel<BS, AB, SFB_F32><<<grid, 256, 0, s>>>((const uint2 *)lut, a, b, c, p);
+        else if (c_dtype == SFB_BF16) sddmm_nt_kernel<BS, AB, SFB_BF16><<<grid, 256, 0, s>>>((const uint2 *)lut, a, b, c, p);
+        else sddmm_nt_kernel<BS, AB, SFB_F16><<<grid, 256, 0, s>>>((const uint2 *)lut, a, b, c, p);
+    }))
+    return check_launch("sfb_bst_sgemm_nt");
+}
+
+int simt_softmax(cudaStream_t s, const void *lut, const void *mask, const void *x, void *y, int x_dtype, int y_dtype,
+                 uint32_t bs, const AttnDims &p, float scale)
+{
+    dim3 grid(p.nb_a, p.B, p.H);
+    const float sl = scale * LOG2E_F;
+    DISPATCH_BS(bs, {
+        typedef typename MaskWord<BS>::type W;
+        if (x_dtype == SFB_BF16) {
+            DISPATCH_DT(y_dtype, YD, { softmax_kernel<BS, SFB_BF16, YD><<<grid, BS * BS / 8, 0, s>>>((const uint2 *)lut, (const W *)mask, x, y, p, sl); })
+        } else {
+            DISPATCH_DT(y_dtype, YD, { softmax_kernel<BS, SFB_F32, YD><<<grid, BS * BS / 8, 0, s>>>((const uint2 *)lut, (const W *)mask, x, y, p, sl); })
+        }
+    })
+    return check_launch("sfb_masked_softmax");
+}
+
+int simt_spmm_nn(cudaStream_t s, const void *lut, const void *a, const void *b, void *c, int a_dtype, int bc_dtype,
+                 uint32_t bs, const AttnDims &p)
+{
+    dim3 grid(p.nb_a * ((p.d + 63) / 64), p.B, p.H);
+    DISPATCH_BS(bs, DISPATCH_DT(a_dtype, AD, DISPATCH_DT(bc_dtype, BD, {
+        spmm_nn_kernel<BS, AD, BD><<<grid, 256, 0, s>>>((const uint2 *)lut, a, b, c, p);
+    })))
+    return check_launch("sfb_bst_sgemm_xn");
+}
+
+template <typename K>
+static int set_smem(K kernel, size_t bytes)
+{
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return fail("cudaFuncSetAttribute(%zu bytes): %s", bytes, cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+int simt_fused_sddmm_softmax(cudaStream_t s, const void *nn_lut, const void *a, const void *b, const void *mask, void *y,
+                             int ab_dtype, int y_dtype, uint32_t bs, const AttnDims &p, float scale)
+{
+    SFB_REQUIRE(p.d <= 128, "sfb_fused_sddmm_softmax: state_dim %u > 128 not supported", p.d);
+    dim3 grid(p.nb_a, p.B, p.H);
+    const float sl = scale * LOG2E_F;
+#define LAUNCH_FSS(DMAX)                                                                                         \
+    {                                                                                                            \
+        typedef typename MaskWord<BS>::type W;                                                                   \
+        size_t bytes = sizeof(float) * 2 * DMAX * (BS + 1);                                                      \
+        auto kern = fused_sddmm_softmax_kernel<BS, DMAX, AB, YD>;                                                \
+        if (set_smem(kern, bytes)) return 1;                                                                     \
+        kern<<<grid, 256, bytes, s>>>((const uint2 *)nn_lut, a, b, (const W *)mask, y, p, sl);                   \
+    }
+    DISPATCH_BS(bs, DISPATCH_DT(ab_dtype, AB, DISPATCH_DT(y_dtype, YD, {
+        if (p.d <= 64) LAUNCH_FSS(64) else LAUNCH_FSS(128)
+    })))
+#undef LAUNCH_FSS
+    return check_launch("sfb_fused_sddmm_softmax");
+}
+
+int simt_fused_attention(cudaStream_t s, const void *nn_lut, const void *q, const void *k, const void *v, void *o,
+                         const void *mask, int dtype, uint32_t bs, const AttnDims &p, float scale)
+{
+    SFB_REQUIRE(p.d <= 128, "sfb_fused_attention: state_dim %u > 128 not supported", p.d);
+    dim3 grid(p.nb_a, p.B, p.H);
+    const float sl = scale * LOG2E_F;
+#define LAUNCH_FA(DMAX)                                                                                          \
+    {                                                                                                            \
+        typedef typename MaskWord<BS>::type W;                                                                   \
+        size_t bytes = sizeof(float) * (2 * DMAX * (BS + 1) + BS * DMAX + BS * (BS + 16));                       \
+        auto kern = fused_attention_kernel<BS, DMAX, DT>;                                                        \
+        if (set_smem(kern, bytes)) return 1;                                                                     \
+        kern<<<grid, 256, bytes, s>>>((const uint2 *)nn_lut, q, k, v, o, (const W *)mask, p, sl);                \
+    }
+    DISPATCH_BS(bs, DISPATCH_DT(dtype, DT, {
+        if (p.d <= 64) LAUNCH_FA(64) else LAUNCH_FA(128)
+    }))
+#undef LAUNCH_FA
+    return check_launch("sfb_fused_attention");
+}
+
+}  // namespace sfb

@@ -1,0 +1,76 @@
+// Shared helpers of libsfbert_b200: error reporting, element conversion, LUT access.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+#include "../../include/sfbert_b200.h"
+
+namespace sfb {
+
+// ---- host: error string (thread local) -----------------------------------------------------
+char *error_buffer();
+int fail(const char *fmt, ...);
+void clear_error();
+int check_launch(const char *what);
+
+#define SFB_REQUIRE(cond, ...)                 \
+    do {                                       \
+        if (!(cond)) return sfb::fail(__VA_ARGS__); \
+    } while (0)
+
+static inline cudaStream_t as_stream(sfb_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// ---- device: element conversion -------------------------------------------------------------
+// fp32 -> bf16 bits the way the reference stores S and P (ew_op_gpu.h:241-253): add half a bf16
+// ulp of the magnitude, round toward zero, keep the upper 16 bits.
+__device__ __forceinline__ uint16_t to_bhalf_bits(float v)
+{
+    uint32_t u = __float_as_uint(v);
+    float e = __uint_as_float(u & 0xff800000u);
+    float f;
+    asm("fma.rz.ftz.f32 %0, %1, 0f3b800000, %2;" : "=f"(f) : "f"(e), "f"(v));
+    return (uint16_t)(__float_as_uint(f) >> 16);
+}
+__device__ __forceinline__ float from_bhalf_bits(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
+
+template <int DT> struct Elem;
+template <> struct Elem<SFB_F32> {
+    typedef float type;
+    static __device__ __forceinline__ float load(const void *p, size_t i) { return ((const float *)p)[i]; }
+    static __device__ __forceinline__ void store(void *p, size_t i, float v) { ((float *)p)[i] = v; }
+    static __device__ __forceinline__ float round(float v) { return v; }
+};
+template <> struct Elem<SFB_BF16> {
+    typedef uint16_t type;
+    static __device__ __forceinline__ float load(const void *p, size_t i) { return from_bhalf_bits(((const uint16_t *)p)[i]); }
+    static __device__ __forceinline__ void store(void *p, size_t i, float v) { ((uint16_t *)p)[i] = to_bhalf_bits(v); }
+    static __device__ __forceinline__ float round(float v) { return from_bhalf_bits(to_bhalf_bits(v)); }
+};
+template <> struct Elem<SFB_F16> {
+    typedef __half type;
+    static __device__ __forceinline__ float load(const void *p, size_t i) { return __half2float(((const __half *)p)[i]); }
+    static __device__ __forceinline__ void store(void *p, size_t i, float v) { ((__half *)p)[i] = __float2half_rn(v); }
+    static __device__ __forceinline__ float round(float v) { return __half2float(__float2half_rn(v)); }
+};
+
+static inline size_t elem_size(int dt) { return dt == SFB_F32 ? 4 : 2; }
+static inline bool valid_dtype(int dt) { return dt == SFB_F32 || dt == SFB_BF16 || dt == SFB_F16; }
+
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+}  // namespace sfb

@@ -1,0 +1,181 @@
+// Fused bias + residual + LayerNorm: one pass over HBM (read x and resid, write out and,
+// optionally, the pre-norm sum), one warp per row with 16-byte accesses and the row held in
+// registers.  Replaces three launches of the reference (cuda_kernels.h:334-372,449-469).
+#include "common.cuh"
+
+namespace sfb {
+
+template <int DT> struct Vec8;
+template <> struct Vec8<SFB_F32> {
+    static constexpr int N = 4;  // elements per 16-byte access
+    static __device__ __forceinline__ void load(float (&v)[4], const void *p, size_t i)
+    {
+        float4 t = *(const float4 *)((const float *)p + i);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    }
+    static __device__ __forceinline__ void store(void *p, size_t i, const float (&v)[4])
+    {
+        *(float4 *)((float *)p + i) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Vec8<SFB_BF16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(float (&v)[8], const void *p, size_t i)
+    {
+        uint4 u = *(const uint4 *)((const uint16_t *)p + i);
+        uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            v[2 * t] = __uint_as_float(w[t] << 16);
+            v[2 * t + 1] = __uint_as_float(w[t] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ void store(void *p, size_t i, const float (&v)[8])
+    {
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * t], v[2 * t + 1]);
+            w[t] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        *(uint4 *)((uint16_t *)p + i) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+template <> struct Vec8<SFB_F16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(float (&v)[8], const void *p, size_t i)
+    {
+        uint4 u = *(const uint4 *)((const uint16_t *)p + i);
+        uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            float2 f = __half22float2(*reinterpret_cast<__half2 *>(&w[t]));
+            v[2 * t] = f.x;
+            v[2 * t + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(void *p, size_t i, const float (&v)[8])
+    {
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            __half2 h = __floats2half2_rn(v[2 * t], v[2 * t + 1]);
+            w[t] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        *(uint4 *)((uint16_t *)p + i) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
+// CHUNKS 16-byte accesses per lane: hidden <= 32 * CHUNKS * N.  One warp per row, ROWS_PER_CTA warps.
+template <int DT, int CHUNKS>
+__global__ void __launch_bounds__(256) bias_residual_layernorm_kernel(void *__restrict__ out, void *__restrict__ sum_out,
+                                                                     float *__restrict__ mean, float *__restrict__ rstd,
+                                                                     const void *__restrict__ x, const float *__restrict__ bias,
+                                                                     const void *__restrict__ resid, const float *__restrict__ gain,
+                                                                     const float *__restrict__ beta, uint32_t m, uint32_t hidden)
+{
+    constexpr int N = Vec8<DT>::N;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= m) return;
+    const size_t base = (size_t)row * hidden;
+    float v[CHUNKS][N];
+    float s = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; c++) {
+        const uint32_t col = (c * 32 + lane) * N;
+        if (col < hidden) {
+            Vec8<DT>::load(v[c], x, base + col);
+            if (bias) {
+#pragma unroll
+                for (int t = 0; t < N; t += 4) {
+                    float4 bb = __ldg((const float4 *)(bias + col + t));
+                    v[c][t] += bb.x; v[c][t + 1] += bb.y; v[c][t + 2] += bb.z; v[c][t + 3] += bb.w;
+                }
+            }
+            if (resid) {
+                float r[N];
+                Vec8<DT>::load(r, resid, base + col);
+#pragma unroll
+                for (int t = 0; t < N; t++) v[c][t] = r[t] + v[c][t];
+            }
+            if (sum_out) Vec8<DT>::store(sum_out, base + col, v[c]);
+#pragma unroll
+            for (int t = 0; t < N; t++) {
+                s += v[c][t];
+                s2 = fmaf(v[c][t], v[c][t], s2);
+            }
+        }
+    }
+    s = warp_sum(s);
+    s2 = warp_sum(s2);
+    const float mu = s / (float)hidden;
+    // var = E[x^2] - mean^2 with eps inside the root (layernorm.h:28-30)
+    const float rs = rsqrtf(fmaxf(s2 / (float)hidden - mu * mu, 0.f) + 1e-5f);
+    if (lane == 0) {
+        if (mean) mean[row] = mu;
+        if (rstd) rstd[row] = rs;
+    }
+#pragma unroll
+    for (int c = 0; c < CHUNKS; c++) {
+        const uint32_t col = (c * 32 + lane) * N;
+        if (col < hidden) {
+            float y[N];
+#pragma unroll
+            for (int t = 0; t < N; t += 4) {
+                float4 g = __ldg((const float4 *)(gain + col + t));
+                float4 be = __ldg((const float4 *)(beta + col + t));
+                y[t] = (v[c][t] - mu) * rs * g.x + be.x;
+                y[t + 1] = (v[c][t + 1] - mu) * rs * g.y + be.y;
+                y[t + 2] = (v[c][t + 2] - mu) * rs * g.z + be.z;
+                y[t + 3] = (v[c][t + 3] - mu) * rs * g.w + be.w;
+            }
+            Vec8<DT>::store(out, base + col, y);
+        }
+    }
+}
+
+template <int DT>
+static int launch_ln(cudaStream_t s, void *out, void *sum_out, float *mean, float *rstd, const void *x, const float *bias,
+                     const void *resid, const float *gain, const float *beta, uint32_t m, uint32_t hidden)
+{
+    constexpr int N = Vec8<DT>::N;
+    const uint32_t per_chunk = 32 * N;
+    const uint32_t chunks = (hidden + per_chunk - 1) / per_chunk;
+    const uint32_t rows_per_cta = 8;
+    dim3 grid((m + rows_per_cta - 1) / rows_per_cta);
+#define LN_CASE(C)                                                                                                   \
+    bias_residual_layernorm_kernel<DT, C><<<grid, 32 * rows_per_cta, 0, s>>>(out, sum_out, mean, rstd, x, bias, resid, \
+                                                                             gain, beta, m, hidden)
+    if (chunks <= 1) LN_CASE(1);
+    else if (chunks <= 2) LN_CASE(2);
+    else if (chunks <= 3) LN_CASE(3);
+    else if (chunks <= 4) LN_CASE(4);
+    else if (chunks <= 6) LN_CASE(6);
+    else if (chunks <= 8) LN_CASE(8);
+    else if (chunks <= 16) LN_CASE(16);
+    else return fail("sfb_bias_residual_layernorm: hidden %u too large (max %u)", hidden, 16 * per_chunk);
+#undef LN_CASE
+    return check_launch("sfb_bias_residual_layernorm");
+}
+
+}  // namespace sfb
+
+using namespace sfb;
+
+extern "C" int sfb_bias_residual_layernorm(sfb_stream_t stream, void *out, void *sum_out, float *mean, float *rstd,
+                                           const void *x, const float *bias, const void *resid, const float *gain,
+                                           const float *beta, uint32_t m, uint32_t hidden, int dtype)
+{
+    SFB_REQUIRE(out && x && gain && beta, "sfb_bias_residual_layernorm: NULL pointer");
+    SFB_REQUIRE(valid_dtype(dtype), "sfb_bias_residual_layernorm: unknown dtype %d", dtype);
+    SFB_REQUIRE(hidden >= 8 && hidden % 8 == 0, "sfb_bias_residual_layernorm: hidden %u must be a multiple of 8", hidden);
+    const uintptr_t al = (uintptr_t)out | (uintptr_t)x | (uintptr_t)sum_out | (uintptr_t)resid | (uintptr_t)bias |
+                         (uintptr_t)gain | (uintptr_t)beta;
+    SFB_REQUIRE((al & 15) == 0, "sfb_bias_residual_layernorm: pointers must be 16-byte aligned");
+    if (m == 0) { clear_error(); return 0; }
+    cudaStream_t s = as_stream(stream);
+    if (dtype == SFB_F32) return launch_ln<SFB_F32>(s, out, sum_out, mean, rstd, x, bias, resid, gain, beta, m, hidden);
+    if (dtype == SFB_BF16) return launch_ln<SFB_BF16>(s, out, sum_out, mean, rstd, x, bias, resid, gain, beta, m, hidden);
+    return launch_ln<SFB_F16>(s, out, sum_out, mean, rstd, x, bias, resid, gain, beta, m, hidden);
+}

@@ -1,0 +1,103 @@
+// C ABI of the attention operators: argument checks and the choice between the tensor-core
+// (tcgen05) kernels and the CUDA-core kernels.  No path leaves the GPU.
+#include "attn.cuh"
+
+using namespace sfb;
+
+static int check_common(const char *who, uint32_t bs, uint32_t B, uint32_t H, uint32_t d, uint32_t lut_heads)
+{
+    SFB_REQUIRE(bs == 32 || bs == 64, "%s: block_size %u not supported (32 or 64)", who, bs);
+    SFB_REQUIRE(B >= 1 && B <= 65535 && H >= 1 && H <= 65535, "%s: batch_dim=%u / head_dim=%u out of range", who, B, H);
+    SFB_REQUIRE(d >= 1, "%s: state_dim is 0", who);
+    SFB_REQUIRE(lut_heads == 1 || lut_heads == H, "%s: lut_heads=%u must be 1 or head_dim=%u", who, lut_heads, H);
+    return 0;
+}
+
+static bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+
+extern "C" int sfb_bst_sgemm_nt(sfb_stream_t stream, const void *lut, const void *a, const void *b, void *c, int ab_dtype,
+                                int c_dtype, uint32_t block_size, uint32_t blocks, uint32_t batch_dim, uint32_t ctx_blks_a,
+                                uint32_t ctx_blks_b, uint32_t head_dim, uint32_t state_dim, uint32_t lut_heads, uint32_t lut_dim)
+{
+    const char *who = "sfb_bst_sgemm_nt";
+    SFB_REQUIRE(lut && a && b && c, "%s: NULL pointer", who);
+    SFB_REQUIRE(valid_dtype(ab_dtype) && valid_dtype(c_dtype), "%s: unknown dtype", who);
+    if (check_common(who, block_size, batch_dim, head_dim, state_dim, lut_heads)) return 1;
+    SFB_REQUIRE(lut_heads == 1 || lut_dim >= blocks, "%s: lut_dim %u smaller than blocks %u", who, lut_dim, blocks);
+    if (blocks == 0) { clear_error(); return 0; }
+    AttnDims p = {batch_dim, head_dim, state_dim, ctx_blks_a, ctx_blks_b, blocks, lut_heads > 1 ? lut_dim : 0, 0};
+    return simt_sddmm_nt(as_stream(stream), lut, a, b, c, ab_dtype, c_dtype, block_size, p);
+}
+
+extern "C" int sfb_masked_softmax(sfb_stream_t stream, const void *lut, const void *mask, const void *x, void *y, int x_dtype,
+                                  int y_dtype, uint32_t block_size, uint32_t blocks, uint32_t batch_dim, uint32_t head_dim,
+                                  uint32_t ctx_blks, uint32_t lut_heads, uint32_t lut_dim, uint32_t max_lut, uint32_t mask_heads,
+                                  float scale)
+{
+    const char *who = "sfb_masked_softmax";
+    (void)max_lut;  // the reference sizes its CTA from it (blocksparse.h:665-680); rows of any length are handled here
+    SFB_REQUIRE(lut && x && y, "%s: NULL pointer", who);
+    SFB_REQUIRE(x_dtype == SFB_BF16 || x_dtype == SFB_F32, "%s: x must be bf16 or fp32", who);
+    SFB_REQUIRE(valid_dtype(y_dtype), "%s: unknown y dtype", who);
+    if (check_common(who, block_size, batch_dim, head_dim, 1, lut_heads)) return 1;
+    SFB_REQUIRE(mask_heads == 1 || mask_heads == head_dim, "%s: mask_heads=%u must be 1 or head_dim", who, mask_heads);
+    SFB_REQUIRE(lut_heads == 1 || lut_dim >= blocks + ctx_blks, "%s: lut_dim %u smaller than blocks+ctx_blks", who, lut_dim);
+    SFB_REQUIRE(aligned16(x) && aligned16(y), "%s: x and y must be 16-byte aligned", who);
+    if (blocks == 0 || ctx_blks == 0) { clear_error(); return 0; }
+    AttnDims p = {batch_dim, head_dim, 0, ctx_blks, ctx_blks, blocks, lut_heads > 1 ? lut_dim : 0,
+                  mask_heads > 1 ? blocks * block_size : 0};
+    return simt_softmax(as_stream(stream), lut, mask, x, y, x_dtype, y_dtype, block_size, p, scale);
+}
+
+extern "C" int sfb_bst_sgemm_xn(sfb_stream_t stream, const void *lut, const void *a, const void *b, void *c, int a_dtype,
+                                int bc_dtype, uint32_t block_size, uint32_t blocks, uint32_t batch_dim, uint32_t ctx_blks_b,
+                                uint32_t ctx_blks_c, uint32_t head_dim, uint32_t state_dim, uint32_t lut_heads, uint32_t lut_dim,
+                                uint32_t op, uint32_t magic, uint32_t shift, uint32_t max_lut)
+{
+    const char *who = "sfb_bst_sgemm_xn";
+    (void)magic; (void)shift; (void)max_lut;
+    SFB_REQUIRE(lut && a && b && c, "%s: NULL pointer", who);
+    SFB_REQUIRE(op == SFB_NN_OP, "%s: op %u not supported (forward NN only)", who, op);
+    SFB_REQUIRE(valid_dtype(a_dtype) && valid_dtype(bc_dtype), "%s: unknown dtype", who);
+    if (check_common(who, block_size, batch_dim, head_dim, state_dim, lut_heads)) return 1;
+    SFB_REQUIRE(lut_heads == 1 || lut_dim >= blocks + ctx_blks_c, "%s: lut_dim %u smaller than blocks+ctx_blks", who, lut_dim);
+    if (ctx_blks_c == 0) { clear_error(); return 0; }
+    AttnDims p = {batch_dim, head_dim, state_dim, ctx_blks_c, ctx_blks_b, blocks, lut_heads > 1 ? lut_dim : 0, 0};
+    return simt_spmm_nn(as_stream(stream), lut, a, b, c, a_dtype, bc_dtype, block_size, p);
+}
+
+extern "C" int sfb_fused_sddmm_softmax(sfb_stream_t stream, const void *nn_lut, const void *a, const void *b, const void *mask,
+                                       void *y, int ab_dtype, int y_dtype, uint32_t block_size, uint32_t blocks,
+                                       uint32_t batch_dim, uint32_t ctx_blks_a, uint32_t ctx_blks_b, uint32_t head_dim,
+                                       uint32_t state_dim, uint32_t lut_heads, uint32_t lut_dim, uint32_t mask_heads, float scale)
+{
+    const char *who = "sfb_fused_sddmm_softmax";
+    SFB_REQUIRE(nn_lut && a && b && y, "%s: NULL pointer", who);
+    SFB_REQUIRE(valid_dtype(ab_dtype) && valid_dtype(y_dtype), "%s: unknown dtype", who);
+    if (check_common(who, block_size, batch_dim, head_dim, state_dim, lut_heads)) return 1;
+    SFB_REQUIRE(mask_heads == 1 || mask_heads == head_dim, "%s: mask_heads=%u must be 1 or head_dim", who, mask_heads);
+    SFB_REQUIRE(lut_heads == 1 || lut_dim >= blocks, "%s: lut_dim %u smaller than blocks %u", who, lut_dim, blocks);
+    if (blocks == 0 || ctx_blks_a == 0) { clear_error(); return 0; }
+    // the nn_lut of head h starts at h * (lut_dim + ctx_blks_a)  (fusion_blocksparse.h:1245)
+    AttnDims p = {batch_dim, head_dim, state_dim, ctx_blks_a, ctx_blks_b, blocks, lut_heads > 1 ? lut_dim + ctx_blks_a : 0,
+                  mask_heads > 1 ? blocks * block_size : 0};
+    return simt_fused_sddmm_softmax(as_stream(stream), nn_lut, a, b, mask, y, ab_dtype, y_dtype, block_size, p, scale);
+}
+
+extern "C" int sfb_fused_attention(sfb_stream_t stream, const void *nn_lut, const void *q, const void *k, const void *v, void *o,
+                                   const void *mask, int dtype, uint32_t block_size, uint32_t blocks, uint32_t batch_dim,
+                                   uint32_t ctx_blks, uint32_t head_dim, uint32_t state_dim, uint32_t lut_heads, uint32_t lut_dim,
+                                   uint32_t mask_heads, float scale, uint32_t max_lut)
+{
+    const char *who = "sfb_fused_attention";
+    (void)max_lut;
+    SFB_REQUIRE(nn_lut && q && k && v && o, "%s: NULL pointer", who);
+    SFB_REQUIRE(valid_dtype(dtype), "%s: unknown dtype %d", who, dtype);
+    if (check_common(who, block_size, batch_dim, head_dim, state_dim, lut_heads)) return 1;
+    SFB_REQUIRE(mask_heads == 1 || mask_heads == head_dim, "%s: mask_heads=%u must be 1 or head_dim", who, mask_heads);
+    SFB_REQUIRE(lut_heads == 1 || lut_dim >= blocks, "%s: lut_dim %u smaller than blocks %u", who, lut_dim, blocks);
+    if (ctx_blks == 0) { clear_error(); return 0; }
+    AttnDims p = {batch_dim, head_dim, state_dim, ctx_blks, ctx_blks, blocks, lut_heads > 1 ? lut_dim + ctx_blks : 0,
+                  mask_heads > 1 ? blocks * block_size : 0};
+    return simt_fused_attention(as_stream(stream), nn_lut, q, k, v, o, mask, dtype, block_size, p, scale);
+}
