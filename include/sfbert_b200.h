@@ -144,6 +144,12 @@ int sfb_fused_attention(sfb_stream_t stream, const void *nn_lut, const void *q, 
                         uint32_t lut_heads, uint32_t lut_dim, uint32_t mask_heads,
                         float scale, uint32_t max_lut);
 
+/* Synchronises with the device and reads the library's status word into *status (HOST pointer):
+ * 0 while no kernel has given up on a bounded wait, otherwise (code << 24 | CTA index) of the
+ * first one that did.  No counterpart in the reference, whose fused kernels spin without a bound
+ * (fusion_blocksparse.h:246-289). */
+int sfb_device_status(uint32_t *status);
+
 /* ---- epilogue -------------------------------------------------------------------------- */
 
 /* out = LayerNorm(resid + (x + bias)) * gain + beta over rows of `hidden` elements; also writes

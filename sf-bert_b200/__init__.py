@@ -21,7 +21,7 @@ NT_OP, NN_OP, TN_OP = 0, 1, 2
 SYMBOLS = [
     "sfb_last_error", "sfb_version", "sfb_layout_generate", "sfb_lut_count", "sfb_lut_build", "sfb_mask_pack",
     "sfb_magicu64", "sfb_bst_sgemm_nt", "sfb_masked_softmax", "sfb_bst_sgemm_xn", "sfb_fused_sddmm_softmax",
-    "sfb_fused_attention", "sfb_bias_residual_layernorm",
+    "sfb_fused_attention", "sfb_bias_residual_layernorm", "sfb_device_status",
 ]
 
 if not os.path.exists(LIB_PATH):
@@ -42,8 +42,18 @@ lib.sfb_bst_sgemm_nt.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] *
 lib.sfb_masked_softmax.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 9 + [_f32]
 lib.sfb_bst_sgemm_xn.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 13
 lib.sfb_fused_sddmm_softmax.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 10 + [_f32]
-lib.sfb_fused_attention.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32] + [_u32] * 8 + [_f32, _u32]
+lib.sfb_fused_attention.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32] + [_u32] * 9 + [_f32, _u32]
 lib.sfb_bias_residual_layernorm.argtypes = [_vp] * 10 + [_u32, _u32, _i32]
+
+
+lib.sfb_device_status.argtypes = [C.POINTER(_u32)]
+
+
+def device_status():
+    """0 unless a kernel gave up on one of its bounded waits (synchronises with the device)."""
+    v = _u32(0)
+    _check(lib.sfb_device_status(C.byref(v)))
+    return v.value
 
 
 class SfbError(RuntimeError):

@@ -22,4 +22,10 @@ int simt_fused_sddmm_softmax(cudaStream_t s, const void *nn_lut, const void *a, 
 int simt_fused_attention(cudaStream_t s, const void *nn_lut, const void *q, const void *k, const void *v, void *o,
                          const void *mask, int dtype, uint32_t bs, const AttnDims &p, float scale);
 
+// tcgen05 kernels (attn_tc.cu)
+bool tc_fused_attention_supported(int dtype, uint32_t bs, const AttnDims &p, float scale, uint32_t max_lut);
+int tc_fused_attention(cudaStream_t s, const void *nn_lut, const void *q, const void *k, const void *v, void *o,
+                       const void *mask, int dtype, const AttnDims &p, float scale);
+int tc_status(uint32_t *out);
+
 }  // namespace sfb

@@ -99,5 +99,16 @@ extern "C" int sfb_fused_attention(sfb_stream_t stream, const void *nn_lut, cons
     if (ctx_blks == 0) { clear_error(); return 0; }
     AttnDims p = {batch_dim, head_dim, state_dim, ctx_blks, ctx_blks, blocks, lut_heads > 1 ? lut_dim + ctx_blks : 0,
                   mask_heads > 1 ? blocks * block_size : 0};
+    // 16-bit operands with 64x64 blocks and 64-wide heads run on the tensor cores
+    if (tc_fused_attention_supported(dtype, block_size, p, scale, max_lut))
+        return tc_fused_attention(as_stream(stream), nn_lut, q, k, v, o, mask, dtype, p, scale);
     return simt_fused_attention(as_stream(stream), nn_lut, q, k, v, o, mask, dtype, block_size, p, scale);
+}
+
+extern "C" int sfb_device_status(uint32_t *status)
+{
+    SFB_REQUIRE(status, "sfb_device_status: NULL pointer");
+    if (tc_status(status)) return 1;
+    clear_error();
+    return 0;
 }

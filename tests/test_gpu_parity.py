@@ -46,8 +46,8 @@ def _make(sfb, oracle, kind, kw, dev, heads, nb, bs):
 @pytest.mark.parametrize("kind,kw,dev", LAYOUTS)
 @pytest.mark.parametrize("heads,nb", [(1, 16), (4, 16), (1, 64), (2, 256)])
 def test_layout_and_lut_bit_exact(sfb, oracle, kind, kw, dev, heads, nb):
-    if kind == "fixed" and heads > 4:
-        pytest.skip("fixed pattern defined for heads <= stride")
+    if kind == "bigbird" and heads > 1:
+        pytest.skip("per-head random blocks give the heads different counts, which the LUT format cannot hold")
     lay, ref_layout, luts = _make(sfb, oracle, kind, kw, dev, heads, nb, 32)
     assert np.array_equal(lay.layout.cpu().numpy(), ref_layout)
     assert lay.blocks == luts["blocks"] and lay.nn_max == luts["nn_max"]
