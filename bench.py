@@ -1,0 +1,311 @@
+#!/usr/bin/env python
+"""Benchmark of the block-sparse attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config NAME]
+
+Workload (default `stride_bertbase`): stride-pattern block-sparse attention at the BERT-base shape,
+fp16 storage with fp32 accumulation, B=8 H=12 L=4096 d=64, 64x64 blocks, layout = band of 4 blocks
+plus every 8th block column (730 kept blocks per head).  A step is one fused attention launch
+(SDDMM + softmax + SpMM in one kernel) over the whole batch.  The metric is TFLOP/s counted on the
+kept blocks only: 4 * 64 * 64 * d * blocks * B * H flops per step.
+
+One JSON line is printed by rank 0.  `value` is measured with the operands resident in HBM;
+`e2e` goes through the same C-ABI call with the operands in pinned host memory, so the
+host->device and device->host copies are inside its timed region.  `--impl reference` times the
+reference's own CPU operators (matmul.h / ewops.h, compiled into oracle/_ref) on a bounded sample.
+With N > 1 every rank runs the workload on its own batch (batch x head sharding, no collective on
+the data path); the NCCL all-gather of the outputs is timed separately as `gather_ms`.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    # name: dtype, B, H, L, d, bs, layout kind + parameters
+    "stride_bertbase": dict(dtype="f16", B=8, H=12, L=4096, d=64, bs=64, layout=("LAYOUT_STRIDE", dict(p0=4, p1=8)),
+                            oracle=("stride", dict(band=4, every=8))),
+    "bigbird": dict(dtype="bf16", B=16, H=12, L=4096, d=64, bs=64,
+                    layout=("LAYOUT_BIGBIRD", dict(p0=1, p1=1, p2=1, p3=3, seed=1236)),
+                    oracle=("bigbird", dict(window=1, g_first=1, g_last=1, nrand=3, seed=1236))),
+    "local_bertlarge": dict(dtype="bf16", B=4, H=16, L=16384, d=64, bs=64, layout=("LAYOUT_LOCAL", dict(p0=8, p1=8)),
+                            oracle=("local", dict(left=8, right=8))),
+    "full_bertlarge": dict(dtype="bf16", B=32, H=16, L=1024, d=64, bs=64, layout=("LAYOUT_FULL", dict()),
+                           oracle=("full", dict())),
+    "fixed_fp32": dict(dtype="f32", B=1, H=4, L=512, d=64, bs=32, layout=("LAYOUT_FIXED", dict(p0=4)),
+                       oracle=("fixed", dict(stride=4)), lut_heads=4),
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(tensor=p["bf16_tflops"], tensor_sustained=p["bf16_tflops_sustained"], hbm=p["hbm_gbs"], source="measured")
+    return dict(tensor=1590.0, tensor_sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.12)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1])); power.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
+        # the busy samples are the ones that matter: take the median of the upper half by power
+        order = sorted(range(len(sm)), key=lambda i: power[i])
+        busy = [sm[i] for i in order[len(order) // 2:]]
+        return dict(sm_mhz=statistics.median(busy), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm),
+                    power_w_max=max(power))
+
+
+def attention_flops(cfg, blocks):
+    return 4.0 * cfg["bs"] * cfg["bs"] * cfg["d"] * blocks * cfg["B"] * cfg["H"]
+
+
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as ge
+    sfb = ge.load_package()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    cfg = CONFIGS[args.config]
+    tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[cfg["dtype"]]
+    B, H, L, d, bs = cfg["B"], cfg["H"], cfg["L"], cfg["d"], cfg["bs"]
+    nb = L // bs
+    lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), nb, bs, **cfg["layout"][1])
+    scale = 1.0 / d ** 0.5
+
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    q, k, v = (torch.randn(B, L, H, d, device="cuda", dtype=torch.float32, generator=gen).to(tdt) for _ in range(3))
+    o = torch.empty_like(q)
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    ho = torch.empty_like(hq).pin_memory()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")   # larger than the 126 MB L2
+
+    def step():
+        sfb.fused_attention(q, k, v, lay, scale, out=o)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        flush.fill_(1)
+        step()
+    sync_all()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    # resident-operand timing: one event pair per step, L2 flushed in between (flush not timed)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    sync_all()
+    for a, b_ in ev:
+        flush.fill_(1)
+        a.record()
+        step()
+        b_.record()
+    sync_all()
+    ms_steps = [a.elapsed_time(b_) for a, b_ in ev]
+    ms_total = sum(ms_steps)
+
+    # end to end through the same call: pinned host operands in, output back to the host
+    def e2e_step():
+        q.copy_(hq, non_blocking=True)
+        k.copy_(hk, non_blocking=True)
+        v.copy_(hv, non_blocking=True)
+        step()
+        ho.copy_(o, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    sync_all()
+    e2e_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+
+    gather_ms = None
+    if world > 1:
+        outs = torch.empty((world,) + tuple(o.shape), dtype=o.dtype, device="cuda")
+        for _ in range(3):
+            dist.all_gather_into_tensor(outs, o)
+        sync_all()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(5):
+            dist.all_gather_into_tensor(outs, o)
+        g1.record()
+        sync_all()
+        gather_ms = g0.elapsed_time(g1) / 5
+
+    status = sfb.device_status()
+    t = torch.tensor([ms_total, e2e_ms, gather_ms or 0.0], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms, gather_max = (float(x) for x in t.cpu())
+
+    if rank == 0:
+        pk = peaks()
+        flops = attention_flops(cfg, lay.blocks)
+        ms_per_step = ms_total / args.steps
+        value = world * flops / (ms_per_step * 1e-3) / 1e12
+        per_gpu = flops / (ms_per_step * 1e-3) / 1e12
+        esz = q.element_size()
+        line = {
+            "metric": "block-sparse attention TFLOP/s on nonzero blocks",
+            "value": round(value, 3), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": cfg["dtype"], "data": "synthetic",
+            "config": {"workload": args.config, "B_per_gpu": B, "H": H, "L": L, "d": d, "block": bs,
+                       "layout": cfg["layout"][0], "nnz_blocks_per_head": lay.blocks, "max_row": lay.nn_max,
+                       "sharding": "batch x head, no collective on the data path", "l2": "flushed between timed steps"},
+            "roofline": {"bound": "tensor", "achieved": round(per_gpu, 3), "peak": pk["tensor"], "unit": "TFLOP/s",
+                         "frac": round(per_gpu / pk["tensor"], 4), "traffic": None, "peak_source": pk["source"] + " burst bf16",
+                         "frac_of_sustained": round(per_gpu / pk["tensor_sustained"], 4),
+                         "min_hbm_bytes": 4 * B * L * H * d * esz,
+                         "kernel": "fused_attention_tc_kernel" if cfg["dtype"] != "f32" else "fused_attention_kernel"},
+            "e2e": {"value": round(world * flops / (e2e_ms / args.steps * 1e-3) / 1e12, 3), "unit": "TFLOP/s",
+                    "ms_per_step": round(e2e_ms / args.steps, 4),
+                    "h2d_bytes_per_step": 3 * B * L * H * d * esz, "d2h_bytes_per_step": B * L * H * d * esz},
+            "gpu_launches": args.steps * 2,   # resident loop + end-to-end loop, one fused kernel per step
+            "clocks": clocks, "device_status": status,
+        }
+        if gather_ms is not None:
+            line["gather_ms"] = round(gather_max, 4)
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_reference_sample(cfg, budget_s=20.0, steps=1)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------------
+def cpu_reference_sample(cfg, budget_s, steps):
+    """Times the reference's CPU attention operators (multiheadmatmulNT -> softmax -> multiheadmatmulNN,
+    transformer_inference_part.cpp:219-224) on B' = host threads batches x 1 head, at the longest
+    sequence length whose estimated time fits the budget.  The reference parallelises over the batch only."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as O
+    R = O.ref()
+    kind = "reference"
+    threads = R.ref_num_threads() if R is not None else O.lib().orc_num_threads()
+    if R is None:
+        kind = "port"
+    d, bs = cfg["d"], cfg["bs"]
+    Bs = max(1, min(threads, 16))
+
+    def one(Ls, reps):
+        nb = Ls // bs
+        luts = O.lut_build(O.layout(cfg["oracle"][0], 1, nb, **cfg["oracle"][1]))
+        q, k, v = (O.fill_normal((Bs, Ls, 1, d), 50 + i) for i in range(3))
+        times = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            if R is not None:
+                O.ref_dense_causal_attention(q, k, v, np.float32(1.0 / d ** 0.5))
+            else:
+                O.attention(q, k, v, luts, bs, np.float32(1.0 / d ** 0.5), want=("o",))
+            times.append(time.perf_counter() - t0)
+        flops = 4.0 * bs * bs * d * luts["blocks"] * Bs
+        return times, flops, luts["blocks"]
+
+    cal, _, _ = one(512, 1)
+    Ls = 512
+    for cand in (cfg["L"], cfg["L"] // 2, cfg["L"] // 4, cfg["L"] // 8):
+        if cand >= 512 and cal[0] * (cand / 512.0) ** 2 <= budget_s / max(steps, 1):
+            Ls = cand
+            break
+    times, flops, blocks = one(Ls, steps)
+    best = sum(times) / len(times)
+    return {"value": flops / best / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": kind,
+            "sample": "%d batches x 1 head, L=%d of %d, d=%d: reference multiheadmatmulNT + softmax + multiheadmatmulNN "
+                      "(dense causal, OpenMP over the batch), flops counted on the %d kept blocks of the %s layout at that "
+                      "length; %.2f s per pass" % (Bs, Ls, cfg["L"], d, blocks, cfg["oracle"][0], best),
+            "seconds_per_pass": best, "L_sample": Ls}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = CONFIGS[args.config]
+    n = max(args.steps + args.warmup, 1)
+    res = cpu_reference_sample(cfg, budget_s=150.0, steps=n)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    line = {
+        "impl": "reference", "metric": "block-sparse attention TFLOP/s on nonzero blocks", "value": res["value"],
+        "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": res["seconds_per_pass"] * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.config, "L": cfg["L"], "d": cfg["d"], "block": cfg["bs"], "layout": cfg["layout"][0]},
+        "cpu_baseline": {"value": res["value"], "unit": "TFLOP/s", "cores": res["cores"], "kind": res["kind"], "sample": res["sample"]},
+        "e2e": {"value": res["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="stride_bertbase", choices=sorted(CONFIGS))
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

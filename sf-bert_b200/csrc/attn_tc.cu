@@ -33,7 +33,7 @@ struct UnionEntry {
 };
 
 struct SharedState {
-    uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[2], s_empty[2], p_full[2], p_empty[2], pv_done, drained;
+    uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[2], s_empty[2], p_full[2], p_empty[2], pv_done, o_final, drained;
     uint32_t tmem_base, n_union, abort_flag, pad;
     UnionEntry entries[kMaxUnion];
     uint8_t found[kMaxUnion];
@@ -217,6 +217,7 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             mbar_init(&st->p_empty[s], 1);
         }
         mbar_init(&st->pv_done, 1);
+        mbar_init(&st->o_final, 1);
         mbar_init(&st->drained, 1);
         st->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -333,6 +334,9 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                 umma_commit(&st->kv_empty[s]);
                 umma_commit(&st->p_empty[t & 1]);
                 umma_commit(&st->pv_done);
+                // the epilogue cannot use pv_done: it may run two completions ahead of it, which a
+                // parity wait cannot tell apart
+                if (t + 1 == T) umma_commit(&st->o_final);
             }
         }
     } else {
@@ -422,7 +426,7 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
         // ---- epilogue: O / l -> global ----
         uint32_t orow[64];
         if (T > 0 && alive) {
-            alive = mbar_wait_warp(&st->pv_done, (T - 1) & 1, abort_flag, 10);
+            alive = mbar_wait_warp(&st->o_final, 0, abort_flag, 10);
             if (alive) {
                 tcgen05_fence_after();
                 TMEM_LD_32((orow), tmem_o + lane_field);

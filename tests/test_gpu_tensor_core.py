@@ -1,0 +1,137 @@
+"""Parity of the tcgen05 fused attention kernel (16-bit operands, 64x64 blocks, 64-wide heads),
+called through the C ABI, against the CPU oracle -- small cases element by element, the five
+benchmark configurations at full size through slices and size-independent properties."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+TD = {"bf16": torch.bfloat16, "f16": torch.float16}
+REL = 2e-2   # 16-bit operands, fp32 accumulation
+
+
+def _rand(oracle, shape, seed, dtype):
+    return torch.from_numpy(oracle.fill_normal(shape, seed)).cuda().to(TD[dtype])
+
+
+def _check_slice(sfb, oracle, lay, luts, q, k, v, o, b, h, scale, mask_np=None):
+    """Oracle on one (batch, head) slice of the full-size problem."""
+    sl = lambda t: t[b:b + 1, :, h:h + 1].float().cpu().numpy()
+    one = dict(luts)
+    if luts["nt"].shape[0] > 1:
+        one = dict(nt=luts["nt"][h:h + 1], nn=luts["nn"][h:h + 1], blocks=luts["blocks"])
+        if mask_np is not None:
+            mask_np = mask_np[h:h + 1]
+    ref = oracle.attention(sl(q), sl(k), sl(v), one, 64, np.float32(scale), mask_np=mask_np, want=("o",))["o"]
+    got = o[b:b + 1, :, h:h + 1].float().cpu().numpy()
+    assert np.abs(got - ref).max() <= REL * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("nb,kind,kw,dev", [
+    (1, "full", dict(), ("LAYOUT_FULL", dict())),
+    (2, "full", dict(), ("LAYOUT_FULL", dict())),
+    (5, "full", dict(causal=1), ("LAYOUT_FULL", dict(causal=1))),       # odd number of block-rows
+    (9, "local", dict(left=1, right=2), ("LAYOUT_LOCAL", dict(p0=1, p1=2))),
+    (16, "bigbird", dict(window=1, g_first=1, g_last=1, nrand=3, seed=3),
+     ("LAYOUT_BIGBIRD", dict(p0=1, p1=1, p2=1, p3=3, seed=3))),
+    (64, "full", dict(), ("LAYOUT_FULL", dict())),                       # rows of 64 blocks
+])
+def test_small_cases_elementwise(sfb, oracle, dtype, nb, kind, kw, dev):
+    B, H, L, d = 2, 2, nb * 64, 64
+    lay = sfb.BlockLayout.generate(getattr(sfb, dev[0]), 1, nb, 64, **dev[1])
+    luts = oracle.lut_build(oracle.layout(kind, 1, nb, **kw))
+    q, k, v = (_rand(oracle, (B, L, H, d), 600 + i, dtype) for i in range(3))
+    o = sfb.fused_attention(q, k, v, lay, 0.125)
+    assert sfb.device_status() == 0
+    ref = oracle.attention(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(), luts, 64,
+                           np.float32(0.125), want=("o",))["o"]
+    assert np.abs(o.float().cpu().numpy() - ref).max() <= REL * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("pred,ctx", [("MASK_CAUSAL_DIAG", 0), ("MASK_LOCAL", 100)])
+def test_element_masks_on_tensor_cores(sfb, oracle, pred, ctx):
+    B, H, nb, d = 1, 3, 7, 64
+    lay = sfb.BlockLayout.generate(sfb.LAYOUT_FULL, 1, nb, 64, causal=1).pack_mask(getattr(sfb, pred), ctx)
+    luts = oracle.lut_build(oracle.layout("full", 1, nb, causal=1))
+    m_np, _ = oracle.mask_pack(luts["nt"], 64, getattr(oracle, pred), ctx)
+    q, k, v = (_rand(oracle, (B, nb * 64, H, d), 700 + i, "bf16") for i in range(3))
+    o = sfb.fused_attention(q, k, v, lay, 0.125, use_mask=True)
+    assert sfb.device_status() == 0
+    ref = oracle.attention(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(), luts, 64,
+                           np.float32(0.125), mask_np=m_np, want=("o",))["o"]
+    assert np.abs(o.float().cpu().numpy() - ref).max() <= REL * np.abs(ref).max()
+
+
+def test_per_head_luts_and_empty_rows(sfb, oracle):
+    H, nb, d = 3, 6, 64
+    layout = np.zeros((H, nb, nb), np.uint8)
+    rng = np.random.RandomState(0)
+    for h in range(H):
+        # 9 blocks per head, rows 1 and 4 left empty
+        cells = [(i, j) for i in (0, 2, 3, 5) for j in range(nb)]
+        for idx in rng.choice(len(cells), 9, replace=False):
+            layout[h][cells[idx]] = 1
+    lay = sfb.BlockLayout(torch.from_numpy(layout).cuda(), 64)
+    luts = oracle.lut_build(layout)
+    q, k, v = (_rand(oracle, (2, nb * 64, H, d), 800 + i, "bf16") for i in range(3))
+    o = torch.full_like(q, 3.0)
+    sfb.fused_attention(q, k, v, lay, 0.125, out=o)
+    assert sfb.device_status() == 0
+    ref = oracle.attention(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(), luts, 64,
+                           np.float32(0.125), want=("o",))["o"]
+    assert np.abs(o.float().cpu().numpy() - ref).max() <= REL * np.abs(ref).max()
+    assert float(o[:, 64:128].abs().max()) == 0.0 and float(o[:, 256:320].abs().max()) == 0.0
+
+
+def test_all_ones_known_answer_16bit(sfb):
+    lay = sfb.BlockLayout.generate(sfb.LAYOUT_STRIDE, 1, 16, 64, p0=4, p1=8)
+    ones = torch.ones(1, 1024, 2, 64, device="cuda", dtype=torch.float16)
+    o = sfb.fused_attention(ones, ones, ones, lay).float()
+    assert float((o - 1.0).abs().max()) < 2e-3
+
+
+FULL = [
+    # name, dtype, B, H, L, layout
+    ("stride_bertbase", "f16", 8, 12, 4096, ("stride", dict(band=4, every=8)), ("LAYOUT_STRIDE", dict(p0=4, p1=8))),
+    ("bigbird", "bf16", 16, 12, 4096, ("bigbird", dict(window=1, g_first=1, g_last=1, nrand=3, seed=1236)),
+     ("LAYOUT_BIGBIRD", dict(p0=1, p1=1, p2=1, p3=3, seed=1236))),
+    ("local_bertlarge", "bf16", 4, 16, 16384, ("local", dict(left=8, right=8)), ("LAYOUT_LOCAL", dict(p0=8, p1=8))),
+    ("full_bertlarge", "bf16", 32, 16, 1024, ("full", dict()), ("LAYOUT_FULL", dict())),
+]
+
+
+@pytest.mark.parametrize("name,dtype,B,H,L,orc,dev", FULL, ids=[c[0] for c in FULL])
+def test_benchmark_configs_full_size(sfb, oracle, name, dtype, B, H, L, orc, dev):
+    """Full-size runs of benchmark configurations 2-5: oracle parity on (batch, head) slices, and
+    properties that do not need the oracle at full size -- rows of P sum to 1 (V = 1 gives O = 1),
+    linearity in V, and agreement of the fused kernel with the unfused three-kernel pipeline."""
+    nb, d = L // 64, 64
+    lay = sfb.BlockLayout.generate(getattr(sfb, dev[0]), 1, nb, 64, **dev[1])
+    luts = oracle.lut_build(oracle.layout(orc[0], 1, nb, **orc[1]))
+    assert np.array_equal(lay.nn_lut.cpu().numpy().astype(np.uint32), luts["nn"])
+    gen = torch.Generator(device="cuda").manual_seed(99)
+    q, k, v = (torch.randn(B, L, H, d, device="cuda", generator=gen).to(TD[dtype]) for _ in range(3))
+    scale = 0.125
+    o = sfb.fused_attention(q, k, v, lay, scale)
+    assert sfb.device_status() == 0
+    assert bool(torch.isfinite(o.float()).all())
+    for (b, h) in [(0, 0), (B - 1, H - 1), (B // 2, 5)]:
+        _check_slice(sfb, oracle, lay, luts, q, k, v, o, b, h, scale)
+    # softmax rows sum to 1
+    ones = torch.ones_like(v)
+    o1 = sfb.fused_attention(q, k, ones, lay, scale).float()
+    assert float((o1 - 1.0).abs().max()) < 1e-3 + 2 ** -8
+    # linearity in V
+    v2 = torch.randn(B, L, H, d, device="cuda", generator=gen).to(TD[dtype])
+    o2 = sfb.fused_attention(q, k, v2, lay, scale).float()
+    o12 = sfb.fused_attention(q, k, (v.float() + v2.float()).to(TD[dtype]), lay, scale).float()
+    assert float((o12 - (o.float() + o2)).abs().max()) <= 3 * REL * float(o12.abs().max())
+    del o1, o2, o12, v2, ones
+    # fused against unfused on one batch element (S and P make the round trip through HBM there)
+    qb, kb, vb = q[:1].contiguous(), k[:1].contiguous(), v[:1].contiguous()
+    s = sfb.bst_sgemm_nt(qb, kb, lay, torch.bfloat16)
+    p = sfb.masked_softmax(s, lay, scale, torch.bfloat16)
+    ou = sfb.bst_sgemm_xn(p, vb, lay).float()
+    assert float((ou - o[:1].float()).abs().max()) <= 2 * REL * float(ou.abs().max())
