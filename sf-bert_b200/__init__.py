@@ -10,7 +10,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libsfbert_b200.so")
+# SFBERT_B200_LIB selects another build of the same library (e.g. an instrumented one)
+LIB_PATH = os.environ.get("SFBERT_B200_LIB") or os.path.join(_HERE, "libsfbert_b200.so")
 
 F32, BF16, F16 = 0, 1, 2
 LAYOUT_FULL, LAYOUT_FIXED, LAYOUT_STRIDE, LAYOUT_SAWTOOTH, LAYOUT_LOCAL, LAYOUT_BIGBIRD = range(6)

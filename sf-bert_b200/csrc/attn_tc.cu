@@ -6,10 +6,13 @@
 // other CTAs.  Per key block:
 //     S  = Q . K^T            tcgen05.mma  (A, B from shared memory, accumulator in TMEM)
 //     P  = exp2(S*c - m)      128 threads, one query row each, straight out of TMEM
-//     O += P . V              tcgen05.mma  (P staged in shared memory, V as an MN-major operand)
-// Warp roles: warp 0 issues the TMA loads, warp 1 issues the MMAs, warps 2-5 do the softmax and the
-// epilogue.  Every wait on an mbarrier is bounded; on a timeout the CTA records a status word and
-// leaves through the common teardown (TMEM freed, loads in flight drained).
+//     O += P . V              tcgen05.mma  (P as the A operand straight from TMEM, where it overwrites S;
+//                                          V from shared memory as an MN-major operand)
+// Warp roles: warp 0 issues the TMA loads, warp 1 issues the MMAs, warps 2-5 and 6-9 are two softmax
+// groups that take the key blocks alternately.  Each group keeps its own running max / sum and its own
+// O accumulator in TMEM (an online softmax over its half of the key blocks); the two halves are merged
+// once, in the epilogue.  Every wait on an mbarrier is bounded; on a timeout the CTA records a status
+// word and leaves through the common teardown (TMEM freed, loads in flight drained).
 #include "attn.cuh"
 #include <cuda.h>
 
@@ -17,12 +20,11 @@ namespace sfb {
 
 namespace tc {
 
-constexpr int kStages = 3;                      // K/V ring depth
+constexpr int kStages = 4;                      // K/V ring depth
 constexpr int kMaxUnion = 512;                  // key blocks a row pair may touch
 constexpr uint32_t kTileBytes = 64 * 64 * 2;    // one 64x64 16-bit tile
 constexpr uint32_t kQBytes = 128 * 64 * 2;
-constexpr uint32_t kPBytes = 128 * 64 * 2;
-constexpr uint32_t kTmemCols = 256;             // S0 | S1 | O | (unused)
+constexpr uint32_t kTmemCols = 256;             // S0 | S1 | O0 | O1, 64 columns each; P(16-bit) reuses S's first 32
 constexpr uint32_t kWaitLimit = 1u << 24;
 constexpr float kRescaleThreshold = 8.0f;       // log2 units: P stays below 2^8
 
@@ -33,13 +35,15 @@ struct UnionEntry {
 };
 
 struct SharedState {
-    uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[2], s_empty[2], p_full[2], p_empty[2], pv_done, o_final, drained;
+    uint64_t q_full, kv_full[kStages], kv_empty[kStages];
+    uint64_t s_full[2], p_full[2], pv_done[2], o_final, drained;
     uint32_t tmem_base, n_union, abort_flag, pad;
+    float2 ml[2][128];             // (running max, running sum) of each group's rows, for the merge
     UnionEntry entries[kMaxUnion];
     uint8_t found[kMaxUnion];
 };
 
-constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + kQBytes + kStages * 2 * kTileBytes + 2 * kPBytes + sizeof(SharedState);
+constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + kQBytes + kStages * 2 * kTileBytes + sizeof(SharedState);
 
 struct Params {
     const uint2 *nn_lut;
@@ -50,7 +54,17 @@ struct Params {
     int is_bf16;
 };
 
-__device__ uint32_t g_status = 0;  // 0 = ok; otherwise (code << 24 | detail) of the first CTA that gave up
+__device__ uint32_t g_status = 0;
+
+#ifdef SFB_TC_TIMING
+// per-phase cycle counts of one softmax lane and the MMA lane of one CTA (profiling builds only)
+__device__ unsigned long long g_timing[32];
+#define TIC(var) const long long var = clock64()
+#define TOC(slot, var) do { if (timing_on) atomicAdd(&g_timing[slot], (unsigned long long)(clock64() - var)); } while (0)
+#else
+#define TIC(var)
+#define TOC(slot, var)
+#endif  // 0 = ok; otherwise (code << 24 | detail) of the first CTA that gave up
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -120,6 +134,16 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// same, with the A operand read from TMEM (lane = row, one 32-bit column = two 16-bit elements along K)
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t *bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -186,8 +210,22 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int is_bf16)
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------
+#define TMEM_LD_16(r, addr)                                                                                          \
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];" \
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),   \
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]) \
+                 : "r"(addr)                                                                                         \
+                 : "memory")
+#define TMEM_ST_16(addr, r)                                                                                          \
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" \
+                 ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), \
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])      \
+                 : "memory")
+
+__device__ __forceinline__ void softmax_groups_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
 template <bool HAS_MASK>
-__global__ void __launch_bounds__(192, 2)
+__global__ void __launch_bounds__(320, 2)
 fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                           const __grid_constant__ CUtensorMap vmap, const Params p)
 {
@@ -195,8 +233,7 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *q_tile = smem;
     uint8_t *kv_tiles = q_tile + kQBytes;                      // stage s: K at s*2*kTileBytes, V right after
-    uint8_t *p_tiles = kv_tiles + kStages * 2 * kTileBytes;
-    SharedState *st = (SharedState *)(p_tiles + 2 * kPBytes);
+    SharedState *st = (SharedState *)(kv_tiles + kStages * 2 * kTileBytes);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t pair = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
@@ -209,14 +246,15 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     // ---- set-up: barriers, TMEM, the union of the two rows' key blocks ----
     if (threadIdx.x == 0) {
         mbar_init(&st->q_full, 1);
-        for (int s = 0; s < kStages; s++) { mbar_init(&st->kv_full[s], 1); mbar_init(&st->kv_empty[s], 1); }
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(&st->kv_full[s], 1);
+            mbar_init(&st->kv_empty[s], 1);
+        }
         for (int s = 0; s < 2; s++) {
             mbar_init(&st->s_full[s], 1);
-            mbar_init(&st->s_empty[s], 128);
             mbar_init(&st->p_full[s], 128);
-            mbar_init(&st->p_empty[s], 1);
+            mbar_init(&st->pv_done[s], 1);
         }
-        mbar_init(&st->pv_done, 1);
         mbar_init(&st->o_final, 1);
         mbar_init(&st->drained, 1);
         st->abort_flag = 0;
@@ -280,29 +318,33 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     __syncthreads();
     tcgen05_fence_after();
 
+#ifdef SFB_TC_TIMING
+    const bool timing_on = blockIdx.x == 7 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 1 || warp == 2);
+#endif
     const uint32_t T = st->n_union;
     const uint32_t tmem = st->tmem_base;
     const uint32_t tmem_s[2] = {tmem, tmem + 64};
-    const uint32_t tmem_o = tmem + 128;
+    const uint32_t tmem_o[2] = {tmem + 128, tmem + 192};
     const uint32_t fmt = p.is_bf16 ? 1u : 0u;
     const int32_t xq = (int32_t)(h * 64);
 
     if (warp == 0) {
-        // ===== TMA producer =====
+        // ===== TMA producer: a stage (K and V of one key block) is released when its P.V has completed =====
         if (lane == 0 && T > 0) {
             mbar_expect_tx(&st->q_full, kQBytes);
             tma_load_2d(smem_u32(q_tile), &qmap, &st->q_full, xq, (int32_t)(b * L + pair * 128));
             for (uint32_t t = 0; t < T; t++) {
                 const uint32_t s = t % kStages;
-                if (t >= kStages && !mbar_wait(&st->kv_empty[s], ((t / kStages) - 1) & 1, abort_flag, 1)) break;
                 const int32_t y = (int32_t)(b * L + st->entries[t].col * 64);
+                if (t >= kStages && !mbar_wait(&st->kv_empty[s], ((t / kStages) - 1) & 1, abort_flag, 1)) break;
                 mbar_expect_tx(&st->kv_full[s], 2 * kTileBytes);
                 tma_load_2d(smem_u32(kv_tiles + s * 2 * kTileBytes), &kmap, &st->kv_full[s], xq, y);
                 tma_load_2d(smem_u32(kv_tiles + s * 2 * kTileBytes + kTileBytes), &vmap, &st->kv_full[s], xq, y);
             }
         }
     } else if (warp == 1) {
-        // ===== MMA issuer =====
+        // ===== MMA issuer: S(0) S(1) | O(0) S(2) | O(1) S(3) | ...  S(t+2) overwrites P(t) in TMEM, which is safe
+        // because the tensor core runs this thread's MMAs in order =====
         if (lane == 0 && T > 0) {
             const uint32_t idesc_qk = instr_desc(fmt, 128, 64, 0);
             const uint32_t idesc_pv = instr_desc(fmt, 128, 64, 1);
@@ -310,8 +352,9 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             bool alive = mbar_wait(&st->q_full, 0, abort_flag, 2);
             auto issue_qk = [&](uint32_t t) -> bool {
                 const uint32_t s = t % kStages;
+                TIC(c0);
                 if (!mbar_wait(&st->kv_full[s], (t / kStages) & 1, abort_flag, 3)) return false;
-                if (t >= 2 && !mbar_wait(&st->s_empty[t & 1], ((t >> 1) - 1) & 1, abort_flag, 4)) return false;
+                TOC(10, c0);
                 tcgen05_fence_after();
                 const uint64_t k_desc = smem_desc_sw128(smem_u32(kv_tiles + s * 2 * kTileBytes));
 #pragma unroll
@@ -321,26 +364,27 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                 return true;
             };
             if (alive) alive = issue_qk(0);
+            if (alive && T > 1) alive = issue_qk(1);
             for (uint32_t t = 0; alive && t < T; t++) {
-                if (t + 1 < T && !issue_qk(t + 1)) { alive = false; break; }
-                if (!mbar_wait(&st->p_full[t & 1], (t >> 1) & 1, abort_flag, 5)) { alive = false; break; }
+                const uint32_t g = t & 1, s = t % kStages;
+                TIC(c2);
+                if (!mbar_wait(&st->p_full[g], (t >> 1) & 1, abort_flag, 5)) { alive = false; break; }
+                TOC(12, c2);
                 tcgen05_fence_after();
-                const uint32_t s = t % kStages;
-                const uint64_t p_desc = smem_desc_sw128(smem_u32(p_tiles + (t & 1) * kPBytes));
                 const uint64_t v_desc = smem_desc_sw128(smem_u32(kv_tiles + s * 2 * kTileBytes + kTileBytes));
 #pragma unroll
-                for (uint32_t kk = 0; kk < 4; kk++)   // 16 keys per MMA: +32 bytes in P's rows, +16 rows (2048 bytes) in V
-                    umma_f16(tmem_o, p_desc + 2 * kk, v_desc + 128 * kk, idesc_pv, (t | kk) ? 1u : 0u);
+                for (uint32_t kk = 0; kk < 4; kk++)   // 16 keys per MMA: 8 TMEM columns of P, 16 rows (2048 bytes) of V
+                    umma_f16_ts(tmem_o[g], tmem_s[g] + 8 * kk, v_desc + 128 * kk, idesc_pv, (t >= 2 || kk) ? 1u : 0u);
                 umma_commit(&st->kv_empty[s]);
-                umma_commit(&st->p_empty[t & 1]);
-                umma_commit(&st->pv_done);
-                // the epilogue cannot use pv_done: it may run two completions ahead of it, which a
-                // parity wait cannot tell apart
+                umma_commit(&st->pv_done[g]);
+                // the epilogue needs "everything done", which the per-group parity barriers cannot express
                 if (t + 1 == T) umma_commit(&st->o_final);
+                if (t + 2 < T && !issue_qk(t + 2)) { alive = false; break; }
             }
         }
     } else {
-        // ===== softmax + epilogue: one query row per thread =====
+        // ===== softmax groups + epilogue: one query row per thread, group g takes key blocks g, g+2, ... =====
+        const uint32_t g = (warp - 2) >> 2;
         const uint32_t quarter = warp & 3;                 // TMEM lanes this warp may touch
         const uint32_t r = quarter * 32 + lane;            // row inside the 128-query tile
         const uint32_t half = r >> 6;                      // which of the two block-rows
@@ -350,15 +394,20 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
         float m_used = -INFINITY, l = 0.f;
         bool alive = true;
 
-        for (uint32_t t = 0; t < T; t++) {
-            if (!mbar_wait_warp(&st->s_full[t & 1], (t >> 1) & 1, abort_flag, 6)) { alive = false; break; }
+        TIC(c_loop);
+        for (uint32_t t = g; t < T; t += 2) {
+            const uint32_t u = t >> 1;
+            TIC(c0);
+            if (!mbar_wait_warp(&st->s_full[g], u & 1, abort_flag, 6)) { alive = false; break; }
+            TOC(0, c0);
+            TIC(c1);
             tcgen05_fence_after();
             uint32_t sr[64];
-            TMEM_LD_32((sr), tmem_s[t & 1] + lane_field);
-            TMEM_LD_32((sr + 32), tmem_s[t & 1] + lane_field + 32);
+            TMEM_LD_32((sr), tmem_s[g] + lane_field);
+            TMEM_LD_32((sr + 32), tmem_s[g] + lane_field + 32);
             tmem_wait_ld();
-            tcgen05_fence_before();
-            mbar_arrive(&st->s_empty[t & 1]);
+            TOC(1, c1);
+            TIC(c2);
 
             const UnionEntry ent = st->entries[t];
             const bool mine = (ent.flags >> half) & 1;
@@ -370,8 +419,12 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                     for (int c = 0; c < 64; c++)
                         if (!((w >> c) & 1)) sr[c] = 0xff800000u;
                 }
+                float m8[8];
 #pragma unroll
-                for (int c = 0; c < 64; c++) mx = fmaxf(mx, __uint_as_float(sr[c]));
+                for (int c = 0; c < 8; c++) m8[c] = __uint_as_float(sr[c]);
+#pragma unroll
+                for (int c = 8; c < 64; c++) m8[c & 7] = fmaxf(m8[c & 7], __uint_as_float(sr[c]));
+                mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
                 mx *= sl;
             }
             // move the reference max only when the row max outgrew it by 2^8: rescaling O stays rare
@@ -383,24 +436,27 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                 l *= alpha;
                 m_used = mx;
             }
-            if (t > 0 && __any_sync(0xffffffffu, fix_o)) {
-                // O must be complete (P.V of the previous key block) before it is rescaled
-                if (!mbar_wait_warp(&st->pv_done, (t - 1) & 1, abort_flag, 7)) { alive = false; break; }
+            if (u > 0 && __any_sync(0xffffffffu, fix_o)) {
+                // this group's O must be complete (its previous key block) before it is rescaled
+                if (!mbar_wait_warp(&st->pv_done[g], (u - 1) & 1, abort_flag, 7)) { alive = false; break; }
                 tcgen05_fence_after();
-                uint32_t orow[64];
-                TMEM_LD_32((orow), tmem_o + lane_field);
-                TMEM_LD_32((orow + 32), tmem_o + lane_field + 32);
-                tmem_wait_ld();
                 const float a = fix_o ? alpha : 1.f;
 #pragma unroll
-                for (int c = 0; c < 64; c++) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * a);
-                TMEM_ST_32(tmem_o + lane_field, (orow));
-                TMEM_ST_32(tmem_o + lane_field + 32, (orow + 32));
+                for (int c0 = 0; c0 < 64; c0 += 16) {
+                    uint32_t oc[16];
+                    TMEM_LD_16((oc), tmem_o[g] + lane_field + c0);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 16; c++) oc[c] = __float_as_uint(__uint_as_float(oc[c]) * a);
+                    TMEM_ST_16(tmem_o[g] + lane_field + c0, (oc));
+                }
                 tmem_wait_st();
             }
+            TOC(2, c2);
+            TIC(c3);
             const float neg_m = m_used > -INFINITY ? -m_used : 0.f;
             uint32_t pk[32];
-            float psum = 0.f;
+            float ps4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < 64; c += 2) {
                 float p0 = 0.f, p1 = 0.f;
@@ -408,45 +464,85 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                     p0 = ex2_approx(fmaf(__uint_as_float(sr[c]), sl, neg_m));
                     p1 = ex2_approx(fmaf(__uint_as_float(sr[c + 1]), sl, neg_m));
                 }
-                psum += p0 + p1;
+                ps4[(c >> 1) & 3] += p0 + p1;
                 pk[c >> 1] = pack2(p0, p1, p.is_bf16);
             }
-            l += psum;
-            if (t >= 2 && !mbar_wait_warp(&st->p_empty[t & 1], ((t >> 1) - 1) & 1, abort_flag, 8)) { alive = false; break; }
-            // row r of the K-major, 128-byte-swizzled P tile: 16-byte chunk c sits at chunk c ^ (r % 8)
-            uint8_t *prow = p_tiles + (t & 1) * kPBytes + r * 128;
-#pragma unroll
-            for (int c = 0; c < 8; c++)
-                *(uint4 *)(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-            fence_proxy_async();
+            l += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+            TOC(3, c3);
+            TIC(c5);
+            // P (16-bit pairs) takes the place of the first 32 columns of this row of S
+            TMEM_ST_32(tmem_s[g] + lane_field, (pk));
+            tmem_wait_st();
             tcgen05_fence_before();
-            mbar_arrive(&st->p_full[t & 1]);
+            mbar_arrive(&st->p_full[g]);
+            TOC(5, c5);
         }
+        TOC(6, c_loop);
+#ifdef SFB_TC_TIMING
+        if (timing_on) atomicAdd(&g_timing[7], (unsigned long long)((T + 1) / 2));
+#endif
 
-        // ---- epilogue: O / l -> global ----
-        uint32_t orow[64];
-        if (T > 0 && alive) {
-            alive = mbar_wait_warp(&st->o_final, 0, abort_flag, 10);
-            if (alive) {
-                tcgen05_fence_after();
-                TMEM_LD_32((orow), tmem_o + lane_field);
-                TMEM_LD_32((orow + 32), tmem_o + lane_field + 32);
-                tmem_wait_ld();
-            }
-        }
-        if (alive && row_valid) {
-            const float inv = (T > 0 && l > 0.f) ? 1.f / l : 0.f;
-            uint16_t *dst = (uint16_t *)p.O + ((size_t)b * L + (size_t)pair * 128 + r) * ((size_t)p.H * 64) + (size_t)h * 64;
+        // ---- epilogue: merge the two groups' partial softmaxes, O / l -> global ----
+        // Both named barriers below are reached by all 256 softmax threads whatever happened before.
+        st->ml[g][r] = make_float2(m_used, l);
+        if (T > 0 && alive) alive = mbar_wait_warp(&st->o_final, 0, abort_flag, 10);
+        tcgen05_fence_after();
+        softmax_groups_sync();
+        const float2 ml0 = st->ml[0][r], ml1 = st->ml[1][r];
+        const float M = fmaxf(ml0.x, ml1.x);
+        const float w0 = ml0.x > -INFINITY ? ex2_approx(ml0.x - M) : 0.f;
+        const float w1 = ml1.x > -INFINITY ? ex2_approx(ml1.x - M) : 0.f;
+        const float lsum = ml0.y * w0 + ml1.y * w1;
+        const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+        // staging for group 1's half: row r = 256 bytes, 16-byte chunk c at chunk c ^ (r % 16); the K/V ring is free now
+        float4 *stage = (float4 *)(kv_tiles) + (size_t)r * 16;
+        if (g == 1) {
+            const float f1 = w1 * inv;
+            const bool have = T > 1 && alive;      // with a single key block group 1 never wrote its accumulator
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
-                uint32_t w[4];
+            for (int c0 = 0; c0 < 64; c0 += 16) {
+                uint32_t oc[16];
+                if (have) {
+                    TMEM_LD_16((oc), tmem_o[1] + lane_field + c0);
+                    tmem_wait_ld();
+                }
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    float a0 = T > 0 ? __uint_as_float(orow[8 * c + 2 * j]) * inv : 0.f;
-                    float a1 = T > 0 ? __uint_as_float(orow[8 * c + 2 * j + 1]) * inv : 0.f;
-                    w[j] = pack2(a0, a1, p.is_bf16);
+                    float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (have)
+                        v4 = make_float4(__uint_as_float(oc[4 * j]) * f1, __uint_as_float(oc[4 * j + 1]) * f1,
+                                         __uint_as_float(oc[4 * j + 2]) * f1, __uint_as_float(oc[4 * j + 3]) * f1);
+                    stage[((c0 >> 2) + j) ^ (r & 15)] = v4;
                 }
-                *(uint4 *)(dst + 8 * c) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+        softmax_groups_sync();
+        if (g == 0 && alive && row_valid) {
+            const float f0 = w0 * inv;
+            uint16_t *dst = (uint16_t *)p.O + ((size_t)b * L + (size_t)pair * 128 + r) * ((size_t)p.H * 64) + (size_t)h * 64;
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) {
+                uint32_t oc[16];
+                if (T > 0) {
+                    TMEM_LD_16((oc), tmem_o[0] + lane_field + c0);
+                    tmem_wait_ld();
+                }
+                uint32_t w[8];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float4 o1 = stage[((c0 >> 2) + j) ^ (r & 15)];
+                    float a0 = o1.x, a1 = o1.y, a2 = o1.z, a3 = o1.w;
+                    if (T > 0) {
+                        a0 += __uint_as_float(oc[4 * j]) * f0;
+                        a1 += __uint_as_float(oc[4 * j + 1]) * f0;
+                        a2 += __uint_as_float(oc[4 * j + 2]) * f0;
+                        a3 += __uint_as_float(oc[4 * j + 3]) * f0;
+                    }
+                    w[2 * j] = pack2(a0, a1, p.is_bf16);
+                    w[2 * j + 1] = pack2(a2, a3, p.is_bf16);
+                }
+                *(uint4 *)(dst + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+                *(uint4 *)(dst + c0 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
             }
         }
     }
@@ -537,10 +633,22 @@ int tc_fused_attention(cudaStream_t s, const void *nn_lut, const void *q, const 
         if (e1 != cudaSuccess || e2 != cudaSuccess) return fail("sfb_fused_attention: cannot reserve %zu bytes of shared memory", kSmemBytes);
         configured = true;
     }
-    if (mask) fused_attention_tc_kernel<true><<<grid, 192, kSmemBytes, s>>>(qm, km, vm, prm);
-    else fused_attention_tc_kernel<false><<<grid, 192, kSmemBytes, s>>>(qm, km, vm, prm);
+    if (mask) fused_attention_tc_kernel<true><<<grid, 320, kSmemBytes, s>>>(qm, km, vm, prm);
+    else fused_attention_tc_kernel<false><<<grid, 320, kSmemBytes, s>>>(qm, km, vm, prm);
     return check_launch("sfb_fused_attention");
 }
+
+#ifdef SFB_TC_TIMING
+extern "C" int sfb_debug_timing(unsigned long long *out, int reset)
+{
+    cudaMemcpyFromSymbol(out, tc::g_timing, sizeof(unsigned long long) * 32);
+    if (reset) {
+        unsigned long long z[32] = {0};
+        cudaMemcpyToSymbol(tc::g_timing, z, sizeof(z));
+    }
+    return 0;
+}
+#endif
 
 int tc_status(uint32_t *out)
 {
