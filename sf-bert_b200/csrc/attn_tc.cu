@@ -4,15 +4,16 @@
 // One CTA owns a PAIR of adjacent block-rows (128 queries = one M=128 MMA tile) and walks the union of
 // the two rows' key blocks.  Nothing is exchanged between CTAs: no flags, no scratch, no waiting on
 // other CTAs.  Per key block:
-//     S  = Q . K^T            tcgen05.mma  (A, B from shared memory, accumulator in TMEM)
-//     P  = exp2(S*c - m)      128 threads, one query row each, straight out of TMEM
-//     O += P . V              tcgen05.mma  (P as the A operand straight from TMEM, where it overwrites S;
-//                                          V from shared memory as an MN-major operand)
-// Warp roles: warp 0 issues the TMA loads, warp 1 issues the MMAs, warps 2-5 and 6-9 are two softmax
-// groups that take the key blocks alternately.  Each group keeps its own running max / sum and its own
-// O accumulator in TMEM (an online softmax over its half of the key blocks); the two halves are merged
-// once, in the epilogue.  Every wait on an mbarrier is bounded; on a timeout the CTA records a status
-// word and leaves through the common teardown (TMEM freed, loads in flight drained).
+//     S  = Q . K^T            tcgen05.mma, A and B from shared memory, accumulator in TMEM (two S buffers)
+//     P  = exp2(S*c - m)      128 threads, one query row each, straight out of TMEM (two exponentials per
+//                             MUFU instruction on packed fp16); P is written back over S as 16-bit pairs
+//     O += P . [V | 1]        tcgen05.mma, P as the A operand from TMEM, V from shared memory as an
+//                             MN-major operand, followed by a tile of ones: 16 extra accumulator
+//                             columns receive the row sums of P, so the softmax denominator comes out
+//                             of the tensor core and is rescaled together with O
+// Warp roles: warp 0 issues the TMA loads, warp 1 issues the MMAs, warps 2-5 do the softmax and the
+// epilogue.  Every wait on an mbarrier is bounded; on a timeout the CTA records a status word and
+// leaves through the common teardown (TMEM freed, loads in flight drained).
 #include "attn.cuh"
 #include <cuda.h>
 
@@ -24,7 +25,8 @@ constexpr int kStages = 4;                      // K/V ring depth
 constexpr int kMaxUnion = 512;                  // key blocks a row pair may touch
 constexpr uint32_t kTileBytes = 64 * 64 * 2;    // one 64x64 16-bit tile
 constexpr uint32_t kQBytes = 128 * 64 * 2;
-constexpr uint32_t kTmemCols = 256;             // S0 | S1 | O0 | O1, 64 columns each; P(16-bit) reuses S's first 32
+constexpr uint32_t kTmemCols = 256;             // S0 | S1 | O (64 + 16 row-sum columns); P reuses S's first 32 columns
+constexpr uint32_t kOnesBytes = 64 * 128;       // the tile of ones behind V
 constexpr uint32_t kWaitLimit = 1u << 24;
 constexpr float kRescaleThreshold = 8.0f;       // log2 units: P stays below 2^8
 
@@ -36,14 +38,13 @@ struct UnionEntry {
 
 struct SharedState {
     uint64_t q_full, kv_full[kStages], kv_empty[kStages];
-    uint64_t s_full[2], p_full[2], pv_done[2], o_final, drained;
+    uint64_t s_full[2], p_full[2], pv_done, o_final, drained;
     uint32_t tmem_base, n_union, abort_flag, pad;
-    float2 ml[2][128];             // (running max, running sum) of each group's rows, for the merge
     UnionEntry entries[kMaxUnion];
     uint8_t found[kMaxUnion];
 };
 
-constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + kQBytes + kStages * 2 * kTileBytes + sizeof(SharedState);
+constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + kQBytes + kStages * 2 * kTileBytes + kOnesBytes + sizeof(SharedState);
 
 struct Params {
     const uint2 *nn_lut;
@@ -149,22 +150,23 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar)
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
+// shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart.  lbo_bytes only matters
+// for an MN-major operand wider than 64 elements: it is the distance to the next group of 64 columns.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_bytes = 16)
 {
     uint64_t d = 0;
     d |= (uint64_t)((addr & 0x3ffffu) >> 4);   // start address
-    d |= (uint64_t)1 << 16;                    // leading byte offset (not used by swizzled layouts)
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;   // leading byte offset
     d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset
     d |= (uint64_t)1 << 46;                    // descriptor version
     d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
     return d;
 }
 
-// instruction descriptor of kind::f16: fp32 accumulator, M x N tile, 16-bit A/B of one format
-__device__ __forceinline__ uint32_t instr_desc(uint32_t fmt, uint32_t M, uint32_t N, uint32_t b_mn_major)
+// instruction descriptor of kind::f16: fp32 accumulator, M x N tile, 16-bit A and B (0 = fp16, 1 = bf16)
+__device__ __forceinline__ uint32_t instr_desc(uint32_t a_fmt, uint32_t b_fmt, uint32_t M, uint32_t N, uint32_t b_mn_major)
 {
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn_major << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
+    return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (b_mn_major << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
 #define TMEM_LD_32(r, addr)                                                                                              \
@@ -199,6 +201,40 @@ __device__ __forceinline__ float ex2_approx(float x)
     return y;
 }
 
+// exp2 of two values at once: fp32 pair -> packed fp16 pair -> MUFU on both halves (lo = first value)
+__device__ __forceinline__ uint32_t ex2_pair_f16(float lo, float hi)
+{
+    __half2 h = __floats2half2_rn(lo, hi);
+    uint32_t x = *reinterpret_cast<uint32_t *>(&h), y;
+    asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+// packed fp16 pair -> packed bf16 pair (the MMA wants A and B in one format)
+__device__ __forceinline__ uint32_t f16x2_to_bf16x2(uint32_t v)
+{
+    const float2 f = __half22float2(*reinterpret_cast<__half2 *>(&v));
+    __nv_bfloat162 o = __floats2bfloat162_rn(f.x, f.y);
+    return *reinterpret_cast<uint32_t *>(&o);
+}
+// (a0, a1) * b + c on the packed fp32 pipe
+__device__ __forceinline__ void fma2(float &d0, float &d1, float a0, float a1, float b, float c)
+{
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %4};\n\t"
+        "mov.b64 rc, {%5, %5};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 __device__ __forceinline__ uint32_t pack2(float a, float b, int is_bf16)
 {
     if (is_bf16) {
@@ -222,10 +258,8 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int is_bf16)
                    "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])      \
                  : "memory")
 
-__device__ __forceinline__ void softmax_groups_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
-
-template <bool HAS_MASK>
-__global__ void __launch_bounds__(320, 2)
+template <bool HAS_MASK, bool BF16>
+__global__ void __launch_bounds__(192, 2)
 fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                           const __grid_constant__ CUtensorMap vmap, const Params p)
 {
@@ -233,7 +267,8 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *q_tile = smem;
     uint8_t *kv_tiles = q_tile + kQBytes;                      // stage s: K at s*2*kTileBytes, V right after
-    SharedState *st = (SharedState *)(kv_tiles + kStages * 2 * kTileBytes);
+    uint8_t *ones_tile = kv_tiles + kStages * 2 * kTileBytes;
+    SharedState *st = (SharedState *)(ones_tile + kOnesBytes);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t pair = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
@@ -242,8 +277,9 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     const uint32_t L = p.nb * 64;
     const uint2 *nn = p.nn_lut + (size_t)h * p.lut_stride;
     volatile uint32_t *abort_flag = &st->abort_flag;
+    const uint32_t fmt = BF16 ? 1u : 0u;
 
-    // ---- set-up: barriers, TMEM, the union of the two rows' key blocks ----
+    // ---- set-up: barriers, the tile of ones, TMEM, the union of the two rows' key blocks ----
     if (threadIdx.x == 0) {
         mbar_init(&st->q_full, 1);
         for (int s = 0; s < kStages; s++) {
@@ -253,12 +289,19 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
         for (int s = 0; s < 2; s++) {
             mbar_init(&st->s_full[s], 1);
             mbar_init(&st->p_full[s], 128);
-            mbar_init(&st->pv_done[s], 1);
         }
+        mbar_init(&st->pv_done, 1);
         mbar_init(&st->o_final, 1);
         mbar_init(&st->drained, 1);
         st->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    {
+        // 1.0 in the operand type of V, everywhere: the swizzle cannot matter
+        const uint32_t one2 = BF16 ? 0x3f803f80u : 0x3c003c00u;
+        for (uint32_t i = threadIdx.x; i < kOnesBytes / 16; i += blockDim.x)
+            ((uint4 *)ones_tile)[i] = make_uint4(one2, one2, one2, one2);
+        fence_proxy_async();
     }
     const uint2 head0 = nn[row0];
     const uint2 head1 = has_row1 ? nn[row1] : make_uint2(0, 0);
@@ -324,8 +367,7 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     const uint32_t T = st->n_union;
     const uint32_t tmem = st->tmem_base;
     const uint32_t tmem_s[2] = {tmem, tmem + 64};
-    const uint32_t tmem_o[2] = {tmem + 128, tmem + 192};
-    const uint32_t fmt = p.is_bf16 ? 1u : 0u;
+    const uint32_t tmem_o = tmem + 128;          // 64 columns of O, then 16 columns that all hold the row sum
     const int32_t xq = (int32_t)(h * 64);
 
     if (warp == 0) {
@@ -343,11 +385,11 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             }
         }
     } else if (warp == 1) {
-        // ===== MMA issuer: S(0) S(1) | O(0) S(2) | O(1) S(3) | ...  S(t+2) overwrites P(t) in TMEM, which is safe
-        // because the tensor core runs this thread's MMAs in order =====
+        // ===== MMA issuer: S(0) | S(1) O(0) | S(2) O(1) | ...  S(t+1) lands in the buffer that held P(t-1); the
+        // tensor core runs this thread's MMAs in order, so P(t-1) has been consumed by then =====
         if (lane == 0 && T > 0) {
-            const uint32_t idesc_qk = instr_desc(fmt, 128, 64, 0);
-            const uint32_t idesc_pv = instr_desc(fmt, 128, 64, 1);
+            const uint32_t idesc_qk = instr_desc(fmt, fmt, 128, 64, 0);
+            const uint32_t idesc_pv = instr_desc(fmt, fmt, 128, 80, 1);   // A and B must share a format
             const uint64_t q_desc = smem_desc_sw128(smem_u32(q_tile));
             bool alive = mbar_wait(&st->q_full, 0, abort_flag, 2);
             auto issue_qk = [&](uint32_t t) -> bool {
@@ -364,47 +406,46 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                 return true;
             };
             if (alive) alive = issue_qk(0);
-            if (alive && T > 1) alive = issue_qk(1);
             for (uint32_t t = 0; alive && t < T; t++) {
-                const uint32_t g = t & 1, s = t % kStages;
+                const uint32_t s = t % kStages;
+                if (t + 1 < T && !issue_qk(t + 1)) { alive = false; break; }
                 TIC(c2);
-                if (!mbar_wait(&st->p_full[g], (t >> 1) & 1, abort_flag, 5)) { alive = false; break; }
+                if (!mbar_wait(&st->p_full[t & 1], (t >> 1) & 1, abort_flag, 5)) { alive = false; break; }
                 TOC(12, c2);
                 tcgen05_fence_after();
-                const uint64_t v_desc = smem_desc_sw128(smem_u32(kv_tiles + s * 2 * kTileBytes + kTileBytes));
+                // B = [V | ones]: 64 columns from the V tile, the next group of columns from the tile of ones
+                const uint32_t v_addr = smem_u32(kv_tiles + s * 2 * kTileBytes + kTileBytes);
+                const uint64_t v_desc = smem_desc_sw128(v_addr, smem_u32(ones_tile) - v_addr);
 #pragma unroll
                 for (uint32_t kk = 0; kk < 4; kk++)   // 16 keys per MMA: 8 TMEM columns of P, 16 rows (2048 bytes) of V
-                    umma_f16_ts(tmem_o[g], tmem_s[g] + 8 * kk, v_desc + 128 * kk, idesc_pv, (t >= 2 || kk) ? 1u : 0u);
+                    umma_f16_ts(tmem_o, tmem_s[t & 1] + 8 * kk, v_desc + 128 * kk, idesc_pv, (t | kk) ? 1u : 0u);
                 umma_commit(&st->kv_empty[s]);
-                umma_commit(&st->pv_done[g]);
-                // the epilogue needs "everything done", which the per-group parity barriers cannot express
+                umma_commit(&st->pv_done);
+                // the epilogue may be two completions ahead of pv_done, which a parity wait cannot tell apart
                 if (t + 1 == T) umma_commit(&st->o_final);
-                if (t + 2 < T && !issue_qk(t + 2)) { alive = false; break; }
             }
         }
     } else {
-        // ===== softmax groups + epilogue: one query row per thread, group g takes key blocks g, g+2, ... =====
-        const uint32_t g = (warp - 2) >> 2;
+        // ===== softmax + epilogue: one query row per thread =====
         const uint32_t quarter = warp & 3;                 // TMEM lanes this warp may touch
         const uint32_t r = quarter * 32 + lane;            // row inside the 128-query tile
         const uint32_t half = r >> 6;                      // which of the two block-rows
         const uint32_t lane_field = (quarter * 32) << 16;
         const bool row_valid = half == 0 || has_row1;
         const float sl = p.scale_log2e;
-        float m_used = -INFINITY, l = 0.f;
+        float m_used = -INFINITY;
         bool alive = true;
 
         TIC(c_loop);
-        for (uint32_t t = g; t < T; t += 2) {
-            const uint32_t u = t >> 1;
+        for (uint32_t t = 0; t < T; t++) {
             TIC(c0);
-            if (!mbar_wait_warp(&st->s_full[g], u & 1, abort_flag, 6)) { alive = false; break; }
+            if (!mbar_wait_warp(&st->s_full[t & 1], (t >> 1) & 1, abort_flag, 6)) { alive = false; break; }
             TOC(0, c0);
             TIC(c1);
             tcgen05_fence_after();
             uint32_t sr[64];
-            TMEM_LD_32((sr), tmem_s[g] + lane_field);
-            TMEM_LD_32((sr + 32), tmem_s[g] + lane_field + 32);
+            TMEM_LD_32((sr), tmem_s[t & 1] + lane_field);
+            TMEM_LD_32((sr + 32), tmem_s[t & 1] + lane_field + 32);
             tmem_wait_ld();
             TOC(1, c1);
             TIC(c2);
@@ -419,13 +460,17 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                     for (int c = 0; c < 64; c++)
                         if (!((w >> c) & 1)) sr[c] = 0xff800000u;
                 }
-                float m8[8];
+                float m4[4];
 #pragma unroll
-                for (int c = 0; c < 8; c++) m8[c] = __uint_as_float(sr[c]);
+                for (int c = 0; c < 4; c++) m4[c] = __uint_as_float(sr[c]);
 #pragma unroll
-                for (int c = 8; c < 64; c++) m8[c & 7] = fmaxf(m8[c & 7], __uint_as_float(sr[c]));
-                mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
-                mx *= sl;
+                for (int c = 4; c < 64; c += 8) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        if (c + 2 * j + 1 < 64)
+                            m4[j] = max3(m4[j], __uint_as_float(sr[c + 2 * j]), __uint_as_float(sr[c + 2 * j + 1]));
+                }
+                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * sl;
             }
             // move the reference max only when the row max outgrew it by 2^8: rescaling O stays rare
             const bool grow = mx > m_used + kRescaleThreshold || (m_used == -INFINITY && mx > -INFINITY);
@@ -433,22 +478,21 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             float alpha = 1.f;
             if (grow) {
                 alpha = fix_o ? ex2_approx(m_used - mx) : 0.f;
-                l *= alpha;
                 m_used = mx;
             }
-            if (u > 0 && __any_sync(0xffffffffu, fix_o)) {
-                // this group's O must be complete (its previous key block) before it is rescaled
-                if (!mbar_wait_warp(&st->pv_done[g], (u - 1) & 1, abort_flag, 7)) { alive = false; break; }
+            if (t > 0 && __any_sync(0xffffffffu, fix_o)) {
+                // O (and the row sums next to it) must be complete before they are rescaled
+                if (!mbar_wait_warp(&st->pv_done, (t - 1) & 1, abort_flag, 7)) { alive = false; break; }
                 tcgen05_fence_after();
                 const float a = fix_o ? alpha : 1.f;
 #pragma unroll
-                for (int c0 = 0; c0 < 64; c0 += 16) {
+                for (int c0 = 0; c0 < 80; c0 += 16) {
                     uint32_t oc[16];
-                    TMEM_LD_16((oc), tmem_o[g] + lane_field + c0);
+                    TMEM_LD_16((oc), tmem_o + lane_field + c0);
                     tmem_wait_ld();
 #pragma unroll
                     for (int c = 0; c < 16; c++) oc[c] = __float_as_uint(__uint_as_float(oc[c]) * a);
-                    TMEM_ST_16(tmem_o[g] + lane_field + c0, (oc));
+                    TMEM_ST_16(tmem_o + lane_field + c0, (oc));
                 }
                 tmem_wait_st();
             }
@@ -456,94 +500,63 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             TIC(c3);
             const float neg_m = m_used > -INFINITY ? -m_used : 0.f;
             uint32_t pk[32];
-            float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (mine) {
 #pragma unroll
-            for (int c = 0; c < 64; c += 2) {
-                float p0 = 0.f, p1 = 0.f;
-                if (mine) {
-                    p0 = ex2_approx(fmaf(__uint_as_float(sr[c]), sl, neg_m));
-                    p1 = ex2_approx(fmaf(__uint_as_float(sr[c + 1]), sl, neg_m));
+                for (int c = 0; c < 64; c += 2) {
+                    float x0, x1;
+                    fma2(x0, x1, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]), sl, neg_m);
+                    const uint32_t e2 = ex2_pair_f16(x0, x1);
+                    pk[c >> 1] = BF16 ? f16x2_to_bf16x2(e2) : e2;
                 }
-                ps4[(c >> 1) & 3] += p0 + p1;
-                pk[c >> 1] = pack2(p0, p1, p.is_bf16);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; c++) pk[c] = 0u;
             }
-            l += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
             TOC(3, c3);
             TIC(c5);
             // P (16-bit pairs) takes the place of the first 32 columns of this row of S
-            TMEM_ST_32(tmem_s[g] + lane_field, (pk));
+            TMEM_ST_32(tmem_s[t & 1] + lane_field, (pk));
             tmem_wait_st();
             tcgen05_fence_before();
-            mbar_arrive(&st->p_full[g]);
+            mbar_arrive(&st->p_full[t & 1]);
             TOC(5, c5);
         }
         TOC(6, c_loop);
 #ifdef SFB_TC_TIMING
-        if (timing_on) atomicAdd(&g_timing[7], (unsigned long long)((T + 1) / 2));
+        if (timing_on) atomicAdd(&g_timing[7], (unsigned long long)T);
 #endif
 
-        // ---- epilogue: merge the two groups' partial softmaxes, O / l -> global ----
-        // Both named barriers below are reached by all 256 softmax threads whatever happened before.
-        st->ml[g][r] = make_float2(m_used, l);
+        // ---- epilogue: O / row sum -> global ----
         if (T > 0 && alive) alive = mbar_wait_warp(&st->o_final, 0, abort_flag, 10);
-        tcgen05_fence_after();
-        softmax_groups_sync();
-        const float2 ml0 = st->ml[0][r], ml1 = st->ml[1][r];
-        const float M = fmaxf(ml0.x, ml1.x);
-        const float w0 = ml0.x > -INFINITY ? ex2_approx(ml0.x - M) : 0.f;
-        const float w1 = ml1.x > -INFINITY ? ex2_approx(ml1.x - M) : 0.f;
-        const float lsum = ml0.y * w0 + ml1.y * w1;
-        const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-        // staging for group 1's half: row r = 256 bytes, 16-byte chunk c at chunk c ^ (r % 16); the K/V ring is free now
-        float4 *stage = (float4 *)(kv_tiles) + (size_t)r * 16;
-        if (g == 1) {
-            const float f1 = w1 * inv;
-            const bool have = T > 1 && alive;      // with a single key block group 1 never wrote its accumulator
-#pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 16) {
-                uint32_t oc[16];
-                if (have) {
-                    TMEM_LD_16((oc), tmem_o[1] + lane_field + c0);
-                    tmem_wait_ld();
-                }
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (have)
-                        v4 = make_float4(__uint_as_float(oc[4 * j]) * f1, __uint_as_float(oc[4 * j + 1]) * f1,
-                                         __uint_as_float(oc[4 * j + 2]) * f1, __uint_as_float(oc[4 * j + 3]) * f1);
-                    stage[((c0 >> 2) + j) ^ (r & 15)] = v4;
-                }
+        if (alive && row_valid) {
+            tcgen05_fence_after();
+            float inv = 0.f;
+            if (T > 0) {
+                uint32_t lc[16];
+                TMEM_LD_16((lc), tmem_o + lane_field + 64);
+                tmem_wait_ld();
+                const float lsum = __uint_as_float(lc[0]);
+                inv = lsum > 0.f ? 1.f / lsum : 0.f;
             }
-        }
-        softmax_groups_sync();
-        if (g == 0 && alive && row_valid) {
-            const float f0 = w0 * inv;
             uint16_t *dst = (uint16_t *)p.O + ((size_t)b * L + (size_t)pair * 128 + r) * ((size_t)p.H * 64) + (size_t)h * 64;
 #pragma unroll
             for (int c0 = 0; c0 < 64; c0 += 16) {
-                uint32_t oc[16];
+                uint32_t oc[16], w[8];
                 if (T > 0) {
-                    TMEM_LD_16((oc), tmem_o[0] + lane_field + c0);
+                    TMEM_LD_16((oc), tmem_o + lane_field + c0);
                     tmem_wait_ld();
                 }
-                uint32_t w[8];
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const float4 o1 = stage[((c0 >> 2) + j) ^ (r & 15)];
-                    float a0 = o1.x, a1 = o1.y, a2 = o1.z, a3 = o1.w;
-                    if (T > 0) {
-                        a0 += __uint_as_float(oc[4 * j]) * f0;
-                        a1 += __uint_as_float(oc[4 * j + 1]) * f0;
-                        a2 += __uint_as_float(oc[4 * j + 2]) * f0;
-                        a3 += __uint_as_float(oc[4 * j + 3]) * f0;
-                    }
-                    w[2 * j] = pack2(a0, a1, p.is_bf16);
-                    w[2 * j + 1] = pack2(a2, a3, p.is_bf16);
+                for (int j = 0; j < 8; j++) {
+                    const float a0 = T > 0 ? __uint_as_float(oc[2 * j]) * inv : 0.f;
+                    const float a1 = T > 0 ? __uint_as_float(oc[2 * j + 1]) * inv : 0.f;
+                    w[j] = pack2(a0, a1, BF16);
                 }
                 *(uint4 *)(dst + c0) = make_uint4(w[0], w[1], w[2], w[3]);
                 *(uint4 *)(dst + c0 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
             }
+        } else if (!row_valid) {
+            // lanes of the absent lower block-row still take part in the aligned TMEM loads above: nothing to do
         }
     }
 
@@ -628,13 +641,17 @@ int tc_fused_attention(cudaStream_t s, const void *nn_lut, const void *q, const 
     dim3 grid((p.nb_a + 1) / 2, p.B, p.H);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e1 = cudaFuncSetAttribute(fused_attention_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-        cudaError_t e2 = cudaFuncSetAttribute(fused_attention_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-        if (e1 != cudaSuccess || e2 != cudaSuccess) return fail("sfb_fused_attention: cannot reserve %zu bytes of shared memory", kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(fused_attention_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(fused_attention_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(fused_attention_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(fused_attention_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        if (e != cudaSuccess) return fail("sfb_fused_attention: cannot reserve %zu bytes of shared memory", kSmemBytes);
         configured = true;
     }
-    if (mask) fused_attention_tc_kernel<true><<<grid, 320, kSmemBytes, s>>>(qm, km, vm, prm);
-    else fused_attention_tc_kernel<false><<<grid, 320, kSmemBytes, s>>>(qm, km, vm, prm);
+    if (mask && is_bf16) fused_attention_tc_kernel<true, true><<<grid, 192, kSmemBytes, s>>>(qm, km, vm, prm);
+    else if (mask) fused_attention_tc_kernel<true, false><<<grid, 192, kSmemBytes, s>>>(qm, km, vm, prm);
+    else if (is_bf16) fused_attention_tc_kernel<false, true><<<grid, 192, kSmemBytes, s>>>(qm, km, vm, prm);
+    else fused_attention_tc_kernel<false, false><<<grid, 192, kSmemBytes, s>>>(qm, km, vm, prm);
     return check_launch("sfb_fused_attention");
 }
 
