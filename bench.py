@@ -231,6 +231,60 @@ def run_ours(args):
 
 
 # ------------------------------------------------------------------------------------------------
+def run_bandwidth_kernel(args):
+    """Roofline lines of the two bandwidth-bound kernels of the path (N=1): `--kernel softmax` is the
+    stand-alone masked softmax (bf16 scores in, bf16 probabilities out) on the workload's layout,
+    `--kernel layernorm` the fused bias + residual + LayerNorm on [B*L, H*d] rows."""
+    import torch
+    import __graft_entry__ as ge
+    sfb = ge.load_package()
+    torch.cuda.set_device(0)
+    cfg = CONFIGS[args.config]
+    B, H, L, d, bs = cfg["B"], cfg["H"], cfg["L"], cfg["d"], cfg["bs"]
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    if args.kernel == "softmax":
+        lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
+        x = torch.randn(B, H, lay.blocks, bs, bs, device="cuda").to(torch.bfloat16)
+        fn = lambda: sfb.masked_softmax(x, lay, 0.125, torch.bfloat16)
+        nbytes = x.numel() * 2 * 2
+        name, unit_name = "softmax_kernel", "bf16 scores read + bf16 probabilities written"
+    else:
+        tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[cfg["dtype"]]
+        m, hidden = B * L, H * d
+        x = torch.randn(m, hidden, device="cuda").to(tdt)
+        r = torch.randn(m, hidden, device="cuda").to(tdt)
+        bias, gain, beta = (torch.randn(hidden, device="cuda") for _ in range(3))
+        fn = lambda: sfb.bias_residual_layernorm(x, bias, r, gain, beta)
+        nbytes = 3 * m * hidden * x.element_size()
+        name, unit_name = "bias_residual_layernorm_kernel", "x and residual read + output written"
+    for _ in range(max(args.warmup, 3)):
+        flush.fill_(1)
+        fn()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a, b_ in ev:
+        flush.fill_(1)
+        a.record()
+        fn()
+        b_.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = sum(a.elapsed_time(b_) for a, b_ in ev) / args.steps
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": args.kernel + " GB/s (algorithmic bytes)", "value": round(gbs, 1), "unit": "GB/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5), "higher_is_better": True,
+        "dtype": "bf16" if args.kernel == "softmax" else cfg["dtype"], "data": "synthetic",
+        "config": {"workload": args.config, "kernel": name, "bytes": unit_name, "l2": "flushed between timed steps"},
+        "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm"], "unit": "GB/s",
+                     "frac": round(gbs / pk["hbm"], 4), "traffic": None, "peak_source": pk["source"] + " copy bandwidth",
+                     "algorithmic_bytes": nbytes},
+        "gpu_launches": args.steps, "clocks": clocks}), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
 def cpu_reference_sample(cfg, budget_s, steps):
     """Times the reference's CPU attention operators (multiheadmatmulNT -> softmax -> multiheadmatmulNN,
     transformer_inference_part.cpp:219-224) on B' = host threads batches x 1 head, at the longest
@@ -304,8 +358,12 @@ if __name__ == "__main__":
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="stride_bertbase", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm"],
+                    help="fused = the headline fused attention; softmax / layernorm = the bandwidth kernels (N=1)")
     a = ap.parse_args()
     if a.impl == "reference":
         run_reference(a)
+    elif a.kernel != "fused":
+        run_bandwidth_kernel(a)
     else:
         run_ours(a)

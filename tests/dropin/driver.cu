@@ -1,0 +1,130 @@
+// A driver shaped like the reference's *_fusion_test.cu programs: it builds the look-up tables on the
+// host the way those programs do, uploads them, and calls the operators through the drop-in headers
+// (include/blocksparse.h, include/fusion_blocksparse.h) with the reference's argument order.  Inputs are
+// all ones, the reference's own known answer (fixed_fusion_test.cu:263-268, test.cu:382-386): every score
+// equals d, every probability 1 / (kept keys of the row), every output 1.
+// Prints "PASS" and returns 0 when all of that holds on the GPU.
+#include <cstdio>
+#include <cstdlib>
+#include <cmath>
+#include <vector>
+#include "blocksparse.h"
+#include "fusion_blocksparse.h"
+
+static float bf(ushort v) { unsigned u = (unsigned)v << 16; float f; memcpy(&f, &u, 4); return f; }
+
+int main()
+{
+    const uint batch_dim = 2, heads_ = 4, head_state_ = 128, blk_size_ = 32, seq_len = 320;
+    const uint ctx_blks_ = seq_len / blk_size_;
+    const float scale = 1.0f / sqrtf((float)head_state_);
+    const uint lut_heads = 1, mask_heads = 1;
+
+    // causal block layout, as no_fusion_test.cu builds it
+    std::vector<uint2> nt;
+    for (uint i = 0; i < ctx_blks_; i++)
+        for (uint j = 0; j <= i; j++) nt.push_back(make_uint2(i, j));
+    const uint blocks = (uint)nt.size();
+    std::vector<uint2> nn(ctx_blks_ + blocks, make_uint2(0, 0));
+    for (uint k = 0; k < blocks; k++) {
+        nn[ctx_blks_ + k] = make_uint2(k, nt[k].y);
+        nn[nt[k].x].y++;
+    }
+    nn[0].x = ctx_blks_;
+    for (uint i = 1; i < ctx_blks_; i++) nn[i].x = nn[i - 1].x + nn[i - 1].y;
+    uint nn_max = 0;
+    for (uint i = 0; i < ctx_blks_; i++) nn_max = nn[i].y > nn_max ? nn[i].y : nn_max;
+    // causal element mask on the diagonal blocks: mask_np [blocks][32] and its transpose [32][blocks]
+    std::vector<uint> mask_np(blocks * blk_size_), mask_t(blocks * blk_size_);
+    for (uint k = 0; k < blocks; k++)
+        for (uint r = 0; r < blk_size_; r++) {
+            uint w = 0;
+            for (uint c = 0; c < blk_size_; c++)
+                if (nt[k].x != nt[k].y || r >= c) w |= 1u << c;
+            mask_np[k * blk_size_ + r] = w;
+            mask_t[r * blocks + k] = w;
+        }
+
+    const size_t n_in = (size_t)batch_dim * seq_len * heads_ * head_state_;
+    const size_t n_blk = (size_t)batch_dim * heads_ * blocks * blk_size_ * blk_size_;
+    std::vector<float> ones(n_in, 1.0f);
+    uint2 *d_nt, *d_nn;
+    uint *d_mask_np, *d_mask_t;
+    float *a_ptr, *b_ptr, *v_ptr, *o_ptr, *o2_ptr, *y_ptr, *Max, *Sum;
+    bhalf *c_ptr, *y2_ptr;
+    int *flag, *flag1;
+    cudaMalloc(&d_nt, sizeof(uint2) * blocks);
+    cudaMalloc(&d_nn, sizeof(uint2) * nn.size());
+    cudaMalloc(&d_mask_np, sizeof(uint) * mask_np.size());
+    cudaMalloc(&d_mask_t, sizeof(uint) * mask_t.size());
+    cudaMalloc(&a_ptr, sizeof(float) * n_in);
+    cudaMalloc(&b_ptr, sizeof(float) * n_in);
+    cudaMalloc(&v_ptr, sizeof(float) * n_in);
+    cudaMalloc(&o_ptr, sizeof(float) * n_in);
+    cudaMalloc(&o2_ptr, sizeof(float) * n_in);
+    cudaMalloc(&y_ptr, sizeof(float) * n_blk);
+    cudaMalloc(&c_ptr, sizeof(bhalf) * n_blk);
+    cudaMalloc(&y2_ptr, sizeof(bhalf) * n_blk);
+    cudaMalloc(&Max, sizeof(float) * batch_dim * heads_ * blocks * blk_size_);
+    cudaMalloc(&Sum, sizeof(float) * batch_dim * heads_ * blocks * blk_size_);
+    cudaMalloc(&flag, sizeof(int) * ctx_blks_ * batch_dim * heads_);
+    cudaMalloc(&flag1, sizeof(int) * ctx_blks_ * batch_dim * heads_);
+    cudaMemcpy(d_nt, nt.data(), sizeof(uint2) * blocks, cudaMemcpyHostToDevice);
+    cudaMemcpy(d_nn, nn.data(), sizeof(uint2) * nn.size(), cudaMemcpyHostToDevice);
+    cudaMemcpy(d_mask_np, mask_np.data(), sizeof(uint) * mask_np.size(), cudaMemcpyHostToDevice);
+    cudaMemcpy(d_mask_t, mask_t.data(), sizeof(uint) * mask_t.size(), cudaMemcpyHostToDevice);
+    cudaMemcpy(a_ptr, ones.data(), sizeof(float) * n_in, cudaMemcpyHostToDevice);
+    cudaMemcpy(b_ptr, ones.data(), sizeof(float) * n_in, cudaMemcpyHostToDevice);
+    cudaMemcpy(v_ptr, ones.data(), sizeof(float) * n_in, cudaMemcpyHostToDevice);
+
+    CUstream custream;
+    cudaStreamCreate(&custream);
+    uint magic_, shift_;
+    magicu64(CEIL_DIV(head_state_, 64), magic_, shift_);
+
+    // the unfused path, as transformer_attention_optimize.cu:728-748 calls it
+    bool ok = bst_sgemm_nt(custream, d_nt, a_ptr, b_ptr, c_ptr, blk_size_, blocks, batch_dim, ctx_blks_, ctx_blks_, heads_,
+                           head_state_, lut_heads, blocks);
+    ok = ok && BlocksparseMaskedSoftmax<bhalf, bhalf2>(custream, d_nn, d_mask_t, c_ptr, y2_ptr, blk_size_, blocks, batch_dim,
+                                                       heads_, ctx_blks_, lut_heads, blocks + ctx_blks_, nn_max, mask_heads, scale);
+    ok = ok && bst_sgemm_xn(custream, d_nn, y2_ptr, v_ptr, o_ptr, blk_size_, blocks, batch_dim, ctx_blks_, ctx_blks_, heads_,
+                            head_state_, lut_heads, blocks + ctx_blks_, NN_OP, magic_, shift_, nn_max);
+    // the fused paths, as the *_fusion_test.cu programs call them
+    ok = ok && fusion_attention2<float, float2>(custream, d_nt, a_ptr, b_ptr, c_ptr, d_nn, flag, flag1, d_mask_np, Max, Sum, y_ptr,
+                                                blk_size_, blocks, batch_dim, ctx_blks_, ctx_blks_, heads_, head_state_,
+                                                lut_heads, blocks, mask_heads, scale);
+    ok = ok && fusion_attention<float, float2>(custream, d_nt, a_ptr, b_ptr, c_ptr, d_nn, flag, flag1, d_mask_np, Max, Sum, y_ptr,
+                                               v_ptr, o2_ptr, blk_size_, blocks, batch_dim, ctx_blks_, ctx_blks_, ctx_blks_, heads_,
+                                               head_state_, lut_heads, blocks, mask_heads, scale, nn_max);
+    // an unsupported block size is reported, not silently ignored
+    const bool rejected = !bst_sgemm_nt(custream, d_nt, a_ptr, b_ptr, c_ptr, 16, blocks, batch_dim, ctx_blks_, ctx_blks_, heads_,
+                                        head_state_, lut_heads, blocks);
+    if (cudaDeviceSynchronize() != cudaSuccess || !ok || !rejected) {
+        printf("FAIL: call failed (%s)\n", sfb_last_error());
+        return 1;
+    }
+
+    std::vector<bhalf> s_h(n_blk);
+    std::vector<float> y_h(n_blk), o_h(n_in), o2_h(n_in);
+    cudaMemcpy(s_h.data(), c_ptr, sizeof(bhalf) * n_blk, cudaMemcpyDeviceToHost);
+    cudaMemcpy(y_h.data(), y_ptr, sizeof(float) * n_blk, cudaMemcpyDeviceToHost);
+    cudaMemcpy(o_h.data(), o_ptr, sizeof(float) * n_in, cudaMemcpyDeviceToHost);
+    cudaMemcpy(o2_h.data(), o2_ptr, sizeof(float) * n_in, cudaMemcpyDeviceToHost);
+    size_t bad = 0;
+    for (size_t i = 0; i < n_blk; i++) bad += bf(s_h[i].x) != (float)head_state_;
+    for (uint bh = 0; bh < batch_dim * heads_; bh++)
+        for (uint k = 0; k < blocks; k++)
+            for (uint r = 0; r < blk_size_; r++) {
+                const uint kept = nt[k].x * blk_size_ + r + 1;   // causal: keys 0 .. row
+                for (uint c = 0; c < blk_size_; c++) {
+                    const bool keep = nt[k].x != nt[k].y || r >= c;
+                    const float want = keep ? 1.0f / kept : 0.0f;
+                    const float got = y_h[(((size_t)bh * blocks + k) * blk_size_ + r) * blk_size_ + c];
+                    bad += fabsf(got - want) > 1e-6f;
+                }
+            }
+    for (size_t i = 0; i < n_in; i++) bad += fabsf(o_h[i] - 1.0f) > 1e-2f;   // bf16 probabilities on this path
+    for (size_t i = 0; i < n_in; i++) bad += fabsf(o2_h[i] - 1.0f) > 1e-5f;
+    printf(bad ? "FAIL: %zu wrong values\n" : "PASS\n", bad);
+    return bad ? 1 : 0;
+}
