@@ -14,7 +14,7 @@ struct AttnDims {
 int simt_sddmm_nt(cudaStream_t s, const void *lut, const void *a, const void *b, void *c, int ab_dtype, int c_dtype,
                   uint32_t bs, const AttnDims &p);
 int simt_softmax(cudaStream_t s, const void *lut, const void *mask, const void *x, void *y, int x_dtype, int y_dtype,
-                 uint32_t bs, const AttnDims &p, float scale);
+                 uint32_t bs, const AttnDims &p, float scale, uint32_t max_lut);
 int simt_spmm_nn(cudaStream_t s, const void *lut, const void *a, const void *b, void *c, int a_dtype, int bc_dtype,
                  uint32_t bs, const AttnDims &p);
 int simt_fused_sddmm_softmax(cudaStream_t s, const void *nn_lut, const void *a, const void *b, const void *mask, void *y,

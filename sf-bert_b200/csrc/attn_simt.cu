@@ -81,35 +81,6 @@ __global__ void __launch_bounds__(256) sddmm_nt_kernel(const uint2 *__restrict__
 }
 
 // ------------------------------------------------------------------------------------------------
-// Masked softmax: one CTA per block-row.  A lane owns 8 consecutive keys of one query row of one
-// block (16 bytes of bf16), so a warp reads 512 contiguous bytes per block; the lanes of a row
-// (BS/8 of them) combine with shuffles.  Pass 1 keeps a running max / sum over the row's blocks,
-// pass 2 re-reads the scores (L2 hits) and writes the probabilities.
-template <int X_DT>
-__device__ __forceinline__ void load8(float (&v)[8], const void *x, size_t idx)
-{
-    if (X_DT == SFB_F32) {
-        const float4 *p = (const float4 *)((const float *)x + idx);
-        float4 a = __ldg(p), b = __ldg(p + 1);
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    } else {
-        uint4 u = __ldg((const uint4 *)((const uint16_t *)x + idx));
-        uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            if (X_DT == SFB_BF16) {
-                v[2 * i] = __uint_as_float(w[i] << 16);
-                v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-            } else {
-                __half2 hh = *reinterpret_cast<__half2 *>(&w[i]);
-                float2 f = __half22float2(hh);
-                v[2 * i] = f.x;
-                v[2 * i + 1] = f.y;
-            }
-        }
-    }
-}
-
 template <int Y_DT>
 __device__ __forceinline__ void store8(void *y, size_t idx, const float (&v)[8])
 {
@@ -132,7 +103,63 @@ __device__ __forceinline__ void store8(void *y, size_t idx, const float (&v)[8])
     }
 }
 
-template <int BS, int X_DT, int Y_DT>
+// raw 16-byte (16-bit types) or 32-byte (fp32) load of 8 scores, kept unconverted so that many can be in flight
+template <int X_DT> struct Raw8 { uint4 a; };
+template <> struct Raw8<SFB_F32> { uint4 a, b; };
+
+template <int X_DT>
+__device__ __forceinline__ Raw8<X_DT> load_raw8(const void *x, size_t idx)
+{
+    Raw8<X_DT> r;
+    if (X_DT == SFB_F32) {
+        const uint4 *p = (const uint4 *)((const float *)x + idx);
+        r.a = __ldg(p);
+        ((Raw8<SFB_F32> &)r).b = __ldg(p + 1);
+    } else {
+        r.a = __ldg((const uint4 *)((const uint16_t *)x + idx));
+    }
+    return r;
+}
+
+template <int X_DT>
+__device__ __forceinline__ void unpack8(float (&v)[8], const Raw8<X_DT> &r)
+{
+    if (X_DT == SFB_F32) {
+        const Raw8<SFB_F32> &q = (const Raw8<SFB_F32> &)r;
+        v[0] = __uint_as_float(q.a.x); v[1] = __uint_as_float(q.a.y); v[2] = __uint_as_float(q.a.z); v[3] = __uint_as_float(q.a.w);
+        v[4] = __uint_as_float(q.b.x); v[5] = __uint_as_float(q.b.y); v[6] = __uint_as_float(q.b.z); v[7] = __uint_as_float(q.b.w);
+    } else {
+        const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (X_DT == SFB_BF16) {
+                v[2 * i] = __uint_as_float(w[i] << 16);
+                v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            } else {
+                float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+                v[2 * i] = f.x;
+                v[2 * i + 1] = f.y;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ float ex2_fast(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Masked softmax: one CTA per block-row.  A lane owns 8 consecutive keys of one query row of one block
+// (16 bytes of bf16), so a warp reads 512 contiguous bytes per block; the lanes of a row (BS/8 of them)
+// combine with shuffles.
+//
+// NB > 0: the row has at most NB blocks.  All of them are loaded up front (NB independent 16-byte loads per
+// lane in flight) and stay in registers: one pass over HBM, one exponential per element.
+// NB == 0: rows of any length.  Pass 1 finds the row maximum, pass 2 the sum of exponentials, pass 3 writes;
+// passes 2 and 3 re-read scores this CTA has just pulled through L2.
+template <int BS, int X_DT, int Y_DT, int NB>
 __global__ void __launch_bounds__(BS * BS / 8) softmax_kernel(const uint2 *__restrict__ lut,
                                                         const typename MaskWord<BS>::type *__restrict__ mask,
                                                         const void *__restrict__ X, void *__restrict__ Y, AttnDims p,
@@ -150,46 +177,97 @@ __global__ void __launch_bounds__(BS * BS / 8) softmax_kernel(const uint2 *__res
     const size_t base = ((size_t)b * p.H + h) * p.blocks * BS * BS + (size_t)r * BS + c0;
     const W *mrow = mask ? mask + (size_t)h * p.mask_stride + (size_t)r * p.blocks : nullptr;
 
-    float mx = -INFINITY, sum = 0.f;
-    for (uint32_t e = 0; e < cnt; e++) {
-        const uint32_t blk = nn[off + e].x;
-        float v[8];
-        load8<X_DT>(v, X, base + (size_t)blk * BS * BS);
-        uint32_t bits = 0xffu;
-        if (mrow) bits = (uint32_t)((__ldg(mrow + blk) >> c0) & 0xffu);
-        float bm = -INFINITY;
+    if (NB > 0) {
+        constexpr int N = NB > 0 ? NB : 1;
+        Raw8<X_DT> raw[N];
+        uint32_t blks[N], bits[N];
 #pragma unroll
-        for (int t = 0; t < 8; t++) {
-            v[t] = ((bits >> t) & 1u) ? v[t] * scale_log2e : -INFINITY;
-            bm = fmaxf(bm, v[t]);
+        for (int j = 0; j < N; j++) {
+            blks[j] = 0;
+            bits[j] = 0;
+            if (j < (int)cnt) {
+                blks[j] = nn[off + j].x;
+                raw[j] = load_raw8<X_DT>(X, base + (size_t)blks[j] * BS * BS);
+                bits[j] = mrow ? (uint32_t)((__ldg(mrow + blks[j]) >> c0) & 0xffu) : 0xffu;
+            }
         }
-        if (bm > mx) {
-            sum *= exp2f(mx - bm);  // exp2f(-inf) = 0 on the first kept element
-            mx = bm;
-        }
-        if (mx > -INFINITY) {
+        float mx = -INFINITY;
 #pragma unroll
-            for (int t = 0; t < 8; t++) sum += exp2f(v[t] - mx);
+        for (int j = 0; j < N; j++) {
+            if (j < (int)cnt) {
+                float v[8];
+                unpack8<X_DT>(v, raw[j]);
+#pragma unroll
+                for (int t = 0; t < 8; t++)
+                    if ((bits[j] >> t) & 1u) mx = fmaxf(mx, v[t]);
+            }
         }
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float mxs = mx > -INFINITY ? mx * scale_log2e : 0.f;
+        // second sweep over the registers: exponentials (kept packed as bf16 pairs would lose bits: keep fp32 of
+        // one block at a time and recompute in the third sweep instead -- an exponential is cheaper than 8 registers)
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < N; j++) {
+            if (j < (int)cnt) {
+                float v[8];
+                unpack8<X_DT>(v, raw[j]);
+#pragma unroll
+                for (int t = 0; t < 8; t++)
+                    if ((bits[j] >> t) & 1u) sum += ex2_fast(fmaf(v[t], scale_log2e, -mxs));
+            }
+        }
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float inv = sum > 0.f ? 1.f / sum : 0.f;
+#pragma unroll
+        for (int j = 0; j < N; j++) {
+            if (j < (int)cnt) {
+                float v[8];
+                unpack8<X_DT>(v, raw[j]);
+#pragma unroll
+                for (int t = 0; t < 8; t++)
+                    v[t] = ((bits[j] >> t) & 1u) ? ex2_fast(fmaf(v[t], scale_log2e, -mxs)) * inv : 0.f;
+                store8<Y_DT>(Y, base + (size_t)blks[j] * BS * BS, v);
+            }
+        }
+        return;
     }
-    // combine the lanes of one query row
-    float rmx = mx;
-#pragma unroll
-    for (int o = LPR / 2; o > 0; o >>= 1) rmx = fmaxf(rmx, __shfl_xor_sync(0xffffffffu, rmx, o));
-    float rsum = (mx > -INFINITY) ? sum * exp2f(mx - rmx) : 0.f;
-#pragma unroll
-    for (int o = LPR / 2; o > 0; o >>= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, o);
-    const float inv = rsum > 0.f ? 1.f / rsum : 0.f;
 
+    float mx = -INFINITY;
     for (uint32_t e = 0; e < cnt; e++) {
         const uint32_t blk = nn[off + e].x;
         float v[8];
-        load8<X_DT>(v, X, base + (size_t)blk * BS * BS);
-        uint32_t bits = 0xffu;
-        if (mrow) bits = (uint32_t)((__ldg(mrow + blk) >> c0) & 0xffu);
+        unpack8<X_DT>(v, load_raw8<X_DT>(X, base + (size_t)blk * BS * BS));
+        const uint32_t bits = mrow ? (uint32_t)((__ldg(mrow + blk) >> c0) & 0xffu) : 0xffu;
 #pragma unroll
         for (int t = 0; t < 8; t++)
-            v[t] = (((bits >> t) & 1u) && inv > 0.f) ? exp2f(v[t] * scale_log2e - rmx) * inv : 0.f;
+            if ((bits >> t) & 1u) mx = fmaxf(mx, v[t]);
+    }
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float mxs = mx > -INFINITY ? mx * scale_log2e : 0.f;
+    float sum = 0.f;
+    for (uint32_t e = 0; e < cnt; e++) {
+        const uint32_t blk = nn[off + e].x;
+        float v[8];
+        unpack8<X_DT>(v, load_raw8<X_DT>(X, base + (size_t)blk * BS * BS));
+        const uint32_t bits = mrow ? (uint32_t)((__ldg(mrow + blk) >> c0) & 0xffu) : 0xffu;
+#pragma unroll
+        for (int t = 0; t < 8; t++)
+            if ((bits >> t) & 1u) sum += ex2_fast(fmaf(v[t], scale_log2e, -mxs));
+    }
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = sum > 0.f ? 1.f / sum : 0.f;
+    for (uint32_t e = 0; e < cnt; e++) {
+        const uint32_t blk = nn[off + e].x;
+        float v[8];
+        unpack8<X_DT>(v, load_raw8<X_DT>(X, base + (size_t)blk * BS * BS));
+        const uint32_t bits = mrow ? (uint32_t)((__ldg(mrow + blk) >> c0) & 0xffu) : 0xffu;
+#pragma unroll
+        for (int t = 0; t < 8; t++) v[t] = ((bits >> t) & 1u) ? ex2_fast(fmaf(v[t], scale_log2e, -mxs)) * inv : 0.f;
         store8<Y_DT>(Y, base + (size_t)blk * BS * BS, v);
     }
 }
@@ -495,18 +573,23 @@ int simt_sddmm_nt(cudaStream_t s, const void *lut, const void *a, const void *b,
 }
 
 int simt_softmax(cudaStream_t s, const void *lut, const void *mask, const void *x, void *y, int x_dtype, int y_dtype,
-                 uint32_t bs, const AttnDims &p, float scale)
+                 uint32_t bs, const AttnDims &p, float scale, uint32_t max_lut)
 {
     dim3 grid(p.nb_a, p.B, p.H);
     const float sl = scale * LOG2E_F;
+    // rows of up to 16 blocks (the caller's max_lut says so) stay in registers; 0 = unknown, stream
+    // (only when the longest row nearly fills the register tile: measured slower than streaming otherwise)
+    const int nb = (max_lut >= 3 && max_lut <= 4) ? 4 : (max_lut >= 7 && max_lut <= 8) ? 8 : (max_lut >= 14 && max_lut <= 16) ? 16 : 0;
+#define SM_LAUNCH(XD, NBV) \
+    DISPATCH_DT(y_dtype, YD, { softmax_kernel<BS, XD, YD, NBV><<<grid, BS * BS / 8, 0, s>>>((const uint2 *)lut, (const W *)mask, x, y, p, sl); })
+#define SM_BY_NB(XD) \
+    if (nb == 4) { SM_LAUNCH(XD, 4) } else if (nb == 8) { SM_LAUNCH(XD, 8) } else if (nb == 16) { SM_LAUNCH(XD, 16) } else { SM_LAUNCH(XD, 0) }
     DISPATCH_BS(bs, {
         typedef typename MaskWord<BS>::type W;
-        if (x_dtype == SFB_BF16) {
-            DISPATCH_DT(y_dtype, YD, { softmax_kernel<BS, SFB_BF16, YD><<<grid, BS * BS / 8, 0, s>>>((const uint2 *)lut, (const W *)mask, x, y, p, sl); })
-        } else {
-            DISPATCH_DT(y_dtype, YD, { softmax_kernel<BS, SFB_F32, YD><<<grid, BS * BS / 8, 0, s>>>((const uint2 *)lut, (const W *)mask, x, y, p, sl); })
-        }
+        if (x_dtype == SFB_BF16) { SM_BY_NB(SFB_BF16) } else { SM_BY_NB(SFB_F32) }
     })
+#undef SM_BY_NB
+#undef SM_LAUNCH
     return check_launch("sfb_masked_softmax");
 }
 

@@ -76,8 +76,9 @@ __global__ void __launch_bounds__(256) bias_residual_layernorm_kernel(void *__re
 {
     constexpr int N = Vec8<DT>::N;
     const uint32_t lane = threadIdx.x & 31;
-    const uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= m) return;
+    const uint32_t warps = gridDim.x * (blockDim.x >> 5);
+    // a fixed grid of warps strides over the rows
+    for (uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < m; row += warps) {
     const size_t base = (size_t)row * hidden;
     float v[CHUNKS][N];
     float s = 0.f, s2 = 0.f;
@@ -133,6 +134,7 @@ __global__ void __launch_bounds__(256) bias_residual_layernorm_kernel(void *__re
             Vec8<DT>::store(out, base + col, y);
         }
     }
+    }
 }
 
 template <int DT>
@@ -143,7 +145,10 @@ static int launch_ln(cudaStream_t s, void *out, void *sum_out, float *mean, floa
     const uint32_t per_chunk = 32 * N;
     const uint32_t chunks = (hidden + per_chunk - 1) / per_chunk;
     const uint32_t rows_per_cta = 8;
-    dim3 grid((m + rows_per_cta - 1) / rows_per_cta);
+    // at most 16 CTAs per SM's worth of warps; the warps loop over the remaining rows
+    uint32_t ctas = (m + rows_per_cta - 1) / rows_per_cta;
+    if (ctas > 148 * 16) ctas = 148 * 16;
+    dim3 grid(ctas);
 #define LN_CASE(C)                                                                                                   \
     bias_residual_layernorm_kernel<DT, C><<<grid, 32 * rows_per_cta, 0, s>>>(out, sum_out, mean, rstd, x, bias, resid, \
                                                                              gain, beta, m, hidden)

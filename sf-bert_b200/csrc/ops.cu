@@ -35,7 +35,6 @@ extern "C" int sfb_masked_softmax(sfb_stream_t stream, const void *lut, const vo
                                   float scale)
 {
     const char *who = "sfb_masked_softmax";
-    (void)max_lut;  // the reference sizes its CTA from it (blocksparse.h:665-680); rows of any length are handled here
     SFB_REQUIRE(lut && x && y, "%s: NULL pointer", who);
     SFB_REQUIRE(x_dtype == SFB_BF16 || x_dtype == SFB_F32, "%s: x must be bf16 or fp32", who);
     SFB_REQUIRE(valid_dtype(y_dtype), "%s: unknown y dtype", who);
@@ -46,7 +45,9 @@ extern "C" int sfb_masked_softmax(sfb_stream_t stream, const void *lut, const vo
     if (blocks == 0 || ctx_blks == 0) { clear_error(); return 0; }
     AttnDims p = {batch_dim, head_dim, 0, ctx_blks, ctx_blks, blocks, lut_heads > 1 ? lut_dim : 0,
                   mask_heads > 1 ? blocks * block_size : 0};
-    return simt_softmax(as_stream(stream), lut, mask, x, y, x_dtype, y_dtype, block_size, p, scale);
+    // max_lut (the reference sizes its CTA from it, blocksparse.h:665-680) picks the register-resident variant;
+    // a value smaller than the longest row would drop blocks, so 0 (= unknown) is always safe
+    return simt_softmax(as_stream(stream), lut, mask, x, y, x_dtype, y_dtype, block_size, p, scale, max_lut);
 }
 
 extern "C" int sfb_bst_sgemm_xn(sfb_stream_t stream, const void *lut, const void *a, const void *b, void *c, int a_dtype,
