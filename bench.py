@@ -43,6 +43,11 @@ CONFIGS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the fused kernel, from the ncu capture
+# summarised in profiles/fused_attention_tc_stride_bertbase.md (not measured by this script)
+NCU_TRAFFIC_BYTES = {"stride_bertbase": 182.8e6}
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -211,7 +216,8 @@ def run_ours(args):
                        "layout": cfg["layout"][0], "nnz_blocks_per_head": lay.blocks, "max_row": lay.nn_max,
                        "sharding": "batch x head, no collective on the data path", "l2": "flushed between timed steps"},
             "roofline": {"bound": "tensor", "achieved": round(per_gpu, 3), "peak": pk["tensor"], "unit": "TFLOP/s",
-                         "frac": round(per_gpu / pk["tensor"], 4), "traffic": None, "peak_source": pk["source"] + " burst bf16",
+                         "frac": round(per_gpu / pk["tensor"], 4), "traffic": NCU_TRAFFIC_BYTES.get(args.config),
+                         "peak_source": pk["source"] + " burst bf16",
                          "frac_of_sustained": round(per_gpu / pk["tensor_sustained"], 4),
                          "min_hbm_bytes": 4 * B * L * H * d * esz,
                          "kernel": "fused_attention_tc_kernel" if cfg["dtype"] != "f32" else "fused_attention_kernel"},

@@ -93,7 +93,10 @@ __device__ __forceinline__ void store8(void *y, size_t idx, const float (&v)[8])
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             if (Y_DT == SFB_BF16) {
-                w[i] = (uint32_t)to_bhalf_bits(v[2 * i]) | ((uint32_t)to_bhalf_bits(v[2 * i + 1]) << 16);
+                // probabilities: the hardware's round-to-nearest-even pack (one instruction per pair); it differs
+                // from the reference's add-half-and-truncate rounding (ew_op_gpu.h:241-253) on exact ties only
+                __nv_bfloat162 hb = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                w[i] = *reinterpret_cast<uint32_t *>(&hb);
             } else {
                 __half2 hh = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
                 w[i] = *reinterpret_cast<uint32_t *>(&hh);
@@ -205,8 +208,8 @@ __global__ void __launch_bounds__(BS * BS / 8) softmax_kernel(const uint2 *__res
 #pragma unroll
         for (int o = LPR / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         const float mxs = mx > -INFINITY ? mx * scale_log2e : 0.f;
-        // second sweep over the registers: exponentials (kept packed as bf16 pairs would lose bits: keep fp32 of
-        // one block at a time and recompute in the third sweep instead -- an exponential is cheaper than 8 registers)
+        // second sweep: one exponential per score; the results replace the raw scores in their registers as
+        // packed fp16 pairs (e is in (0, 1], 11 bits are more than the 16-bit output keeps)
         float sum = 0.f;
 #pragma unroll
         for (int j = 0; j < N; j++) {
@@ -214,8 +217,16 @@ __global__ void __launch_bounds__(BS * BS / 8) softmax_kernel(const uint2 *__res
                 float v[8];
                 unpack8<X_DT>(v, raw[j]);
 #pragma unroll
-                for (int t = 0; t < 8; t++)
-                    if ((bits[j] >> t) & 1u) sum += ex2_fast(fmaf(v[t], scale_log2e, -mxs));
+                for (int t = 0; t < 8; t++) {
+                    v[t] = ((bits[j] >> t) & 1u) ? ex2_fast(fmaf(v[t], scale_log2e, -mxs)) : 0.f;
+                    sum += v[t];
+                }
+                if (Y_DT != SFB_F32) {   // fp32 outputs recompute the exponential below instead: fp16 would cost them bits
+                    __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+                    __half2 h2 = __floats2half2_rn(v[4], v[5]), h3 = __floats2half2_rn(v[6], v[7]);
+                    raw[j].a = make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
+                                          *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
+                }
             }
         }
 #pragma unroll
@@ -225,10 +236,20 @@ __global__ void __launch_bounds__(BS * BS / 8) softmax_kernel(const uint2 *__res
         for (int j = 0; j < N; j++) {
             if (j < (int)cnt) {
                 float v[8];
-                unpack8<X_DT>(v, raw[j]);
+                if (Y_DT != SFB_F32) {
+                    const uint32_t w[4] = {raw[j].a.x, raw[j].a.y, raw[j].a.z, raw[j].a.w};
 #pragma unroll
-                for (int t = 0; t < 8; t++)
-                    v[t] = ((bits[j] >> t) & 1u) ? ex2_fast(fmaf(v[t], scale_log2e, -mxs)) * inv : 0.f;
+                    for (int t = 0; t < 4; t++) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[t]));
+                        v[2 * t] = f.x * inv;
+                        v[2 * t + 1] = f.y * inv;
+                    }
+                } else {
+                    unpack8<X_DT>(v, raw[j]);
+#pragma unroll
+                    for (int t = 0; t < 8; t++)
+                        v[t] = ((bits[j] >> t) & 1u) ? ex2_fast(fmaf(v[t], scale_log2e, -mxs)) * inv : 0.f;
+                }
                 store8<Y_DT>(Y, base + (size_t)blks[j] * BS * BS, v);
             }
         }

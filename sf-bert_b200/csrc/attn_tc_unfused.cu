@@ -1,0 +1,365 @@
+// The unfused operators on the tensor cores (tcgen05) for 16-bit operands, block_size 64, head size 64:
+//   sddmm_tc_kernel   S(block) = Q_i . K_j^T for every kept block          (bst_sgemm_nt,  blocksparse.h:425)
+//   spmm_tc_kernel    O_i = sum over the row's blocks of P(block) . V_j     (bst_sgemm_xn,  blocksparse.h:965)
+// Same tiling as the fused kernel: a CTA owns a pair of adjacent block-rows (128 queries, one M=128 MMA
+// tile) and walks the union of their key blocks; operands arrive by TMA into 128-byte-swizzled shared
+// memory, accumulators live in TMEM.  Both operators are HBM-bound (8 KB of S or P per 1 MFLOP), so the
+// point of the tensor cores here is to get the arithmetic out of the way of the memory system.
+#include "tc_common.cuh"
+
+namespace sfb {
+namespace tc {
+
+constexpr int kUStages = 4;
+
+struct UShared {
+    uint64_t q_full, in_full[kUStages], in_empty[kUStages], s_full[2], s_empty[2], o_final, drained;
+    uint32_t tmem_base, n_union, abort_flag, pad;
+    UnionEntry entries[kMaxUnion];
+    uint8_t found[kMaxUnion];
+};
+
+struct UParams {
+    const uint2 *nn_lut;
+    void *out;                 // S blocks (sddmm) or O (spmm)
+    uint32_t B, H, nb, blocks, lut_stride;
+    int out_dtype;             // SFB_F32 / SFB_BF16 / SFB_F16
+    int is_bf16;               // operand format
+    uint32_t p_rows;           // spmm: rows of the 2-D view of P (= B*H*blocks*64); a coordinate beyond it reads zeros
+};
+
+constexpr size_t kSddmmSmem = 1024 + kUStages * 2 * kTileBytes + sizeof(UShared);
+constexpr size_t kSpmmSmem = 1024 + kUStages * (kQBytes + kTileBytes) + sizeof(UShared);
+
+__device__ __forceinline__ void store_row16(void *dst_base, size_t elem_off, const uint32_t (&v)[16], int out_dtype, int c0)
+{
+    // 16 consecutive fp32 accumulator values of one row -> the output type
+    if (out_dtype == SFB_F32) {
+        float4 *d = (float4 *)((float *)dst_base + elem_off + c0);
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            d[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                               __uint_as_float(v[4 * j + 3]));
+    } else {
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) w[j] = pack2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), out_dtype == SFB_BF16);
+        uint4 *d = (uint4 *)((uint16_t *)dst_base + elem_off + c0);
+        d[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        d[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+}
+
+// ---- SDDMM ----------------------------------------------------------------------------------------
+// The operator only receives the nt_lut (one (row, column) pair per kept block, in any order), so a CTA takes
+// a run of kChunk consecutive blocks.  Per block one stage holds the 64 query rows followed by the 64 key rows;
+// the M=128 MMA reads the stage as its A operand, so accumulator lanes 0-63 hold Q.K^T and lanes 64-127 a
+// by-product (K.K^T) that is never read -- the operator is bound by the 8 KB of S it writes per block, not by
+// tensor work.  warp 0: TMA; warp 1: MMA; warps 4-5: TMEM lanes 0-63 -> global, one score row per thread.
+constexpr uint32_t kChunk = 32;
+
+__global__ void __launch_bounds__(192, 2)
+sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap, const UParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *tiles = smem;                                   // stage s: Q rows (8 KB) then K rows (8 KB)
+    UShared *st = (UShared *)(tiles + kUStages * 2 * kTileBytes);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t b = blockIdx.y, h = blockIdx.z;
+    const uint32_t k0 = blockIdx.x * kChunk;
+    const uint32_t T = min(kChunk, p.blocks - k0);
+    const uint32_t L = p.nb * 64;
+    const uint2 *lut = p.nn_lut + (size_t)h * p.lut_stride + k0;   // here: the nt_lut
+    volatile uint32_t *abort_flag = &st->abort_flag;
+    const uint32_t fmt = p.is_bf16 ? 1u : 0u;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kUStages; s++) { mbar_init(&st->in_full[s], 1); mbar_init(&st->in_empty[s], 1); }
+        for (int s = 0; s < 2; s++) { mbar_init(&st->s_full[s], 1); mbar_init(&st->s_empty[s], 64); }
+        mbar_init(&st->drained, 1);
+        st->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&st->tmem_base)), "r"(128u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem = st->tmem_base;
+    const int32_t xq = (int32_t)(h * 64);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (uint32_t t = 0; t < T; t++) {
+                const uint32_t s = t % kUStages;
+                if (t >= kUStages && !mbar_wait(&st->in_empty[s], ((t / kUStages) - 1) & 1, abort_flag, 21)) break;
+                const uint2 ent = lut[t];
+                if (ent.x >= p.nb || ent.y >= p.nb) {   // a LUT entry outside the block grid: report, do not fetch
+                    st->abort_flag = 1;
+                    atomicCAS(&g_status, 0u, (20u << 24) | (blockIdx.x & 0xffffffu));
+                    break;
+                }
+                mbar_expect_tx(&st->in_full[s], 2 * kTileBytes);
+                tma_load_2d(smem_u32(tiles + s * 2 * kTileBytes), &qmap, &st->in_full[s], xq, (int32_t)(b * L + ent.x * 64));
+                tma_load_2d(smem_u32(tiles + s * 2 * kTileBytes + kTileBytes), &kmap, &st->in_full[s], xq, (int32_t)(b * L + ent.y * 64));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(fmt, fmt, 128, 64, 0);
+            for (uint32_t t = 0; t < T; t++) {
+                const uint32_t s = t % kUStages;
+                if (!mbar_wait(&st->in_full[s], (t / kUStages) & 1, abort_flag, 23)) break;
+                if (t >= 2 && !mbar_wait(&st->s_empty[t & 1], ((t >> 1) - 1) & 1, abort_flag, 24)) break;
+                tcgen05_fence_after();
+                const uint64_t a_desc = smem_desc_sw128(smem_u32(tiles + s * 2 * kTileBytes));
+                const uint64_t b_desc = smem_desc_sw128(smem_u32(tiles + s * 2 * kTileBytes + kTileBytes));
+#pragma unroll
+                for (uint32_t kk = 0; kk < 4; kk++) umma_f16(tmem + 64 * (t & 1), a_desc + 2 * kk, b_desc + 2 * kk, idesc, kk);
+                umma_commit(&st->s_full[t & 1]);
+                umma_commit(&st->in_empty[s]);
+            }
+        }
+    } else if (warp >= 4) {
+        const uint32_t quarter = warp & 3;                 // 0 and 1: TMEM lanes 0-63
+        const uint32_t r = quarter * 32 + lane;
+        const uint32_t lane_field = (quarter * 32) << 16;
+        for (uint32_t t = 0; t < T; t++) {
+            if (!mbar_wait_warp(&st->s_full[t & 1], (t >> 1) & 1, abort_flag, 25)) break;
+            tcgen05_fence_after();
+            const size_t off = ((((size_t)b * p.H + h) * p.blocks + k0 + t) * 64 + r) * 64;
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) {
+                uint32_t v[16];
+                TMEM_LD_16((v), tmem + 64 * (t & 1) + lane_field + c0);
+                tmem_wait_ld();
+                store_row16(p.out, off, v, p.out_dtype, c0);
+            }
+            tcgen05_fence_before();
+            mbar_arrive(&st->s_empty[t & 1]);
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (st->abort_flag) {
+        if (warp == 1 && lane == 0) {
+            umma_commit(&st->drained);
+            for (uint32_t i = 0; i < kWaitLimit && !mbar_try_wait(&st->drained, 0); i++) {}
+        }
+        if (warp == 0 && lane == 0) {
+            const uint64_t t0 = clock64();
+            while (clock64() - t0 < 2000000ull) {}
+        }
+        __syncthreads();
+    }
+    if (warp == 0) {
+        __syncwarp();
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(128u) : "memory");
+    }
+}
+
+// ---- SpMM -----------------------------------------------------------------------------------------
+// warp 0: TMA (per key block: the two 64-row halves of the P tile -- a half whose block-row does not keep the
+// block is fetched from beyond the tensor and arrives as zeros -- and the V tile); warp 1: MMA; warps 2-5: epilogue
+__global__ void __launch_bounds__(192, 2)
+spmm_tc_kernel(const __grid_constant__ CUtensorMap pmap, const __grid_constant__ CUtensorMap vmap, const UParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *tiles = smem;                                   // stage s: P (16 KB) then V (8 KB)
+    constexpr uint32_t kStageBytes = kQBytes + kTileBytes;
+    UShared *st = (UShared *)(tiles + kUStages * kStageBytes);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t pair = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
+    const bool has_row1 = pair * 2 + 1 < p.nb;
+    const uint32_t L = p.nb * 64;
+    const uint2 *nn = p.nn_lut + (size_t)h * p.lut_stride;
+    volatile uint32_t *abort_flag = &st->abort_flag;
+    const uint32_t fmt = p.is_bf16 ? 1u : 0u;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kUStages; s++) { mbar_init(&st->in_full[s], 1); mbar_init(&st->in_empty[s], 1); }
+        mbar_init(&st->o_final, 1);
+        mbar_init(&st->drained, 1);
+        st->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    build_union(nn, pair, p.nb, st->entries, st->found, &st->n_union, &st->abort_flag);
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&st->tmem_base)), "r"(64u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+
+    const uint32_t T = st->n_union;
+    const uint32_t tmem = st->tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0 && T > 0) {
+            const uint32_t bh_rows = ((b * p.H + h) * p.blocks) * 64;    // first row of this (b,h) in the 2-D view of P
+            for (uint32_t t = 0; t < T; t++) {
+                const uint32_t s = t % kUStages;
+                if (t >= kUStages && !mbar_wait(&st->in_empty[s], ((t / kUStages) - 1) & 1, abort_flag, 31)) break;
+                const UnionEntry ent = st->entries[t];
+                uint8_t *ptile = tiles + s * kStageBytes;
+                mbar_expect_tx(&st->in_full[s], kStageBytes);
+                const int32_t y0 = (ent.flags & 1) ? (int32_t)(bh_rows + ent.blk[0] * 64) : (int32_t)p.p_rows;
+                const int32_t y1 = (ent.flags & 2) ? (int32_t)(bh_rows + ent.blk[1] * 64) : (int32_t)p.p_rows;
+                tma_load_2d(smem_u32(ptile), &pmap, &st->in_full[s], 0, y0);
+                tma_load_2d(smem_u32(ptile + kTileBytes), &pmap, &st->in_full[s], 0, y1);
+                tma_load_2d(smem_u32(ptile + kQBytes), &vmap, &st->in_full[s], (int32_t)(h * 64), (int32_t)(b * L + ent.col * 64));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && T > 0) {
+            const uint32_t idesc = instr_desc(fmt, fmt, 128, 64, 1);
+            for (uint32_t t = 0; t < T; t++) {
+                const uint32_t s = t % kUStages;
+                if (!mbar_wait(&st->in_full[s], (t / kUStages) & 1, abort_flag, 33)) break;
+                tcgen05_fence_after();
+                const uint64_t p_desc = smem_desc_sw128(smem_u32(tiles + s * kStageBytes));
+                const uint64_t v_desc = smem_desc_sw128(smem_u32(tiles + s * kStageBytes + kQBytes));
+#pragma unroll
+                for (uint32_t kk = 0; kk < 4; kk++) umma_f16(tmem, p_desc + 2 * kk, v_desc + 128 * kk, idesc, (t | kk) ? 1u : 0u);
+                umma_commit(&st->in_empty[s]);
+                if (t + 1 == T) umma_commit(&st->o_final);
+            }
+        }
+    } else {
+        const uint32_t quarter = warp & 3;
+        const uint32_t r = quarter * 32 + lane;
+        const uint32_t lane_field = (quarter * 32) << 16;
+        const bool row_valid = (r >> 6) == 0 || has_row1;
+        bool alive = true;
+        if (T > 0) alive = mbar_wait_warp(&st->o_final, 0, abort_flag, 35);
+        if (alive) {
+            tcgen05_fence_after();
+            const size_t off = ((size_t)b * L + (size_t)pair * 128 + r) * ((size_t)p.H * 64) + (size_t)h * 64;
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) {
+                uint32_t v[16];
+                if (T > 0) {
+                    TMEM_LD_16((v), tmem + lane_field + c0);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = 0u;    // rows without blocks are written as zeros (blocksparse.h:949-962)
+                }
+                if (row_valid) store_row16(p.out, off, v, p.out_dtype, c0);
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (st->abort_flag) {
+        if (warp == 1 && lane == 0) {
+            umma_commit(&st->drained);
+            for (uint32_t i = 0; i < kWaitLimit && !mbar_try_wait(&st->drained, 0); i++) {}
+        }
+        if (warp == 0 && lane == 0) {
+            const uint64_t t0 = clock64();
+            while (clock64() - t0 < 2000000ull) {}
+        }
+        __syncthreads();
+    }
+    if (warp == 0) {
+        __syncwarp();
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(64u) : "memory");
+    }
+}
+
+// P viewed as [rows, 64] 16-bit row-major, boxes of 64 x 64, 128-byte swizzle, zero fill outside
+static int make_p_map(CUtensorMap *map, const void *base, uint64_t rows, int is_bf16)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail("cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {64, rows};
+    cuuint64_t strides[1] = {128};
+    cuuint32_t box[2] = {64, 64};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)base, dims,
+                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+}  // namespace tc
+
+static bool tc_shape_ok(uint32_t bs, const AttnDims &p, uint32_t max_lut)
+{
+    return bs == 64 && p.d == 64 && p.nb_a == p.nb_b && max_lut != 0 && 2 * (uint64_t)max_lut <= tc::kMaxUnion &&
+           (uint64_t)p.B * p.nb_a * 64 < (1ull << 31) && (uint64_t)p.B * p.H * p.blocks * 64 < (1ull << 31) - 64;
+}
+
+bool tc_sddmm_supported(int ab_dtype, uint32_t bs, const AttnDims &p)
+{
+    return (ab_dtype == SFB_BF16 || ab_dtype == SFB_F16) && bs == 64 && p.d == 64 && p.blocks > 0 &&
+           (uint64_t)p.B * (p.nb_a > p.nb_b ? p.nb_a : p.nb_b) * 64 < (1ull << 31);
+}
+
+int tc_sddmm(cudaStream_t s, const void *nt_lut, const void *a, const void *b, void *c, int ab_dtype, int c_dtype, const AttnDims &p)
+{
+    using namespace tc;
+    SFB_REQUIRE((((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) == 0, "sfb_bst_sgemm_nt: a, b, c must be 16-byte aligned");
+    SFB_REQUIRE(p.nb_a == p.nb_b, "sfb_bst_sgemm_nt: ctx_blks_a != ctx_blks_b is not supported for 16-bit operands");
+    const int is_bf16 = ab_dtype == SFB_BF16;
+    const uint64_t rows = (uint64_t)p.B * p.nb_a * 64;
+    CUtensorMap qm, km;
+    if (make_map(&qm, a, rows, p.H, is_bf16, 64) || make_map(&km, b, rows, p.H, is_bf16, 64)) return 1;
+    UParams prm = {(const uint2 *)nt_lut, c, p.B, p.H, p.nb_a, p.blocks, p.lut_stride, c_dtype, is_bf16, 0};
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(sddmm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSddmmSmem) != cudaSuccess)
+            return fail("sfb_bst_sgemm_nt: cannot reserve %zu bytes of shared memory", kSddmmSmem);
+        configured = true;
+    }
+    sddmm_tc_kernel<<<dim3((p.blocks + kChunk - 1) / kChunk, p.B, p.H), 192, kSddmmSmem, s>>>(qm, km, prm);
+    return check_launch("sfb_bst_sgemm_nt");
+}
+
+bool tc_spmm_supported(int a_dtype, int bc_dtype, uint32_t bs, const AttnDims &p, uint32_t max_lut)
+{
+    return a_dtype == bc_dtype && (a_dtype == SFB_BF16 || a_dtype == SFB_F16) && p.blocks > 0 && tc_shape_ok(bs, p, max_lut);
+}
+
+int tc_spmm(cudaStream_t s, const void *nn_lut, const void *a, const void *b, void *c, int dtype, const AttnDims &p)
+{
+    using namespace tc;
+    SFB_REQUIRE((((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) == 0, "sfb_bst_sgemm_xn: a, b, c must be 16-byte aligned");
+    const int is_bf16 = dtype == SFB_BF16;
+    const uint64_t prow = (uint64_t)p.B * p.H * p.blocks * 64;
+    CUtensorMap pm, vm;
+    if (make_p_map(&pm, a, prow, is_bf16) || make_map(&vm, b, (uint64_t)p.B * p.nb_b * 64, p.H, is_bf16, 64)) return 1;
+    UParams prm = {(const uint2 *)nn_lut, c, p.B, p.H, p.nb_a, p.blocks, p.lut_stride, dtype, is_bf16, (uint32_t)prow};
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(spmm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSpmmSmem) != cudaSuccess)
+            return fail("sfb_bst_sgemm_xn: cannot reserve %zu bytes of shared memory", kSpmmSmem);
+        configured = true;
+    }
+    spmm_tc_kernel<<<dim3((p.nb_a + 1) / 2, p.B, p.H), 192, kSpmmSmem, s>>>(pm, vm, prm);
+    return check_launch("sfb_bst_sgemm_xn");
+}
+
+int tc_status_unfused(uint32_t *out)
+{
+    cudaError_t e = cudaMemcpyFromSymbol(out, tc::g_status, sizeof(uint32_t));
+    if (e != cudaSuccess) return fail("sfb_device_status: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+}  // namespace sfb

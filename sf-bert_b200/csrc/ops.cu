@@ -26,6 +26,7 @@ extern "C" int sfb_bst_sgemm_nt(sfb_stream_t stream, const void *lut, const void
     SFB_REQUIRE(lut_heads == 1 || lut_dim >= blocks, "%s: lut_dim %u smaller than blocks %u", who, lut_dim, blocks);
     if (blocks == 0) { clear_error(); return 0; }
     AttnDims p = {batch_dim, head_dim, state_dim, ctx_blks_a, ctx_blks_b, blocks, lut_heads > 1 ? lut_dim : 0, 0};
+    if (tc_sddmm_supported(ab_dtype, block_size, p)) return tc_sddmm(as_stream(stream), lut, a, b, c, ab_dtype, c_dtype, p);
     return simt_sddmm_nt(as_stream(stream), lut, a, b, c, ab_dtype, c_dtype, block_size, p);
 }
 
@@ -56,7 +57,7 @@ extern "C" int sfb_bst_sgemm_xn(sfb_stream_t stream, const void *lut, const void
                                 uint32_t op, uint32_t magic, uint32_t shift, uint32_t max_lut)
 {
     const char *who = "sfb_bst_sgemm_xn";
-    (void)magic; (void)shift; (void)max_lut;
+    (void)magic; (void)shift;
     SFB_REQUIRE(lut && a && b && c, "%s: NULL pointer", who);
     SFB_REQUIRE(op == SFB_NN_OP, "%s: op %u not supported (forward NN only)", who, op);
     SFB_REQUIRE(valid_dtype(a_dtype) && valid_dtype(bc_dtype), "%s: unknown dtype", who);
@@ -64,6 +65,7 @@ extern "C" int sfb_bst_sgemm_xn(sfb_stream_t stream, const void *lut, const void
     SFB_REQUIRE(lut_heads == 1 || lut_dim >= blocks + ctx_blks_c, "%s: lut_dim %u smaller than blocks+ctx_blks", who, lut_dim);
     if (ctx_blks_c == 0) { clear_error(); return 0; }
     AttnDims p = {batch_dim, head_dim, state_dim, ctx_blks_c, ctx_blks_b, blocks, lut_heads > 1 ? lut_dim : 0, 0};
+    if (tc_spmm_supported(a_dtype, bc_dtype, block_size, p, max_lut)) return tc_spmm(as_stream(stream), lut, a, b, c, a_dtype, p);
     return simt_spmm_nn(as_stream(stream), lut, a, b, c, a_dtype, bc_dtype, block_size, p);
 }
 
@@ -109,7 +111,9 @@ extern "C" int sfb_fused_attention(sfb_stream_t stream, const void *nn_lut, cons
 extern "C" int sfb_device_status(uint32_t *status)
 {
     SFB_REQUIRE(status, "sfb_device_status: NULL pointer");
-    if (tc_status(status)) return 1;
+    uint32_t a = 0, b = 0;
+    if (tc_status_fused(&a) || tc_status_unfused(&b)) return 1;
+    *status = a ? a : b;
     clear_error();
     return 0;
 }

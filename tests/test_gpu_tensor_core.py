@@ -135,3 +135,72 @@ def test_benchmark_configs_full_size(sfb, oracle, name, dtype, B, H, L, orc, dev
     p = sfb.masked_softmax(s, lay, scale, torch.bfloat16)
     ou = sfb.bst_sgemm_xn(p, vb, lay).float()
     assert float((ou - o[:1].float()).abs().max()) <= 2 * REL * float(ou.abs().max())
+
+
+# --------------------------------------------------------------------------------------------
+# the unfused operators on the tensor cores (16-bit operands, 64x64 blocks, 64-wide heads)
+def _random_layout(H, nb, per_head, seed, empty_rows=()):
+    rng = np.random.RandomState(seed)
+    layout = np.zeros((H, nb, nb), np.uint8)
+    rows = [i for i in range(nb) if i not in empty_rows]
+    cells = [(i, j) for i in rows for j in range(nb)]
+    for h in range(H):
+        for idx in rng.choice(len(cells), per_head, replace=False):
+            layout[h][cells[idx]] = 1
+    return layout
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("out", ["f32", "bf16"])
+@pytest.mark.parametrize("H_lut,nb,per_head,empty", [(1, 5, 11, ()), (3, 6, 9, (1, 4)), (1, 40, 70, ())])
+def test_sddmm_on_tensor_cores(sfb, oracle, dtype, out, H_lut, nb, per_head, empty):
+    B, H, d = 2, 3, 64
+    layout = _random_layout(H_lut, nb, per_head, 5, empty)
+    lay = sfb.BlockLayout(torch.from_numpy(layout).cuda(), 64)
+    luts = oracle.lut_build(layout)
+    q, k, v = (_rand(oracle, (B, nb * 64, H, d), 900 + i, dtype) for i in range(3))
+    ref = oracle.attention(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(), luts, 64,
+                           np.float32(0.125), want=("s",))["s"]
+    s = sfb.bst_sgemm_nt(q, k, lay, {"f32": torch.float32, "bf16": torch.bfloat16}[out])
+    assert sfb.device_status() == 0
+    tol = 1e-3 * np.sqrt(d) if out == "f32" else np.abs(ref).max() * 2.0 ** -7
+    assert np.abs(s.float().cpu().numpy() - ref).max() <= tol
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("H_lut,nb,per_head,empty", [(1, 5, 11, ()), (3, 6, 9, (1, 4)), (1, 40, 70, ()), (1, 1, 1, ())])
+def test_spmm_on_tensor_cores(sfb, oracle, dtype, H_lut, nb, per_head, empty):
+    B, H, d = 2, 3, 64
+    layout = _random_layout(H_lut, nb, per_head, 6, empty)
+    lay = sfb.BlockLayout(torch.from_numpy(layout).cuda(), 64)
+    luts = oracle.lut_build(layout)
+    v = _rand(oracle, (B, nb * 64, H, d), 950, dtype)
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    p = torch.rand(B, H, lay.blocks, 64, 64, device="cuda", generator=gen).to(TD[dtype])
+    o = torch.full_like(v, 5.0)
+    o = sfb.bst_sgemm_xn(p, v, lay)
+    assert sfb.device_status() == 0
+    pn, vn = p.float().cpu().numpy(), v.float().cpu().numpy()
+    want = np.zeros_like(vn)
+    for h in range(H):
+        nt = luts["nt"][h if H_lut > 1 else 0]
+        for kk in range(luts["blocks"]):
+            i, j = int(nt[kk, 0]), int(nt[kk, 1])
+            want[:, i * 64:(i + 1) * 64, h] += np.einsum("brc,bcd->brd", pn[:, h, kk], vn[:, j * 64:(j + 1) * 64, h])
+    assert np.abs(o.float().cpu().numpy() - want).max() <= REL * max(1.0, np.abs(want).max())
+    for i in empty:
+        assert float(o[:, i * 64:(i + 1) * 64].abs().max()) == 0.0
+
+
+def test_unfused_pipeline_16bit_full_size(sfb, oracle):
+    """SDDMM -> softmax -> SpMM, all 16-bit, at the BigBird configuration's full size, against the fused kernel."""
+    B, H, L, d = 16, 12, 4096, 64
+    lay = sfb.BlockLayout.generate(sfb.LAYOUT_BIGBIRD, 1, L // 64, 64, p0=1, p1=1, p2=1, p3=3, seed=1236)
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    q, k, v = (torch.randn(B, L, H, d, device="cuda", generator=gen).to(torch.bfloat16) for _ in range(3))
+    s = sfb.bst_sgemm_nt(q, k, lay, torch.bfloat16)
+    p = sfb.masked_softmax(s, lay, 0.125, torch.bfloat16)
+    o = sfb.bst_sgemm_xn(p, v, lay).float()
+    assert sfb.device_status() == 0
+    fused = sfb.fused_attention(q, k, v, lay, 0.125).float()
+    assert float((o - fused).abs().max()) <= 2 * REL * float(fused.abs().max())
