@@ -28,7 +28,12 @@ struct UParams {
     uint32_t p_rows;           // spmm: rows of the 2-D view of P (= B*H*blocks*64); a coordinate beyond it reads zeros
 };
 
-constexpr size_t kSddmmSmem = 1024 + kUStages * 2 * kTileBytes + sizeof(UShared);
+constexpr int kSdStages = 3;
+struct SdShared {
+    uint64_t in_full[kSdStages], in_empty[kSdStages], s_full[2], s_empty[2], drained;
+    uint32_t tmem_base, abort_flag;
+};
+constexpr size_t kSddmmSmem = 1024 + kSdStages * 2 * kTileBytes + sizeof(SdShared);
 constexpr size_t kSpmmSmem = 1024 + kUStages * (kQBytes + kTileBytes) + sizeof(UShared);
 
 __device__ __forceinline__ void store_row16(void *dst_base, size_t elem_off, const uint32_t (&v)[16], int out_dtype, int c0)
@@ -44,9 +49,10 @@ __device__ __forceinline__ void store_row16(void *dst_base, size_t elem_off, con
         uint32_t w[8];
 #pragma unroll
         for (int j = 0; j < 8; j++) w[j] = pack2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), out_dtype == SFB_BF16);
-        uint4 *d = (uint4 *)((uint16_t *)dst_base + elem_off + c0);
-        d[0] = make_uint4(w[0], w[1], w[2], w[3]);
-        d[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        // one 32-byte store: a whole sector per thread
+        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"((uint16_t *)dst_base + elem_off + c0), "r"(w[0]),
+                     "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                     : "memory");
     }
 }
 
@@ -55,16 +61,17 @@ __device__ __forceinline__ void store_row16(void *dst_base, size_t elem_off, con
 // a run of kChunk consecutive blocks.  Per block one stage holds the 64 query rows followed by the 64 key rows;
 // the M=128 MMA reads the stage as its A operand, so accumulator lanes 0-63 hold Q.K^T and lanes 64-127 a
 // by-product (K.K^T) that is never read -- the operator is bound by the 8 KB of S it writes per block, not by
-// tensor work.  warp 0: TMA; warp 1: MMA; warps 4-5: TMEM lanes 0-63 -> global, one score row per thread.
+// tensor work.  warp 0: TMA; warp 1: MMA; warps 4-5 and 8-9: TMEM lanes 0-63 -> global, half a score row (32
+// columns) per thread.
 constexpr uint32_t kChunk = 32;
 
-__global__ void __launch_bounds__(192, 2)
+__global__ void __launch_bounds__(320, 4)
 sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap, const UParams p)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *tiles = smem;                                   // stage s: Q rows (8 KB) then K rows (8 KB)
-    UShared *st = (UShared *)(tiles + kUStages * 2 * kTileBytes);
+    SdShared *st = (SdShared *)(tiles + kSdStages * 2 * kTileBytes);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t b = blockIdx.y, h = blockIdx.z;
@@ -76,8 +83,8 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
     const uint32_t fmt = p.is_bf16 ? 1u : 0u;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kUStages; s++) { mbar_init(&st->in_full[s], 1); mbar_init(&st->in_empty[s], 1); }
-        for (int s = 0; s < 2; s++) { mbar_init(&st->s_full[s], 1); mbar_init(&st->s_empty[s], 64); }
+        for (int s = 0; s < kSdStages; s++) { mbar_init(&st->in_full[s], 1); mbar_init(&st->in_empty[s], 1); }
+        for (int s = 0; s < 2; s++) { mbar_init(&st->s_full[s], 1); mbar_init(&st->s_empty[s], 128); }
         mbar_init(&st->drained, 1);
         st->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -96,8 +103,8 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
     if (warp == 0) {
         if (lane == 0) {
             for (uint32_t t = 0; t < T; t++) {
-                const uint32_t s = t % kUStages;
-                if (t >= kUStages && !mbar_wait(&st->in_empty[s], ((t / kUStages) - 1) & 1, abort_flag, 21)) break;
+                const uint32_t s = t % kSdStages;
+                if (t >= kSdStages && !mbar_wait(&st->in_empty[s], ((t / kSdStages) - 1) & 1, abort_flag, 21)) break;
                 const uint2 ent = lut[t];
                 if (ent.x >= p.nb || ent.y >= p.nb) {   // a LUT entry outside the block grid: report, do not fetch
                     st->abort_flag = 1;
@@ -113,8 +120,8 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
         if (lane == 0) {
             const uint32_t idesc = instr_desc(fmt, fmt, 128, 64, 0);
             for (uint32_t t = 0; t < T; t++) {
-                const uint32_t s = t % kUStages;
-                if (!mbar_wait(&st->in_full[s], (t / kUStages) & 1, abort_flag, 23)) break;
+                const uint32_t s = t % kSdStages;
+                if (!mbar_wait(&st->in_full[s], (t / kSdStages) & 1, abort_flag, 23)) break;
                 if (t >= 2 && !mbar_wait(&st->s_empty[t & 1], ((t >> 1) - 1) & 1, abort_flag, 24)) break;
                 tcgen05_fence_after();
                 const uint64_t a_desc = smem_desc_sw128(smem_u32(tiles + s * 2 * kTileBytes));
@@ -125,8 +132,9 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
                 umma_commit(&st->in_empty[s]);
             }
         }
-    } else if (warp >= 4) {
+    } else if (warp == 4 || warp == 5 || warp == 8 || warp == 9) {
         const uint32_t quarter = warp & 3;                 // 0 and 1: TMEM lanes 0-63
+        const int cbase = warp >= 8 ? 32 : 0;              // which half of the 64 columns
         const uint32_t r = quarter * 32 + lane;
         const uint32_t lane_field = (quarter * 32) << 16;
         for (uint32_t t = 0; t < T; t++) {
@@ -134,7 +142,7 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
             tcgen05_fence_after();
             const size_t off = ((((size_t)b * p.H + h) * p.blocks + k0 + t) * 64 + r) * 64;
 #pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 16) {
+            for (int c0 = cbase; c0 < cbase + 32; c0 += 16) {
                 uint32_t v[16];
                 TMEM_LD_16((v), tmem + 64 * (t & 1) + lane_field + c0);
                 tmem_wait_ld();
@@ -327,7 +335,7 @@ int tc_sddmm(cudaStream_t s, const void *nt_lut, const void *a, const void *b, v
             return fail("sfb_bst_sgemm_nt: cannot reserve %zu bytes of shared memory", kSddmmSmem);
         configured = true;
     }
-    sddmm_tc_kernel<<<dim3((p.blocks + kChunk - 1) / kChunk, p.B, p.H), 192, kSddmmSmem, s>>>(qm, km, prm);
+    sddmm_tc_kernel<<<dim3((p.blocks + kChunk - 1) / kChunk, p.B, p.H), 320, kSddmmSmem, s>>>(qm, km, prm);
     return check_launch("sfb_bst_sgemm_nt");
 }
 
