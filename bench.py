@@ -249,6 +249,8 @@ def run_bandwidth_kernel(args):
     B, H, L, d, bs = cfg["B"], cfg["H"], cfg["L"], cfg["d"], cfg["bs"]
     pk = peaks()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    if args.kernel == "encoder_layer":
+        return run_encoder_layer(args, sfb, cfg, pk, flush)
     if args.kernel == "softmax":
         lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
         x = torch.randn(B, H, lay.blocks, bs, bs, device="cuda").to(torch.bfloat16)
@@ -302,6 +304,46 @@ def run_bandwidth_kernel(args):
                      "frac": round(gbs / pk["hbm"], 4), "traffic": None, "peak_source": pk["source"] + " copy bandwidth",
                      "algorithmic_bytes": nbytes},
         "gpu_launches": args.steps, "clocks": clocks}), flush=True)
+
+
+def run_encoder_layer(args, sfb, cfg, pk, flush):
+    """Sequences per second of one encoder layer (post-LN, GELU FFN of 4 x hidden) at the workload's shape:
+    projections by the GEMM library, attention / LayerNorm / GELU by this library (N=1)."""
+    import importlib.util
+    import torch
+    spec = importlib.util.spec_from_file_location("sfb_encoder", os.path.join(ROOT, "sf-bert_b200", "encoder.py"))
+    enc = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(enc)
+    B, H, L, d, bs = cfg["B"], cfg["H"], cfg["L"], cfg["d"], cfg["bs"]
+    tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[cfg["dtype"]]
+    hidden, ffn = H * d, 4 * H * d
+    lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
+    w = enc.EncoderLayerWeights(hidden, ffn, tdt, seed=1)
+    x = torch.randn(B, L, hidden, device="cuda").to(tdt)
+    fn = lambda: enc.encoder_layer(sfb, x, w, lay, H, "post")
+    for _ in range(max(args.warmup, 3)):
+        fn()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a, b_ in ev:
+        flush.fill_(1)
+        a.record()
+        fn()
+        b_.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = sum(a.elapsed_time(b_) for a, b_ in ev) / args.steps
+    gemm_flops = 2.0 * B * L * hidden * (4 * hidden + 2 * ffn)
+    attn_flops = attention_flops(cfg, lay.blocks)
+    print(json.dumps({
+        "metric": "encoder-layer sequences/s", "value": round(B / (ms * 1e-3), 2), "unit": "seq/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "dtype": cfg["dtype"], "data": "synthetic",
+        "config": {"workload": args.config, "B": B, "L": L, "hidden": hidden, "ffn": ffn, "heads": H, "ln": "post",
+                   "projections": "torch.matmul (cuBLAS)", "l2": "flushed between timed steps"},
+        "tflops_total": round((gemm_flops + attn_flops) / (ms * 1e-3) / 1e12, 1),
+        "gpu_launches": args.steps * 4, "clocks": clocks}), flush=True)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -378,7 +420,7 @@ if __name__ == "__main__":
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="stride_bertbase", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm"],
+    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "encoder_layer"],
                     help="fused = the headline fused attention; softmax / layernorm = the bandwidth kernels (N=1)")
     a = ap.parse_args()
     if a.impl == "reference":

@@ -162,6 +162,12 @@ int sfb_bias_residual_layernorm(sfb_stream_t stream, void *out, void *sum_out, f
                                 const float *gain, const float *beta, uint32_t m, uint32_t hidden,
                                 int dtype);
 
+/* out = t * sigmoid(1.702 t), t = x + bias, over m rows of n elements (bias fp32 [n], may be NULL; out may
+ * alias x).  Replaces tensor_add_vector_gpu_2048 + gelu_gpu_v2 (cuda_kernels.h:471-489, :561-581; call site
+ * transformer_attention_optimize.cu:781-785); CPU twin gelu, ewops.h:32-43. */
+int sfb_bias_gelu(sfb_stream_t stream, void *out, const void *x, const float *bias, uint32_t m,
+                  uint32_t n, int dtype);
+
 #ifdef __cplusplus
 }
 #endif

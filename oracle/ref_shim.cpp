@@ -46,6 +46,9 @@ void ref_tensor_add_tensor(float *C, float *A, float *B, int d0, int d1, int d2)
     tensor_add_tensor(C, A, B, d0, d1, d2);
 }
 
+/* ewops.h:32-43 */
+void ref_gelu(float *C, float *A, int batch, int seq_len, int state) { gelu(C, A, batch, seq_len, state); }
+
 /* layernorm.h:13-38 */
 void ref_layernorm(float *out, float *mean, float *rstd, const float *in, const float *gain,
                    const float *b, int batch, int seq_len, int state)

@@ -420,6 +420,20 @@ void orc_bias_residual_layernorm(float *out, float *sum_out, float *mean, float 
 }
 
 /* ------------------------------------------------------------------------------ */
+void orc_bias_gelu(float *out, const float *x, const float *bias, uint32_t m, uint32_t n)
+{
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < (long long)m; i++)
+        for (uint32_t j = 0; j < n; j++) {
+            float a = x[(size_t)i * n + j];
+            if (bias) a = a + bias[j];                 /* ewops.h:13-14 */
+            float ex = (float)exp(-(1.702 * a));       /* ewops.h:37: double arithmetic, float result */
+            float rcp = (float)(1.0 / (ex + 1.0));     /* ewops.h:38 */
+            out[(size_t)i * n + j] = a * rcp;          /* ewops.h:40 */
+        }
+}
+
+/* ------------------------------------------------------------------------------ */
 void orc_magicu64(uint32_t d, uint32_t *magic, uint32_t *shift)
 {
     /* blocksparse.h:1016-1043: smallest p with 2^p > nc*(d-1-(2^p-1)%d) */

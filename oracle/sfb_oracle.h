@@ -117,6 +117,10 @@ void orc_bias_residual_layernorm(float *out, float *sum_out, float *mean, float 
                                  const float *gain, const float *beta,
                                  uint32_t m, uint32_t hidden);
 
+/* out = t * (1 / (exp(-1.702 t) + 1)), t = x + bias (ewops.h:10-17 then ewops.h:32-43: the exponential in
+ * double of the float product, the reciprocal and the result in float).  bias may be NULL. */
+void orc_bias_gelu(float *out, const float *x, const float *bias, uint32_t m, uint32_t n);
+
 /* magic-number division constants (blocksparse.h:1016-1043) */
 void orc_magicu64(uint32_t d, uint32_t *magic, uint32_t *shift);
 

@@ -22,7 +22,7 @@ NT_OP, NN_OP, TN_OP = 0, 1, 2
 SYMBOLS = [
     "sfb_last_error", "sfb_version", "sfb_layout_generate", "sfb_lut_count", "sfb_lut_build", "sfb_mask_pack",
     "sfb_magicu64", "sfb_bst_sgemm_nt", "sfb_masked_softmax", "sfb_bst_sgemm_xn", "sfb_fused_sddmm_softmax",
-    "sfb_fused_attention", "sfb_bias_residual_layernorm", "sfb_device_status",
+    "sfb_fused_attention", "sfb_bias_residual_layernorm", "sfb_device_status", "sfb_bias_gelu",
 ]
 
 if not os.path.exists(LIB_PATH):
@@ -48,6 +48,7 @@ lib.sfb_bias_residual_layernorm.argtypes = [_vp] * 10 + [_u32, _u32, _i32]
 
 
 lib.sfb_device_status.argtypes = [C.POINTER(_u32)]
+lib.sfb_bias_gelu.argtypes = [_vp, _vp, _vp, _vp, _u32, _u32, _i32]
 
 
 def device_status():
@@ -216,3 +217,11 @@ def bias_residual_layernorm(x, bias, resid, gain, beta, want_sum=False):
     _check(lib.sfb_bias_residual_layernorm(_stream(), _p(out), _p(summed), _p(mean), _p(rstd), _p(x), _p(bias), _p(resid),
                                            _p(gain), _p(beta), m, hidden, dtype_tag(x)))
     return out, summed, mean, rstd
+
+
+def bias_gelu(x, bias, out=None):
+    """(x + bias) * sigmoid(1.702 (x + bias)) (tensor_add_vector_gpu_2048 + gelu_gpu_v2, cuda_kernels.h:471,561)."""
+    m, n = x.shape
+    out = torch.empty_like(x) if out is None else out
+    _check(lib.sfb_bias_gelu(_stream(), _p(out), _p(x), _p(bias), m, n, dtype_tag(x)))
+    return out

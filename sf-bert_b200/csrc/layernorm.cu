@@ -184,3 +184,47 @@ extern "C" int sfb_bias_residual_layernorm(sfb_stream_t stream, void *out, void 
     if (dtype == SFB_BF16) return launch_ln<SFB_BF16>(s, out, sum_out, mean, rstd, x, bias, resid, gain, beta, m, hidden);
     return launch_ln<SFB_F16>(s, out, sum_out, mean, rstd, x, bias, resid, gain, beta, m, hidden);
 }
+
+// ---- bias + GELU ------------------------------------------------------------------------------------
+// y = t * sigmoid(1.702 t), t = x + bias  (the reference's GELU, ewops.h:32-43 / cuda_kernels.h:561-581,
+// with the bias add of cuda_kernels.h:471-489 folded in).  One 16-byte access per thread and step.
+namespace sfb {
+
+template <int DT>
+__global__ void __launch_bounds__(256) bias_gelu_kernel(void *__restrict__ out, const void *__restrict__ x,
+                                                       const float *__restrict__ bias, size_t total, uint32_t n)
+{
+    constexpr int N = Vec8<DT>::N;
+    const size_t stride = (size_t)gridDim.x * blockDim.x * N;
+    for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * N; i < total; i += stride) {
+        float v[N];
+        Vec8<DT>::load(v, x, i);
+        const uint32_t col = (uint32_t)(i % n);
+#pragma unroll
+        for (int t = 0; t < N; t++) {
+            const float a = v[t] + (bias ? __ldg(bias + col + t) : 0.f);
+            v[t] = a / (1.f + __expf(-1.702f * a));
+        }
+        Vec8<DT>::store(out, i, v);
+    }
+}
+
+}  // namespace sfb
+
+extern "C" int sfb_bias_gelu(sfb_stream_t stream, void *out, const void *x, const float *bias, uint32_t m, uint32_t n, int dtype)
+{
+    SFB_REQUIRE(out && x, "sfb_bias_gelu: NULL pointer");
+    SFB_REQUIRE(valid_dtype(dtype), "sfb_bias_gelu: unknown dtype %d", dtype);
+    SFB_REQUIRE(n >= 8 && n % 8 == 0, "sfb_bias_gelu: row length %u must be a multiple of 8", n);
+    SFB_REQUIRE((((uintptr_t)out | (uintptr_t)x | (uintptr_t)bias) & 15) == 0, "sfb_bias_gelu: pointers must be 16-byte aligned");
+    const size_t total = (size_t)m * n;
+    if (total == 0) { clear_error(); return 0; }
+    cudaStream_t s = as_stream(stream);
+    const int per = dtype == SFB_F32 ? 4 : 8;
+    size_t ctas = (total / per + 255) / 256;
+    if (ctas > 148 * 16) ctas = 148 * 16;
+    if (dtype == SFB_F32) bias_gelu_kernel<SFB_F32><<<(unsigned)ctas, 256, 0, s>>>(out, x, bias, total, n);
+    else if (dtype == SFB_BF16) bias_gelu_kernel<SFB_BF16><<<(unsigned)ctas, 256, 0, s>>>(out, x, bias, total, n);
+    else bias_gelu_kernel<SFB_F16><<<(unsigned)ctas, 256, 0, s>>>(out, x, bias, total, n);
+    return check_launch("sfb_bias_gelu");
+}

@@ -1,0 +1,55 @@
+"""One transformer encoder layer around the block-sparse attention path, in the operation order of the
+reference's driver (transformer_attention_optimize.cu:688-801 / transformer_inference_part.cpp:210-239):
+
+    pre-LN  (the reference):  h = LN(x); a = Attn(hWq+bq, hWk+bk, hWv+bv); x1 = x + aWo + bo;
+                              h2 = LN(x1); x2 = x1 + GELU(h2 W1 + b1) W2 + b2
+    post-LN (BERT):           x1 = LN(x + Attn(...)Wo + bo); x2 = LN(x1 + GELU(x1 W1 + b1) W2 + b2)
+
+The dense projections are plain library GEMMs (torch.matmul -> cuBLAS; the reference calls cublasSgemm
+there).  Everything else -- attention, bias + residual + LayerNorm, bias + GELU -- is this library's
+kernels.  Dropout is off (keep probability 1), as in every parity run."""
+import math
+
+import torch
+
+
+class EncoderLayerWeights:
+    def __init__(self, hidden, ffn, dtype, device="cuda", seed=0, std=0.02):
+        g = torch.Generator(device=device).manual_seed(seed)
+        rn = lambda *s: (torch.randn(*s, device=device, generator=g) * std).to(dtype)
+        self.wq, self.wk, self.wv, self.wo = (rn(hidden, hidden) for _ in range(4))
+        self.w1, self.w2 = rn(hidden, ffn), rn(ffn, hidden)
+        z = lambda n: torch.zeros(n, device=device, dtype=torch.float32)
+        self.bq, self.bk, self.bv, self.bo, self.b2 = (z(hidden) for _ in range(5))
+        self.b1 = z(ffn)
+        self.g1, self.g2 = (torch.ones(hidden, device=device, dtype=torch.float32) for _ in range(2))
+        self.be1, self.be2 = z(hidden), z(hidden)
+
+
+def encoder_layer(sfb, x, w, lay, heads, ln_order="post"):
+    """x [B, L, hidden] -> [B, L, hidden].  `sfb` is the loaded package, `lay` a BlockLayout."""
+    B, L, hidden = x.shape
+    d = hidden // heads
+    m = B * L
+    x2d = x.reshape(m, hidden)
+    scale = 1.0 / math.sqrt(d)
+
+    def attn(h2d):
+        q = torch.addmm(w.bq.to(h2d.dtype), h2d, w.wq).view(B, L, heads, d)
+        k = torch.addmm(w.bk.to(h2d.dtype), h2d, w.wk).view(B, L, heads, d)
+        v = torch.addmm(w.bv.to(h2d.dtype), h2d, w.wv).view(B, L, heads, d)
+        return sfb.fused_attention(q, k, v, lay, scale).view(m, hidden)
+
+    if ln_order == "pre":
+        h, _, _, _ = sfb.bias_residual_layernorm(x2d, None, None, w.g1, w.be1)
+        a = torch.mm(attn(h), w.wo)
+        h2, x1, _, _ = sfb.bias_residual_layernorm(a, w.bo, x2d, w.g2, w.be2, want_sum=True)
+        f = sfb.bias_gelu(torch.mm(h2, w.w1), w.b1)
+        y = torch.addmm(w.b2.to(x.dtype), f, w.w2)
+        return (x1 + y).view(B, L, hidden)
+    a = torch.mm(attn(x2d), w.wo)
+    x1, _, _, _ = sfb.bias_residual_layernorm(a, w.bo, x2d, w.g1, w.be1)
+    f = sfb.bias_gelu(torch.mm(x1, w.w1), w.b1)
+    y = torch.mm(f, w.w2)
+    out, _, _, _ = sfb.bias_residual_layernorm(y, w.b2, x1, w.g2, w.be2)
+    return out.view(B, L, hidden)

@@ -166,6 +166,27 @@ def bias_residual_layernorm(x, bias, resid, gain, beta):
     return out, summed, mean, rstd
 
 
+def bias_gelu(x, bias):
+    x = np.ascontiguousarray(x, np.float32)
+    m, n = x.shape
+    out = np.zeros_like(x)
+    b = None if bias is None else np.ascontiguousarray(bias, np.float32)
+    lib().orc_bias_gelu(_ptr(out, _f32p), _ptr(x, _f32p), _ptr(b, _f32p), C.c_uint32(m), C.c_uint32(n))
+    return out
+
+
+def ref_bias_gelu(x, bias):
+    R = ref()
+    assert R is not None
+    x = np.ascontiguousarray(x, np.float32)
+    m, n = x.shape
+    t = np.zeros_like(x)
+    R.ref_bias(_ptr(t, _f32p), _ptr(x, _f32p), _ptr(np.ascontiguousarray(bias, np.float32), _f32p), C.c_int(n), C.c_int(m))
+    out = np.zeros_like(x)
+    R.ref_gelu(_ptr(out, _f32p), _ptr(t, _f32p), C.c_int(1), C.c_int(m), C.c_int(n))
+    return out
+
+
 def magicu64(d):
     mg, sh = C.c_uint32(0), C.c_uint32(0)
     lib().orc_magicu64(C.c_uint32(d), C.byref(mg), C.byref(sh))

@@ -284,3 +284,13 @@ def test_layernorm_matches_reference_cpu_golden(sfb, oracle):
     np.testing.assert_allclose(y.cpu().numpy(), g["ln/y"], atol=1e-5)
     np.testing.assert_allclose(mean.cpu().numpy(), g["ln/mean"], atol=1e-6)
     np.testing.assert_allclose(rstd.cpu().numpy(), g["ln/rstd"], rtol=1e-5)
+
+
+@pytest.mark.parametrize("dtype,m,n", [("f32", 100, 3072), ("bf16", 64, 4096), ("f16", 33, 768)])
+def test_bias_gelu(sfb, oracle, dtype, m, n):
+    x = torch.from_numpy(oracle.fill_normal((m, n), 61, 2.0)).cuda().to(TD[dtype])
+    b = torch.from_numpy(oracle.fill_normal((n,), 62, 0.5)).cuda()
+    want = oracle.bias_gelu(x.float().cpu().numpy(), b.cpu().numpy())
+    got = sfb.bias_gelu(x, b).float().cpu().numpy()
+    tol = 2e-6 if dtype == "f32" else 2e-2
+    assert np.abs(got - want).max() <= tol * max(1.0, np.abs(want).max())

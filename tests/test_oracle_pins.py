@@ -158,3 +158,11 @@ def test_to_bhalf_rounds_half_away(oracle):
     v = np.array([1.0, 1.00390625, below, 1.0117188, -1.00390625, 0.0, 3.0e38], np.float32)
     bits = oracle.to_bhalf(v)
     assert list(bits[:5]) == [0x3F80, 0x3F81, 0x3F80, 0x3F82, 0xBF81]
+
+
+def test_gelu_matches_live_reference_when_built(oracle):
+    if oracle.ref() is None:
+        pytest.skip("oracle/_ref not built on this machine")
+    x = oracle.fill_normal((7, 96), 41, 2.0)
+    b = oracle.fill_normal((96,), 42, 0.5)
+    assert np.array_equal(oracle.bias_gelu(x, b), oracle.ref_bias_gelu(x, b))
