@@ -289,6 +289,170 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap pmap, const __grid_constant__
     }
 }
 
+// ---- fused SDDMM + softmax, probabilities out ----------------------------------------------------------
+// Row-pair tiling as the three-stage kernel.  The row's scores are produced twice by the tensor core instead of
+// making a round trip through memory: sweep 1 over the row pair's key blocks keeps the running row max and sum,
+// sweep 2 recomputes S and writes exp2(s*c - max) / sum.  warp 0: TMA (Q once, the K tiles twice); warp 1: MMA;
+// warps 2-5: one query row per thread.
+struct FpParams {
+    const uint2 *nn_lut;
+    const uint64_t *mask;      // mask_np order, or NULL
+    void *Y;
+    uint32_t B, H, nb, blocks, lut_stride, mask_stride;
+    float scale_log2e;
+    int out_dtype, is_bf16;
+};
+
+constexpr size_t kFpSmem = 1024 + kQBytes + kUStages * kTileBytes + sizeof(UShared);
+
+__global__ void __launch_bounds__(192, 2)
+fused_p_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap, const FpParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *q_tile = smem;
+    uint8_t *k_tiles = q_tile + kQBytes;
+    UShared *st = (UShared *)(k_tiles + kUStages * kTileBytes);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t pair = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
+    const uint32_t L = p.nb * 64;
+    const uint2 *nn = p.nn_lut + (size_t)h * p.lut_stride;
+    volatile uint32_t *abort_flag = &st->abort_flag;
+    const uint32_t fmt = p.is_bf16 ? 1u : 0u;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&st->q_full, 1);
+        for (int s = 0; s < kUStages; s++) { mbar_init(&st->in_full[s], 1); mbar_init(&st->in_empty[s], 1); }
+        for (int s = 0; s < 2; s++) { mbar_init(&st->s_full[s], 1); mbar_init(&st->s_empty[s], 128); }
+        mbar_init(&st->drained, 1);
+        st->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    build_union(nn, pair, p.nb, st->entries, st->found, &st->n_union, &st->abort_flag);
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&st->tmem_base)), "r"(128u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+
+    const uint32_t T = st->n_union;
+    const uint32_t T2 = 2 * T;                 // every key block is visited twice
+    const uint32_t tmem = st->tmem_base;
+    const int32_t xq = (int32_t)(h * 64);
+
+    if (warp == 0) {
+        if (lane == 0 && T > 0) {
+            mbar_expect_tx(&st->q_full, kQBytes);
+            tma_load_2d(smem_u32(q_tile), &qmap, &st->q_full, xq, (int32_t)(b * L + pair * 128));
+            for (uint32_t t = 0; t < T2; t++) {
+                const uint32_t s = t % kUStages;
+                if (t >= kUStages && !mbar_wait(&st->in_empty[s], ((t / kUStages) - 1) & 1, abort_flag, 41)) break;
+                mbar_expect_tx(&st->in_full[s], kTileBytes);
+                tma_load_2d(smem_u32(k_tiles + s * kTileBytes), &kmap, &st->in_full[s], xq,
+                            (int32_t)(b * L + st->entries[t % T].col * 64));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && T > 0) {
+            const uint32_t idesc = instr_desc(fmt, fmt, 128, 64, 0);
+            const uint64_t q_desc = smem_desc_sw128(smem_u32(q_tile));
+            bool alive = mbar_wait(&st->q_full, 0, abort_flag, 42);
+            for (uint32_t t = 0; alive && t < T2; t++) {
+                const uint32_t s = t % kUStages;
+                if (!mbar_wait(&st->in_full[s], (t / kUStages) & 1, abort_flag, 43)) break;
+                if (t >= 2 && !mbar_wait(&st->s_empty[t & 1], ((t >> 1) - 1) & 1, abort_flag, 44)) break;
+                tcgen05_fence_after();
+                const uint64_t k_desc = smem_desc_sw128(smem_u32(k_tiles + s * kTileBytes));
+#pragma unroll
+                for (uint32_t kk = 0; kk < 4; kk++) umma_f16(tmem + 64 * (t & 1), q_desc + 2 * kk, k_desc + 2 * kk, idesc, kk);
+                umma_commit(&st->s_full[t & 1]);
+                umma_commit(&st->in_empty[s]);
+            }
+        }
+    } else {
+        const uint32_t quarter = warp & 3;
+        const uint32_t r = quarter * 32 + lane;
+        const uint32_t half = r >> 6;
+        const uint32_t lane_field = (quarter * 32) << 16;
+        const float sl = p.scale_log2e;
+        float m = -INFINITY, l = 0.f, inv = 0.f;
+        for (uint32_t t = 0; t < T2; t++) {
+            if (!mbar_wait_warp(&st->s_full[t & 1], (t >> 1) & 1, abort_flag, 45)) break;
+            tcgen05_fence_after();
+            uint32_t sr[64];
+            TMEM_LD_32((sr), tmem + 64 * (t & 1) + lane_field);
+            TMEM_LD_32((sr + 32), tmem + 64 * (t & 1) + lane_field + 32);
+            tmem_wait_ld();
+            tcgen05_fence_before();
+            mbar_arrive(&st->s_empty[t & 1]);
+
+            const UnionEntry ent = st->entries[t % T];
+            const bool mine = (ent.flags >> half) & 1;
+            if (!mine) continue;
+            if (p.mask) {
+                const uint64_t w = p.mask[(size_t)h * p.mask_stride + (size_t)ent.blk[half] * 64 + (r & 63)];
+#pragma unroll
+                for (int c = 0; c < 64; c++)
+                    if (!((w >> c) & 1)) sr[c] = 0xff800000u;
+            }
+            if (t < T) {
+                // sweep 1: running max and sum
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 64; c++) mx = fmaxf(mx, __uint_as_float(sr[c]));
+                mx *= sl;
+                if (mx > m) {
+                    l *= ex2_approx(m - mx);     // 0 while m is still -inf
+                    m = mx;
+                }
+                if (m > -INFINITY) {
+                    float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int c = 0; c < 64; c++) ps4[c & 3] += ex2_approx(fmaf(__uint_as_float(sr[c]), sl, -m));
+                    l += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+                }
+                if (t + 1 == T) inv = l > 0.f ? 1.f / l : 0.f;
+            } else {
+                // sweep 2: probabilities out
+                if (t == T) inv = l > 0.f ? 1.f / l : 0.f;
+                const float neg_m = m > -INFINITY ? -m : 0.f;
+                const size_t off = ((((size_t)b * p.H + h) * p.blocks + ent.blk[half]) * 64 + (r & 63)) * 64;
+#pragma unroll
+                for (int c0 = 0; c0 < 64; c0 += 16) {
+                    uint32_t v[16];
+#pragma unroll
+                    for (int c = 0; c < 16; c++)
+                        v[c] = __float_as_uint(inv > 0.f ? ex2_approx(fmaf(__uint_as_float(sr[c0 + c]), sl, neg_m)) * inv : 0.f);
+                    store_row16(p.Y, off, v, p.out_dtype, c0);
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (st->abort_flag) {
+        if (warp == 1 && lane == 0) {
+            umma_commit(&st->drained);
+            for (uint32_t i = 0; i < kWaitLimit && !mbar_try_wait(&st->drained, 0); i++) {}
+        }
+        if (warp == 0 && lane == 0) {
+            const uint64_t t0 = clock64();
+            while (clock64() - t0 < 2000000ull) {}
+        }
+        __syncthreads();
+    }
+    if (warp == 0) {
+        __syncwarp();
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(128u) : "memory");
+    }
+}
+
 // P viewed as [rows, 64] 16-bit row-major, boxes of 64 x 64, 128-byte swizzle, zero fill outside
 static int make_p_map(CUtensorMap *map, const void *base, uint64_t rows, int is_bf16)
 {
@@ -322,7 +486,7 @@ bool tc_sddmm_supported(int ab_dtype, uint32_t bs, const AttnDims &p)
 int tc_sddmm(cudaStream_t s, const void *nt_lut, const void *a, const void *b, void *c, int ab_dtype, int c_dtype, const AttnDims &p)
 {
     using namespace tc;
-    SFB_REQUIRE((((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) == 0, "sfb_bst_sgemm_nt: a, b, c must be 16-byte aligned");
+    SFB_REQUIRE((((uintptr_t)a | (uintptr_t)b) & 15) == 0 && ((uintptr_t)c & 31) == 0, "sfb_bst_sgemm_nt: a, b must be 16-byte and c 32-byte aligned");
     SFB_REQUIRE(p.nb_a == p.nb_b, "sfb_bst_sgemm_nt: ctx_blks_a != ctx_blks_b is not supported for 16-bit operands");
     const int is_bf16 = ab_dtype == SFB_BF16;
     const uint64_t rows = (uint64_t)p.B * p.nb_a * 64;
@@ -339,6 +503,34 @@ int tc_sddmm(cudaStream_t s, const void *nt_lut, const void *a, const void *b, v
     return check_launch("sfb_bst_sgemm_nt");
 }
 
+bool tc_fused_p_supported(int ab_dtype, uint32_t bs, const AttnDims &p, float scale)
+{
+    // the longest row is not an argument of the fused entry points: any row of the block grid must fit the union list
+    return (ab_dtype == SFB_BF16 || ab_dtype == SFB_F16) && scale > 0.f && p.blocks > 0 &&
+           tc_shape_ok(bs, p, p.nb_a <= tc::kMaxUnion / 2 ? p.nb_a : 0);
+}
+
+int tc_fused_p(cudaStream_t s, const void *nn_lut, const void *a, const void *b, const void *mask, void *y, int ab_dtype,
+               int y_dtype, const AttnDims &p, float scale)
+{
+    using namespace tc;
+    SFB_REQUIRE((((uintptr_t)a | (uintptr_t)b | (uintptr_t)y) & 31) == 0, "sfb_fused_sddmm_softmax: a, b, y must be 32-byte aligned");
+    const int is_bf16 = ab_dtype == SFB_BF16;
+    const uint64_t rows = (uint64_t)p.B * p.nb_a * 64;
+    CUtensorMap qm, km;
+    if (make_map(&qm, a, rows, p.H, is_bf16, 128) || make_map(&km, b, rows, p.H, is_bf16, 64)) return 1;
+    FpParams prm = {(const uint2 *)nn_lut, (const uint64_t *)mask, y, p.B, p.H, p.nb_a, p.blocks, p.lut_stride, p.mask_stride,
+                    scale * 1.4426950408889634f, y_dtype, is_bf16};
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(fused_p_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFpSmem) != cudaSuccess)
+            return fail("sfb_fused_sddmm_softmax: cannot reserve %zu bytes of shared memory", kFpSmem);
+        configured = true;
+    }
+    fused_p_tc_kernel<<<dim3((p.nb_a + 1) / 2, p.B, p.H), 192, kFpSmem, s>>>(qm, km, prm);
+    return check_launch("sfb_fused_sddmm_softmax");
+}
+
 bool tc_spmm_supported(int a_dtype, int bc_dtype, uint32_t bs, const AttnDims &p, uint32_t max_lut)
 {
     return a_dtype == bc_dtype && (a_dtype == SFB_BF16 || a_dtype == SFB_F16) && p.blocks > 0 && tc_shape_ok(bs, p, max_lut);
@@ -347,7 +539,7 @@ bool tc_spmm_supported(int a_dtype, int bc_dtype, uint32_t bs, const AttnDims &p
 int tc_spmm(cudaStream_t s, const void *nn_lut, const void *a, const void *b, void *c, int dtype, const AttnDims &p)
 {
     using namespace tc;
-    SFB_REQUIRE((((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) == 0, "sfb_bst_sgemm_xn: a, b, c must be 16-byte aligned");
+    SFB_REQUIRE((((uintptr_t)a | (uintptr_t)b) & 15) == 0 && ((uintptr_t)c & 31) == 0, "sfb_bst_sgemm_xn: a, b must be 16-byte and c 32-byte aligned");
     const int is_bf16 = dtype == SFB_BF16;
     const uint64_t prow = (uint64_t)p.B * p.H * p.blocks * 64;
     CUtensorMap pm, vm;

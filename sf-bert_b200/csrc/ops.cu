@@ -84,6 +84,8 @@ extern "C" int sfb_fused_sddmm_softmax(sfb_stream_t stream, const void *nn_lut, 
     // the nn_lut of head h starts at h * (lut_dim + ctx_blks_a)  (fusion_blocksparse.h:1245)
     AttnDims p = {batch_dim, head_dim, state_dim, ctx_blks_a, ctx_blks_b, blocks, lut_heads > 1 ? lut_dim + ctx_blks_a : 0,
                   mask_heads > 1 ? blocks * block_size : 0};
+    if (ctx_blks_a == ctx_blks_b && tc_fused_p_supported(ab_dtype, block_size, p, scale))
+        return tc_fused_p(as_stream(stream), nn_lut, a, b, mask, y, ab_dtype, y_dtype, p, scale);
     return simt_fused_sddmm_softmax(as_stream(stream), nn_lut, a, b, mask, y, ab_dtype, y_dtype, block_size, p, scale);
 }
 

@@ -204,3 +204,26 @@ def test_unfused_pipeline_16bit_full_size(sfb, oracle):
     assert sfb.device_status() == 0
     fused = sfb.fused_attention(q, k, v, lay, 0.125).float()
     assert float((o - fused).abs().max()) <= 2 * REL * float(fused.abs().max())
+
+
+@pytest.mark.parametrize("dtype,out", [("bf16", "f32"), ("f16", "f16"), ("bf16", "bf16")])
+@pytest.mark.parametrize("pred,ctx", [(None, 0), ("MASK_CAUSAL_DIAG", 0), ("MASK_LOCAL", 100)])
+def test_fused_sddmm_softmax_on_tensor_cores(sfb, oracle, dtype, out, pred, ctx):
+    """fusion_attention1/2/_full/_local/2_64 for 16-bit operands: probabilities against the oracle, rows sum to 1."""
+    B, H, nb, d = 2, 3, 9, 64
+    lay = sfb.BlockLayout.generate(sfb.LAYOUT_FULL, 1, nb, 64, causal=1)
+    luts = oracle.lut_build(oracle.layout("full", 1, nb, causal=1))
+    m_np = None
+    if pred:
+        lay.pack_mask(getattr(sfb, pred), ctx)
+        m_np, _ = oracle.mask_pack(luts["nt"], 64, getattr(oracle, pred), ctx)
+    q, k, v = (_rand(oracle, (B, nb * 64, H, d), 1000 + i, dtype) for i in range(3))
+    ref = oracle.attention(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(), luts, 64,
+                           np.float32(0.125), mask_np=m_np, want=("p",))["p"]
+    odt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[out]
+    p = sfb.fused_sddmm_softmax(q, k, lay, 0.125, odt, use_mask=pred is not None).float().cpu().numpy()
+    assert sfb.device_status() == 0
+    tol = 2e-3 if out == "f32" else REL
+    assert np.abs(p - ref).max() <= tol * ref.max()
+    sums = oracle.blocks_to_dense(p, luts["nt"], nb, 64).sum(-1)
+    np.testing.assert_allclose(sums, 1.0, atol=1e-3 if out == "f32" else 2e-2)
