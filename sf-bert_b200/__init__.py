@@ -225,3 +225,47 @@ def bias_gelu(x, bias, out=None):
     out = torch.empty_like(x) if out is None else out
     _check(lib.sfb_bias_gelu(_stream(), _p(out), _p(x), _p(bias), m, n, dtype_tag(x)))
     return out
+
+
+class HostPipeline:
+    """Fused attention on operands that live in pinned HOST memory: the batch is cut into chunks and the
+    host->device copies, the kernel and the device->host copy of consecutive chunks overlap on three streams
+    (PCIe is full duplex, and the kernel is much shorter than either copy).  Device staging buffers are
+    allocated once, here; a call allocates nothing."""
+
+    def __init__(self, shape, dtype, lay, chunks=None, device="cuda"):
+        B = shape[0]
+        self.chunks = chunks or B
+        assert B % self.chunks == 0
+        self.lay = lay
+        self.q, self.k, self.v, self.o = (torch.empty(shape, dtype=dtype, device=device) for _ in range(4))
+        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(device=device) for _ in range(3))
+        self.ev_in = [torch.cuda.Event() for _ in range(self.chunks)]
+        self.ev_run = [torch.cuda.Event() for _ in range(self.chunks)]
+
+    def __call__(self, hq, hk, hv, ho, scale):
+        B = hq.shape[0]
+        per = B // self.chunks
+        cur = torch.cuda.current_stream()
+        start = torch.cuda.Event()
+        start.record(cur)
+        for s in (self.s_in, self.s_run, self.s_out):
+            s.wait_event(start)
+        for c in range(self.chunks):
+            sl = slice(c * per, (c + 1) * per)
+            with torch.cuda.stream(self.s_in):
+                self.q[sl].copy_(hq[sl], non_blocking=True)
+                self.k[sl].copy_(hk[sl], non_blocking=True)
+                self.v[sl].copy_(hv[sl], non_blocking=True)
+                self.ev_in[c].record(self.s_in)
+            with torch.cuda.stream(self.s_run):
+                self.s_run.wait_event(self.ev_in[c])
+                fused_attention(self.q[sl], self.k[sl], self.v[sl], self.lay, scale, out=self.o[sl])
+                self.ev_run[c].record(self.s_run)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(self.ev_run[c])
+                ho[sl].copy_(self.o[sl], non_blocking=True)
+        done = torch.cuda.Event()
+        done.record(self.s_out)
+        cur.wait_event(done)
+        return ho

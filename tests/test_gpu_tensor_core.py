@@ -227,3 +227,19 @@ def test_fused_sddmm_softmax_on_tensor_cores(sfb, oracle, dtype, out, pred, ctx)
     assert np.abs(p - ref).max() <= tol * ref.max()
     sums = oracle.blocks_to_dense(p, luts["nt"], nb, 64).sum(-1)
     np.testing.assert_allclose(sums, 1.0, atol=1e-3 if out == "f32" else 2e-2)
+
+
+def test_host_pipeline_matches_resident_call(sfb):
+    """Pinned host operands through the chunked, overlapped pipeline give the result of the resident call."""
+    B, L, H, d = 4, 1024, 3, 64
+    lay = sfb.BlockLayout.generate(sfb.LAYOUT_STRIDE, 1, L // 64, 64, p0=4, p1=8)
+    gen = torch.Generator(device="cuda").manual_seed(21)
+    q, k, v = (torch.randn(B, L, H, d, device="cuda", generator=gen).to(torch.bfloat16) for _ in range(3))
+    want = sfb.fused_attention(q, k, v, lay, 0.125)
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    ho = torch.empty_like(hq).pin_memory()
+    pipe = sfb.HostPipeline(tuple(q.shape), torch.bfloat16, lay, chunks=4)
+    for _ in range(2):
+        pipe(hq, hk, hv, ho, 0.125)
+        torch.cuda.synchronize()
+        assert torch.equal(ho, want.cpu())
