@@ -166,7 +166,7 @@ template <int BS, int X_DT, int Y_DT, int NB>
 __global__ void __launch_bounds__(BS * BS / 8) softmax_kernel(const uint2 *__restrict__ lut,
                                                         const typename MaskWord<BS>::type *__restrict__ mask,
                                                         const void *__restrict__ X, void *__restrict__ Y, AttnDims p,
-                                                        float scale_log2e)
+                                                        float scale_log2e, int rescale_in_place)
 {
     typedef typename MaskWord<BS>::type W;
     constexpr int LPR = BS / 8;  // lanes per query row
@@ -256,40 +256,97 @@ __global__ void __launch_bounds__(BS * BS / 8) softmax_kernel(const uint2 *__res
         return;
     }
 
+    // pass 1: the row maximum (packed bf16 max when there is no mask: 4 instructions per 8 scores)
     float mx = -INFINITY;
-    for (uint32_t e = 0; e < cnt; e++) {
-        const uint32_t blk = nn[off + e].x;
-        float v[8];
-        unpack8<X_DT>(v, load_raw8<X_DT>(X, base + (size_t)blk * BS * BS));
-        const uint32_t bits = mrow ? (uint32_t)((__ldg(mrow + blk) >> c0) & 0xffu) : 0xffu;
+    if (X_DT == SFB_BF16 && !mrow) {
+        uint32_t acc[4] = {0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u};   // pairs of -inf
+        for (uint32_t e = 0; e < cnt; e++) {
+            const uint32_t blk = nn[off + e].x;
+            const Raw8<X_DT> r8 = load_raw8<X_DT>(X, base + (size_t)blk * BS * BS);
+            const uint32_t w[4] = {r8.a.x, r8.a.y, r8.a.z, r8.a.w};
 #pragma unroll
-        for (int t = 0; t < 8; t++)
-            if ((bits >> t) & 1u) mx = fmaxf(mx, v[t]);
+            for (int t = 0; t < 4; t++) {
+                __nv_bfloat162 m2 = __hmax2(*reinterpret_cast<__nv_bfloat162 *>(&acc[t]), *reinterpret_cast<const __nv_bfloat162 *>(&w[t]));
+                acc[t] = *reinterpret_cast<uint32_t *>(&m2);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+            mx = fmaxf(mx, fmaxf(__uint_as_float(acc[t] << 16), __uint_as_float(acc[t] & 0xffff0000u)));
+    } else {
+        for (uint32_t e = 0; e < cnt; e++) {
+            const uint32_t blk = nn[off + e].x;
+            float v[8];
+            unpack8<X_DT>(v, load_raw8<X_DT>(X, base + (size_t)blk * BS * BS));
+            const uint32_t bits = mrow ? (uint32_t)((__ldg(mrow + blk) >> c0) & 0xffu) : 0xffu;
+#pragma unroll
+            for (int t = 0; t < 8; t++)
+                if ((bits >> t) & 1u) mx = fmaxf(mx, v[t]);
+        }
     }
 #pragma unroll
     for (int o = LPR / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     const float mxs = mx > -INFINITY ? mx * scale_log2e : 0.f;
+    // pass 2: one exponential per score; the unnormalised value goes to Y in the output type
     float sum = 0.f;
     for (uint32_t e = 0; e < cnt; e++) {
         const uint32_t blk = nn[off + e].x;
         float v[8];
         unpack8<X_DT>(v, load_raw8<X_DT>(X, base + (size_t)blk * BS * BS));
-        const uint32_t bits = mrow ? (uint32_t)((__ldg(mrow + blk) >> c0) & 0xffu) : 0xffu;
+        if (mrow) {
+            const uint32_t bits = (uint32_t)((__ldg(mrow + blk) >> c0) & 0xffu);
 #pragma unroll
-        for (int t = 0; t < 8; t++)
-            if ((bits >> t) & 1u) sum += ex2_fast(fmaf(v[t], scale_log2e, -mxs));
+            for (int t = 0; t < 8; t++) v[t] = ((bits >> t) & 1u) ? ex2_fast(fmaf(v[t], scale_log2e, -mxs)) : 0.f;
+        } else {
+#pragma unroll
+            for (int t = 0; t < 8; t++) v[t] = ex2_fast(fmaf(v[t], scale_log2e, -mxs));
+        }
+#pragma unroll
+        for (int t = 0; t < 8; t++) sum += v[t];
+        if (rescale_in_place) store8<Y_DT>(Y, base + (size_t)blk * BS * BS, v);
     }
 #pragma unroll
     for (int o = LPR / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     const float inv = sum > 0.f ? 1.f / sum : 0.f;
+    if (!rescale_in_place) {
+        // pass 3 for long rows (their Y would not stay in L2 between two passes): exponentials again, from X
+        for (uint32_t e = 0; e < cnt; e++) {
+            const uint32_t blk = nn[off + e].x;
+            float v[8];
+            unpack8<X_DT>(v, load_raw8<X_DT>(X, base + (size_t)blk * BS * BS));
+            const uint32_t bits = mrow ? (uint32_t)((__ldg(mrow + blk) >> c0) & 0xffu) : 0xffu;
+#pragma unroll
+            for (int t = 0; t < 8; t++) v[t] = ((bits >> t) & 1u) ? ex2_fast(fmaf(v[t], scale_log2e, -mxs)) * inv : 0.f;
+            store8<Y_DT>(Y, base + (size_t)blk * BS * BS, v);
+        }
+        return;
+    }
+    // pass 3: every thread rescales the values it wrote itself (they are still in L2): packed multiplies
     for (uint32_t e = 0; e < cnt; e++) {
         const uint32_t blk = nn[off + e].x;
-        float v[8];
-        unpack8<X_DT>(v, load_raw8<X_DT>(X, base + (size_t)blk * BS * BS));
-        const uint32_t bits = mrow ? (uint32_t)((__ldg(mrow + blk) >> c0) & 0xffu) : 0xffu;
+        const size_t idx = base + (size_t)blk * BS * BS;
+        if (Y_DT == SFB_F32) {
+            float4 *py = (float4 *)((float *)Y + idx);
+            float4 y0 = py[0], y1 = py[1];
+            py[0] = make_float4(y0.x * inv, y0.y * inv, y0.z * inv, y0.w * inv);
+            py[1] = make_float4(y1.x * inv, y1.y * inv, y1.z * inv, y1.w * inv);
+        } else {
+            uint4 *py = (uint4 *)((uint16_t *)Y + idx);
+            uint4 u = *py;
+            uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-        for (int t = 0; t < 8; t++) v[t] = ((bits >> t) & 1u) ? ex2_fast(fmaf(v[t], scale_log2e, -mxs)) * inv : 0.f;
-        store8<Y_DT>(Y, base + (size_t)blk * BS * BS, v);
+            for (int t = 0; t < 4; t++) {
+                if (Y_DT == SFB_BF16) {
+                    __nv_bfloat162 r2 = __hmul2(*reinterpret_cast<__nv_bfloat162 *>(&w[t]), __float2bfloat162_rn(inv));
+                    w[t] = *reinterpret_cast<uint32_t *>(&r2);
+                } else {
+                    const float2 f = __half22float2(*reinterpret_cast<__half2 *>(&w[t]));
+                    __half2 r2 = __floats2half2_rn(f.x * inv, f.y * inv);
+                    w[t] = *reinterpret_cast<uint32_t *>(&r2);
+                }
+            }
+            *py = make_uint4(w[0], w[1], w[2], w[3]);
+        }
     }
 }
 
@@ -600,9 +657,10 @@ int simt_softmax(cudaStream_t s, const void *lut, const void *mask, const void *
     const float sl = scale * LOG2E_F;
     // rows of up to 16 blocks (the caller's max_lut says so) stay in registers; 0 = unknown, stream
     // (only when the longest row nearly fills the register tile: measured slower than streaming otherwise)
+    const int inplace = max_lut != 0 && max_lut <= 12;   // short rows: unnormalised values wait in L2 for the rescale
     const int nb = (max_lut >= 3 && max_lut <= 4) ? 4 : (max_lut >= 7 && max_lut <= 8) ? 8 : (max_lut >= 14 && max_lut <= 16) ? 16 : 0;
 #define SM_LAUNCH(XD, NBV) \
-    DISPATCH_DT(y_dtype, YD, { softmax_kernel<BS, XD, YD, NBV><<<grid, BS * BS / 8, 0, s>>>((const uint2 *)lut, (const W *)mask, x, y, p, sl); })
+    DISPATCH_DT(y_dtype, YD, { softmax_kernel<BS, XD, YD, NBV><<<grid, BS * BS / 8, 0, s>>>((const uint2 *)lut, (const W *)mask, x, y, p, sl, inplace); })
 #define SM_BY_NB(XD) \
     if (nb == 4) { SM_LAUNCH(XD, 4) } else if (nb == 8) { SM_LAUNCH(XD, 8) } else if (nb == 16) { SM_LAUNCH(XD, 16) } else { SM_LAUNCH(XD, 0) }
     DISPATCH_BS(bs, {
