@@ -12,6 +12,8 @@ namespace tc {
 
 constexpr int kUStages = 4;
 
+static int make_p_map(CUtensorMap *map, const void *base, uint64_t rows, int is_bf16);
+
 struct UShared {
     uint64_t q_full, in_full[kUStages], in_empty[kUStages], s_full[2], s_empty[2], o_final, drained;
     uint32_t tmem_base, n_union, abort_flag, pad;
@@ -33,7 +35,7 @@ struct SdShared {
     uint64_t in_full[kSdStages], in_empty[kSdStages], s_full[2], s_empty[2], drained;
     uint32_t tmem_base, abort_flag;
 };
-constexpr size_t kSddmmSmem = 1024 + kSdStages * 2 * kTileBytes + sizeof(SdShared);
+constexpr size_t kSddmmSmem = 1024 + kSdStages * 2 * kTileBytes + 2 * kTileBytes /* output staging */ + sizeof(SdShared);
 constexpr size_t kSpmmSmem = 1024 + kUStages * (kQBytes + kTileBytes) + sizeof(UShared);
 
 __device__ __forceinline__ void store_row16(void *dst_base, size_t elem_off, const uint32_t (&v)[16], int out_dtype, int c0)
@@ -66,12 +68,14 @@ __device__ __forceinline__ void store_row16(void *dst_base, size_t elem_off, con
 constexpr uint32_t kChunk = 32;
 
 __global__ void __launch_bounds__(320, 4)
-sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap, const UParams p)
+sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+                const __grid_constant__ CUtensorMap omap, const UParams p)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *tiles = smem;                                   // stage s: Q rows (8 KB) then K rows (8 KB)
-    SdShared *st = (SdShared *)(tiles + kSdStages * 2 * kTileBytes);
+    uint8_t *stage_out = tiles + kSdStages * 2 * kTileBytes; // two 8 KB tiles of 16-bit scores on their way out
+    SdShared *st = (SdShared *)(stage_out + 2 * kTileBytes);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t b = blockIdx.y, h = blockIdx.z;
@@ -138,19 +142,54 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
         const uint32_t r = quarter * 32 + lane;
         const uint32_t lane_field = (quarter * 32) << 16;
         for (uint32_t t = 0; t < T; t++) {
-            if (!mbar_wait_warp(&st->s_full[t & 1], (t >> 1) & 1, abort_flag, 25)) break;
+            // the four drain warps leave together or not at all: they meet at named barriers below
+            const bool ok = mbar_wait_warp(&st->s_full[t & 1], (t >> 1) & 1, abort_flag, 25);
+            uint32_t all_ok;
+            asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.red.and.pred p, 2, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
+            if (!all_ok) break;
             tcgen05_fence_after();
             const size_t off = ((((size_t)b * p.H + h) * p.blocks + k0 + t) * 64 + r) * 64;
+            if (p.out_dtype == SFB_F32) {
 #pragma unroll
-            for (int c0 = cbase; c0 < cbase + 32; c0 += 16) {
-                uint32_t v[16];
-                TMEM_LD_16((v), tmem + 64 * (t & 1) + lane_field + c0);
-                tmem_wait_ld();
-                store_row16(p.out, off, v, p.out_dtype, c0);
+                for (int c0 = cbase; c0 < cbase + 32; c0 += 16) {
+                    uint32_t v[16];
+                    TMEM_LD_16((v), tmem + 64 * (t & 1) + lane_field + c0);
+                    tmem_wait_ld();
+                    store_row16(p.out, off, v, p.out_dtype, c0);
+                }
+            } else {
+                // 16-bit scores leave through shared memory and one TMA store per tile: rows of 128 bytes, 16-byte
+                // chunk c of row r at chunk c ^ (r % 8) (the tensor map's 128-byte swizzle)
+                const bool leader = warp == 4 && lane == 0;
+                if (leader) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the store that used this buffer has read it
+                asm volatile("bar.sync 4, 128;" ::: "memory");
+                uint8_t *orow = stage_out + (t & 1) * kTileBytes + r * 128;
+#pragma unroll
+                for (int c0 = cbase; c0 < cbase + 32; c0 += 16) {
+                    uint32_t v[16], w[8];
+                    TMEM_LD_16((v), tmem + 64 * (t & 1) + lane_field + c0);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 8; j++) w[j] = pack2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), p.out_dtype == SFB_BF16);
+                    const uint32_t ch = c0 >> 3;
+                    *(uint4 *)(orow + ((ch ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *(uint4 *)(orow + (((ch + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+                }
+                fence_proxy_async();
+                asm volatile("bar.sync 3, 128;" ::: "memory");
+                if (leader) {
+                    const int32_t y = (int32_t)((((size_t)b * p.H + h) * p.blocks + k0 + t) * 64);
+                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                                 ::"l"((uint64_t)&omap), "r"(smem_u32(stage_out + (t & 1) * kTileBytes)), "r"(0), "r"(y) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
             }
             tcgen05_fence_before();
             mbar_arrive(&st->s_empty[t & 1]);
         }
+        // shared memory must outlive the stores that read it
+        if (warp == 4 && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     }
 
     tcgen05_fence_before();
@@ -490,8 +529,11 @@ int tc_sddmm(cudaStream_t s, const void *nt_lut, const void *a, const void *b, v
     SFB_REQUIRE(p.nb_a == p.nb_b, "sfb_bst_sgemm_nt: ctx_blks_a != ctx_blks_b is not supported for 16-bit operands");
     const int is_bf16 = ab_dtype == SFB_BF16;
     const uint64_t rows = (uint64_t)p.B * p.nb_a * 64;
-    CUtensorMap qm, km;
+    CUtensorMap qm, km, om;
     if (make_map(&qm, a, rows, p.H, is_bf16, 64) || make_map(&km, b, rows, p.H, is_bf16, 64)) return 1;
+    // the scores as [B*H*blocks*64 rows, 64] for the TMA stores of 16-bit outputs (unused for fp32 outputs)
+    if (make_p_map(&om, c, (uint64_t)p.B * p.H * p.blocks * 64, c_dtype != SFB_F16)) return 1;
+    SFB_REQUIRE((uint64_t)p.B * p.H * p.blocks * 64 < (1ull << 31), "sfb_bst_sgemm_nt: too many blocks for one launch");
     UParams prm = {(const uint2 *)nt_lut, c, p.B, p.H, p.nb_a, p.blocks, p.lut_stride, c_dtype, is_bf16, 0};
     static bool configured = false;
     if (!configured) {
@@ -499,7 +541,7 @@ int tc_sddmm(cudaStream_t s, const void *nt_lut, const void *a, const void *b, v
             return fail("sfb_bst_sgemm_nt: cannot reserve %zu bytes of shared memory", kSddmmSmem);
         configured = true;
     }
-    sddmm_tc_kernel<<<dim3((p.blocks + kChunk - 1) / kChunk, p.B, p.H), 320, kSddmmSmem, s>>>(qm, km, prm);
+    sddmm_tc_kernel<<<dim3((p.blocks + kChunk - 1) / kChunk, p.B, p.H), 320, kSddmmSmem, s>>>(qm, km, om, prm);
     return check_launch("sfb_bst_sgemm_nt");
 }
 
