@@ -256,13 +256,16 @@ def run_bandwidth_kernel(args):
         fn = lambda: sfb.masked_softmax(x, lay, 0.125, torch.bfloat16)
         nbytes = x.numel() * 2 * 2
         name, unit_name = "softmax_kernel", "bf16 scores read + bf16 probabilities written"
-    elif args.kernel in ("sddmm", "spmm"):
+    elif args.kernel in ("sddmm", "spmm", "fused_p"):
         tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.bfloat16}[cfg["dtype"]]
         lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
         q, k = (torch.randn(B, L, H, d, device="cuda").to(tdt) for _ in range(2))
         if args.kernel == "sddmm":
             fn = lambda: sfb.bst_sgemm_nt(q, k, lay, torch.bfloat16)
             name, unit_name = "sddmm_tc_kernel", "bf16 scores written + Q, K read once"
+        elif args.kernel == "fused_p":
+            fn = lambda: sfb.fused_sddmm_softmax(q, k, lay, 0.125, torch.bfloat16)
+            name, unit_name = "fused_p_tc_kernel", "bf16 probabilities written + Q, K read once"
         else:
             pblk = torch.rand(B, H, lay.blocks, bs, bs, device="cuda").to(tdt)
             fn = lambda: sfb.bst_sgemm_xn(pblk, k, lay)
@@ -297,7 +300,7 @@ def run_bandwidth_kernel(args):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5), "higher_is_better": True,
         "dtype": "bf16" if args.kernel == "softmax" else cfg["dtype"], "data": "synthetic",
         "tflops_on_kept_blocks": (round(2.0 * bs * bs * d * lay.blocks * B * H / (ms * 1e-3) / 1e12, 1)
-                                  if args.kernel in ("sddmm", "spmm") else None),
+                                  if args.kernel in ("sddmm", "spmm", "fused_p") else None),
         "config": {"workload": args.config, "kernel": name, "bytes": unit_name, "l2": "flushed between timed steps"},
         "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm"], "unit": "GB/s",
                      "frac": round(gbs / pk["hbm"], 4), "traffic": None, "peak_source": pk["source"] + " copy bandwidth",
@@ -419,7 +422,7 @@ if __name__ == "__main__":
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="stride_bertbase", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "encoder_layer"],
+    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer"],
                     help="fused = the headline fused attention; softmax / layernorm = the bandwidth kernels (N=1)")
     a = ap.parse_args()
     if a.impl == "reference":
