@@ -30,7 +30,7 @@ struct SharedState {
     uint64_t s_full[2], p_full[2], pv_done, o_final, drained;
     uint32_t tmem_base, n_union, abort_flag, pad;
     UnionEntry entries[kMaxUnion];
-    uint8_t found[kMaxUnion];
+    uint2 cand[kMaxUnion];
 };
 
 constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + kQBytes + kStages * 2 * kTileBytes + kOnesBytes + sizeof(SharedState);
@@ -45,15 +45,6 @@ struct Params {
 };
 
 
-#ifdef SFB_TC_TIMING
-// per-phase cycle counts of one softmax lane and the MMA lane of one CTA (profiling builds only)
-__device__ unsigned long long g_timing[32];
-#define TIC(var) const long long var = clock64()
-#define TOC(slot, var) do { if (timing_on) atomicAdd(&g_timing[slot], (unsigned long long)(clock64() - var)); } while (0)
-#else
-#define TIC(var)
-#define TOC(slot, var)
-#endif
 
 // ---- the kernel ---------------------------------------------------------------------------------
 template <bool HAS_MASK, bool BF16>
@@ -92,6 +83,14 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
         mbar_init(&st->drained, 1);
         st->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // Q does not depend on the LUT: it travels while the union is built
+        mbar_expect_tx(&st->q_full, kQBytes);
+        tma_load_2d(smem_u32(q_tile), &qmap, &st->q_full, (int32_t)(h * 64), (int32_t)(b * L + pair * 128));
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&st->tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     {
         // 1.0 in the operand type of V, everywhere: the swizzle cannot matter
@@ -100,19 +99,11 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             ((uint4 *)ones_tile)[i] = make_uint4(one2, one2, one2, one2);
         fence_proxy_async();
     }
-    build_union(nn, pair, p.nb, st->entries, st->found, &st->n_union, &st->abort_flag);
-    if (warp == 0) {
-        __syncwarp();
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&st->tmem_base)), "r"(kTmemCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
+    build_union(nn, pair, p.nb, st->entries, st->cand, &st->n_union, &st->abort_flag);
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
 
-#ifdef SFB_TC_TIMING
-    const bool timing_on = blockIdx.x == 7 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 1 || warp == 2);
-#endif
     const uint32_t T = st->n_union;
     const uint32_t tmem = st->tmem_base;
     const uint32_t tmem_s[2] = {tmem, tmem + 64};
@@ -121,9 +112,7 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
 
     if (warp == 0) {
         // ===== TMA producer: a stage (K and V of one key block) is released when its P.V has completed =====
-        if (lane == 0 && T > 0) {
-            mbar_expect_tx(&st->q_full, kQBytes);
-            tma_load_2d(smem_u32(q_tile), &qmap, &st->q_full, xq, (int32_t)(b * L + pair * 128));
+        if (lane == 0) {
             for (uint32_t t = 0; t < T; t++) {
                 const uint32_t s = t % kStages;
                 const int32_t y = (int32_t)(b * L + st->entries[t].col * 64);
@@ -132,6 +121,7 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                 tma_load_2d(smem_u32(kv_tiles + s * 2 * kTileBytes), &kmap, &st->kv_full[s], xq, y);
                 tma_load_2d(smem_u32(kv_tiles + s * 2 * kTileBytes + kTileBytes), &vmap, &st->kv_full[s], xq, y);
             }
+            if (T == 0) mbar_wait(&st->q_full, 0, abort_flag, 2);   // nobody else waits for the Q tile then
         }
     } else if (warp == 1) {
         // ===== MMA issuer: S(0) | S(1) O(0) | S(2) O(1) | ...  S(t+1) lands in the buffer that held P(t-1); the
@@ -143,9 +133,7 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             bool alive = mbar_wait(&st->q_full, 0, abort_flag, 2);
             auto issue_qk = [&](uint32_t t) -> bool {
                 const uint32_t s = t % kStages;
-                TIC(c0);
                 if (!mbar_wait(&st->kv_full[s], (t / kStages) & 1, abort_flag, 3)) return false;
-                TOC(10, c0);
                 tcgen05_fence_after();
                 const uint64_t k_desc = smem_desc_sw128(smem_u32(kv_tiles + s * 2 * kTileBytes));
 #pragma unroll
@@ -158,9 +146,7 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             for (uint32_t t = 0; alive && t < T; t++) {
                 const uint32_t s = t % kStages;
                 if (t + 1 < T && !issue_qk(t + 1)) { alive = false; break; }
-                TIC(c2);
                 if (!mbar_wait(&st->p_full[t & 1], (t >> 1) & 1, abort_flag, 5)) { alive = false; break; }
-                TOC(12, c2);
                 tcgen05_fence_after();
                 // B = [V | ones]: 64 columns from the V tile, the next group of columns from the tile of ones
                 const uint32_t v_addr = smem_u32(kv_tiles + s * 2 * kTileBytes + kTileBytes);
@@ -184,96 +170,123 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
         const float sl = p.scale_log2e;
         float m_used = -INFINITY;
         bool alive = true;
-
-        TIC(c_loop);
-        for (uint32_t t = 0; t < T; t++) {
-            TIC(c0);
-            if (!mbar_wait_warp(&st->s_full[t & 1], (t >> 1) & 1, abort_flag, 6)) { alive = false; break; }
-            TOC(0, c0);
-            TIC(c1);
-            tcgen05_fence_after();
-            uint32_t sr[64];
-            TMEM_LD_32((sr), tmem_s[t & 1] + lane_field);
-            TMEM_LD_32((sr + 32), tmem_s[t & 1] + lane_field + 32);
-            tmem_wait_ld();
-            TOC(1, c1);
-            TIC(c2);
-
-            const UnionEntry ent = st->entries[t];
-            const bool mine = (ent.flags >> half) & 1;
-            float mx = -INFINITY;
-            if (mine) {
-                if (HAS_MASK) {
-                    const uint64_t w = p.mask[(size_t)h * p.mask_stride + (size_t)ent.blk[half] * 64 + (r & 63)];
-#pragma unroll
-                    for (int c = 0; c < 64; c++)
-                        if (!((w >> c) & 1)) sr[c] = 0xff800000u;
-                }
-                float m4[4];
-#pragma unroll
-                for (int c = 0; c < 4; c++) m4[c] = __uint_as_float(sr[c]);
-#pragma unroll
-                for (int c = 4; c < 64; c += 8) {
-#pragma unroll
-                    for (int j = 0; j < 4; j++)
-                        if (c + 2 * j + 1 < 64)
-                            m4[j] = max3(m4[j], __uint_as_float(sr[c + 2 * j]), __uint_as_float(sr[c + 2 * j + 1]));
-                }
-                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * sl;
-            }
-            // move the reference max only when the row max outgrew it by 2^8: rescaling O stays rare
-            const bool grow = mx > m_used + kRescaleThreshold || (m_used == -INFINITY && mx > -INFINITY);
-            const bool fix_o = grow && m_used > -INFINITY;
-            float alpha = 1.f;
-            if (grow) {
-                alpha = fix_o ? ex2_approx(m_used - mx) : 0.f;
-                m_used = mx;
-            }
-            if (t > 0 && __any_sync(0xffffffffu, fix_o)) {
-                // O (and the row sums next to it) must be complete before they are rescaled
-                if (!mbar_wait_warp(&st->pv_done, (t - 1) & 1, abort_flag, 7)) { alive = false; break; }
+        uint32_t sr[64];                                   // this row of S(t), fp32 bits
+        if (T > 0) {
+            alive = mbar_wait_warp(&st->s_full[0], 0, abort_flag, 6);
+            if (alive) {
                 tcgen05_fence_after();
-                const float a = fix_o ? alpha : 1.f;
-#pragma unroll
-                for (int c0 = 0; c0 < 80; c0 += 16) {
-                    uint32_t oc[16];
-                    TMEM_LD_16((oc), tmem_o + lane_field + c0);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int c = 0; c < 16; c++) oc[c] = __float_as_uint(__uint_as_float(oc[c]) * a);
-                    TMEM_ST_16(tmem_o + lane_field + c0, (oc));
-                }
-                tmem_wait_st();
+                TMEM_LD_32((sr), tmem_s[0] + lane_field);
+                TMEM_LD_32((sr + 32), tmem_s[0] + lane_field + 32);
             }
-            TOC(2, c2);
-            TIC(c3);
-            const float neg_m = m_used > -INFINITY ? -m_used : 0.f;
+        }
+        for (uint32_t t = 0; alive && t < T; t++) {
+            tmem_wait_ld();
+            const UnionEntry ent = st->entries[t];
+            const bool mine = (ent.flags >> half) & 1;     // the same for the whole warp
+            if (HAS_MASK && mine) {
+                const uint64_t w = p.mask[(size_t)h * p.mask_stride + (size_t)ent.blk[half] * 64 + (r & 63)];
+#pragma unroll
+                for (int c = 0; c < 64; c++)
+                    if (!((w >> c) & 1)) sr[c] = 0xff800000u;
+            }
             uint32_t pk[32];
-            if (mine) {
+            float mx = -INFINITY;
+            bool settle = true;
+            if (t > 0) {
+                // Speculate that the reference max still holds (it moves only when a row max outgrows it by
+                // 2^8): exponentials and the row max come out of ONE pass over the registers, so the max no
+                // longer sits in front of the MUFU work.  A warp that guessed wrong repeats the tile below.
+                if (mine) {
+                    const float neg_m = m_used > -INFINITY ? -m_used : 0.f;
+                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int c = 0; c < 64; c += 2) {
-                    float x0, x1;
-                    fma2(x0, x1, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]), sl, neg_m);
-                    const uint32_t e2 = ex2_pair_f16(x0, x1);
-                    pk[c >> 1] = BF16 ? f16x2_to_bf16x2(e2) : e2;
+                    for (int c = 0; c < 64; c += 2) {
+                        float x0, x1;
+                        m4[(c >> 1) & 3] = max3(m4[(c >> 1) & 3], __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
+                        fma2(x0, x1, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]), sl, neg_m);
+                        const uint32_t e2 = ex2_pair_f16(x0, x1);
+                        pk[c >> 1] = BF16 ? f16x2_to_bf16x2(e2) : e2;
+                    }
+                    mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * sl;
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; c++) pk[c] = 0u;
                 }
-            } else {
-#pragma unroll
-                for (int c = 0; c < 32; c++) pk[c] = 0u;
+                const bool grow = mx > m_used + kRescaleThreshold || (m_used == -INFINITY && mx > -INFINITY);
+                settle = __any_sync(0xffffffffu, grow);
             }
-            TOC(3, c3);
-            TIC(c5);
-            // P (16-bit pairs) takes the place of the first 32 columns of this row of S
+            if (settle) {
+                if (t == 0 && mine) {
+                    float m4[4];
+#pragma unroll
+                    for (int c = 0; c < 4; c++) m4[c] = __uint_as_float(sr[c]);
+#pragma unroll
+                    for (int c = 4; c < 64; c += 8) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            if (c + 2 * j + 1 < 64)
+                                m4[j] = max3(m4[j], __uint_as_float(sr[c + 2 * j]), __uint_as_float(sr[c + 2 * j + 1]));
+                    }
+                    mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * sl;
+                }
+                const bool grow = mx > m_used + kRescaleThreshold || (m_used == -INFINITY && mx > -INFINITY);
+                const bool fix_o = grow && m_used > -INFINITY;
+                float alpha = 1.f;
+                if (grow) {
+                    alpha = fix_o ? ex2_approx(m_used - mx) : 0.f;
+                    m_used = mx;
+                }
+                if (t > 0 && __any_sync(0xffffffffu, fix_o)) {
+                    // O (and the row sums next to it) must be complete before they are rescaled
+                    if (!mbar_wait_warp(&st->pv_done, (t - 1) & 1, abort_flag, 7)) { alive = false; break; }
+                    tcgen05_fence_after();
+                    const float a = fix_o ? alpha : 1.f;
+#pragma unroll
+                    for (int c0 = 0; c0 < 80; c0 += 16) {
+                        uint32_t oc[16];
+                        TMEM_LD_16((oc), tmem_o + lane_field + c0);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 16; c++) oc[c] = __float_as_uint(__uint_as_float(oc[c]) * a);
+                        TMEM_ST_16(tmem_o + lane_field + c0, (oc));
+                    }
+                    tmem_wait_st();
+                }
+                const float neg_m = m_used > -INFINITY ? -m_used : 0.f;
+                if (mine) {
+#pragma unroll
+                    for (int c = 0; c < 64; c += 2) {
+                        float x0, x1;
+                        fma2(x0, x1, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]), sl, neg_m);
+                        const uint32_t e2 = ex2_pair_f16(x0, x1);
+                        pk[c >> 1] = BF16 ? f16x2_to_bf16x2(e2) : e2;
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; c++) pk[c] = 0u;
+                }
+            }
+            // P (16-bit pairs) takes the place of the first 32 columns of this row of S; while that store is in
+            // flight the next tile's scores start their way into the registers
             TMEM_ST_32(tmem_s[t & 1] + lane_field, (pk));
+            // if S(t+1) is there already its load overlaps the store; P(t) is never held back waiting for it
+            const bool early = t + 1 < T && __all_sync(0xffffffffu, mbar_try_wait(&st->s_full[(t + 1) & 1], ((t + 1) >> 1) & 1));
+            if (early) {
+                tcgen05_fence_after();
+                TMEM_LD_32((sr), tmem_s[(t + 1) & 1] + lane_field);
+                TMEM_LD_32((sr + 32), tmem_s[(t + 1) & 1] + lane_field + 32);
+            }
             tmem_wait_st();
             tcgen05_fence_before();
             mbar_arrive(&st->p_full[t & 1]);
-            TOC(5, c5);
+            if (t + 1 < T && !early) {
+                if (!mbar_wait_warp(&st->s_full[(t + 1) & 1], ((t + 1) >> 1) & 1, abort_flag, 6)) { alive = false; break; }
+                tcgen05_fence_after();
+                TMEM_LD_32((sr), tmem_s[(t + 1) & 1] + lane_field);
+                TMEM_LD_32((sr + 32), tmem_s[(t + 1) & 1] + lane_field + 32);
+            }
         }
-        TOC(6, c_loop);
-#ifdef SFB_TC_TIMING
-        if (timing_on) atomicAdd(&g_timing[7], (unsigned long long)T);
-#endif
+        tmem_wait_ld();
 
         // ---- epilogue: O / row sum -> global ----
         if (T > 0 && alive) alive = mbar_wait_warp(&st->o_final, 0, abort_flag, 10);
@@ -369,18 +382,6 @@ int tc_fused_attention(cudaStream_t s, const void *nn_lut, const void *q, const 
     else fused_attention_tc_kernel<false, false><<<grid, 192, kSmemBytes, s>>>(qm, km, vm, prm);
     return check_launch("sfb_fused_attention");
 }
-
-#ifdef SFB_TC_TIMING
-extern "C" int sfb_debug_timing(unsigned long long *out, int reset)
-{
-    cudaMemcpyFromSymbol(out, tc::g_timing, sizeof(unsigned long long) * 32);
-    if (reset) {
-        unsigned long long z[32] = {0};
-        cudaMemcpyToSymbol(tc::g_timing, z, sizeof(z));
-    }
-    return 0;
-}
-#endif
 
 int tc_status_fused(uint32_t *out)
 {

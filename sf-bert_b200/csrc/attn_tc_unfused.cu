@@ -18,7 +18,7 @@ struct UShared {
     uint64_t q_full, in_full[kUStages], in_empty[kUStages], s_full[2], s_empty[2], o_final, drained;
     uint32_t tmem_base, n_union, abort_flag, pad;
     UnionEntry entries[kMaxUnion];
-    uint8_t found[kMaxUnion];
+    uint2 cand[kMaxUnion];
 };
 
 struct UParams {
@@ -239,7 +239,7 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap pmap, const __grid_constant__
         st->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    build_union(nn, pair, p.nb, st->entries, st->found, &st->n_union, &st->abort_flag);
+    build_union(nn, pair, p.nb, st->entries, st->cand, &st->n_union, &st->abort_flag);
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&st->tmem_base)), "r"(64u) : "memory");
@@ -368,7 +368,7 @@ fused_p_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         st->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    build_union(nn, pair, p.nb, st->entries, st->found, &st->n_union, &st->abort_flag);
+    build_union(nn, pair, p.nb, st->entries, st->cand, &st->n_union, &st->abort_flag);
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&st->tmem_base)), "r"(128u) : "memory");

@@ -213,10 +213,13 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int is_bf16)
                    "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])      \
                  : "memory")
 
-// Builds the union of the key blocks of block-rows 2*pair and 2*pair+1 in shared memory (all threads of the
-// CTA call it; it contains __syncthreads).  Returns through *n_out; 0 with *too_long set if it does not fit.
+// Builds the union of the key blocks of block-rows 2*pair and 2*pair+1 in shared memory: the upper row's
+// blocks in LUT order, then the blocks only the lower row has.  All threads of the CTA call it (it contains
+// __syncthreads); the result is complete after the caller's next __syncthreads.  cand is kMaxUnion words of
+// scratch.  Returns through *n_out; 0 with *abort_flag set if a row does not fit.  Two dependent global reads
+// deep (row headers, then both rows' entries at once); everything after that works from shared memory.
 __device__ __forceinline__ void build_union(const uint2 *nn, uint32_t pair, uint32_t nb, UnionEntry *entries,
-                                            uint8_t *found, uint32_t *n_out, uint32_t *abort_flag)
+                                            uint2 *cand, uint32_t *n_out, uint32_t *abort_flag)
 {
     const uint32_t row0 = pair * 2, row1 = pair * 2 + 1;
     const uint2 head0 = nn[row0];
@@ -224,49 +227,60 @@ __device__ __forceinline__ void build_union(const uint2 *nn, uint32_t pair, uint
     const uint32_t n0 = head0.y, n1 = head1.y;
     const bool fits = n0 <= kMaxUnion && n1 <= kMaxUnion;
     if (fits) {
-        for (uint32_t e = threadIdx.x; e < n0; e += blockDim.x) {
-            uint2 ent = nn[head0.x + e];
-            entries[e].col = ent.y;
-            entries[e].flags = 1;
-            entries[e].blk[0] = ent.x;
-            entries[e].blk[1] = 0;
+        for (uint32_t i = threadIdx.x; i < n0 + n1; i += blockDim.x) {
+            if (i < n0) {
+                const uint2 ent = nn[head0.x + i];
+                entries[i].col = ent.y;
+                entries[i].flags = 1;
+                entries[i].blk[0] = ent.x;
+                entries[i].blk[1] = 0;
+            } else {
+                cand[i - n0] = nn[head1.x + (i - n0)];
+            }
         }
     }
     __syncthreads();
     if (fits) {
+        // lower-row blocks the upper row has too: tag the existing entry, mark the candidate as placed
         for (uint32_t e = threadIdx.x; e < n1; e += blockDim.x) {
-            uint2 ent = nn[head1.x + e];
-            uint8_t f = 0;
+            const uint2 ent = cand[e];
             for (uint32_t u = 0; u < n0; u++)
                 if (entries[u].col == ent.y) {
                     entries[u].flags |= 2;
                     entries[u].blk[1] = ent.x;
-                    f = 1;
+                    cand[e].y = 0xffffffffu;
                     break;
                 }
-            found[e] = f;
         }
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (threadIdx.x < 32) {
+        // the rest are appended in order: ballot + prefix count per group of 32 candidates
         uint32_t n = n0;
         bool ok = fits;
-        for (uint32_t e = 0; ok && e < n1; e++)
-            if (!found[e]) {
-                if (n >= kMaxUnion) { ok = false; break; }
-                uint2 ent = nn[head1.x + e];
-                entries[n].col = ent.y;
-                entries[n].flags = 2;
-                entries[n].blk[0] = 0;
-                entries[n].blk[1] = ent.x;
-                n++;
+        for (uint32_t base = 0; ok && base < n1; base += 32) {
+            const uint32_t e = base + threadIdx.x;
+            const uint2 ent = e < n1 ? cand[e] : make_uint2(0, 0xffffffffu);
+            const bool fresh = ent.y != 0xffffffffu;
+            const uint32_t votes = __ballot_sync(0xffffffffu, fresh);
+            const uint32_t at = n + __popc(votes & ((1u << threadIdx.x) - 1u));
+            ok = n + __popc(votes) <= kMaxUnion;
+            if (ok && fresh) {
+                entries[at].col = ent.y;
+                entries[at].flags = 2;
+                entries[at].blk[0] = 0;
+                entries[at].blk[1] = ent.x;
             }
-        if (!ok) {
-            n = 0;
-            *abort_flag = 1;
-            atomicCAS(&g_status, 0u, (9u << 24) | (blockIdx.x & 0xffffffu));  // row pair too long for these kernels
+            n += __popc(votes);
         }
-        *n_out = n;
+        if (threadIdx.x == 0) {
+            if (!ok) {
+                n = 0;
+                *abort_flag = 1;
+                atomicCAS(&g_status, 0u, (9u << 24) | (blockIdx.x & 0xffffffu));  // row pair too long for these kernels
+            }
+            *n_out = n;
+        }
     }
 }
 
