@@ -31,6 +31,18 @@ void ref_softmax(float *C, float *A, float scaler, int seq_len, int batch, int h
     softmax<float, float>(C, A, scaler, seq_len, batch, heads);
 }
 
+/* ewops.h:103-122  dx = (dy - sum_row(dy*y)) * y * scaler, dense rows */
+void ref_softmax_grad(float *out, float *dy, float *y, float scaler, int batch, int heads, int seq_len)
+{
+    softmax_grad<float, float, float>(out, dy, y, scaler, batch, heads, seq_len);
+}
+
+/* matmul.h:81-99  C[b,h] = A[b,h]^T . B[b,h], A [mA,nA], B [mA,nB] */
+void ref_multiheadmatmulTN(float *C, float *A, float *B, int batch, int heads, int mA, int nA, int nB)
+{
+    multiheadmatmulTN<float, float, float>(C, A, B, batch, heads, mA, nA, nB);
+}
+
 /* ewops.h:314-331  [d0,d1,d2,d3] -> [d0,d2,d1,d3] */
 void ref_transpose_0123to0213(float *src, float *des, int d0, int d1, int d2, int d3)
 {

@@ -202,6 +202,44 @@ int orc_lut_build(const uint8_t *layout, uint32_t heads, uint32_t nb, uint32_t b
     return 0;
 }
 
+/* The column-major twin of nn_lut that the backward matmuls walk (bst_sgemm_xn with TN_OP,
+ * blocksparse.h:1005-1010).  The reference builds it for the dense causal layout only
+ * (generate_tn_lut, ewops.h:675-701): header[c] = (offset, count) of block column c with the
+ * offsets starting at nb, entries (block id in the row-major scan, row block) column by column,
+ * rows ascending.  This is that rule for any layout. */
+int orc_lut_build_tn(const uint8_t *layout, uint32_t heads, uint32_t nb, uint32_t blocks,
+                     uint32_t *tn_lut, uint32_t *tn_max)
+{
+    uint32_t maxc = 0;
+    for (uint32_t h = 0; h < heads; h++) {
+        uint32_t *tn = tn_lut + (size_t)h * (nb + blocks) * 2;
+        memset(tn, 0, sizeof(uint32_t) * 2 * (nb + blocks));
+        uint32_t total = 0;
+        for (uint32_t j = 0; j < nb; j++) {
+            uint32_t cnt = 0;
+            for (uint32_t i = 0; i < nb; i++) cnt += LAY(h, i, j) ? 1u : 0u;
+            tn[2 * j] = nb + total;
+            tn[2 * j + 1] = cnt;
+            total += cnt;
+            if (cnt > maxc) maxc = cnt;
+        }
+        if (total != blocks) return -1;
+        uint32_t id = 0;
+        uint32_t *fill = (uint32_t *)calloc(nb, sizeof(uint32_t));
+        if (!fill) return -1;
+        for (uint32_t i = 0; i < nb; i++)
+            for (uint32_t j = 0; j < nb; j++)
+                if (LAY(h, i, j)) {
+                    const uint32_t at = tn[2 * j] + fill[j]++;
+                    tn[2 * at] = id++;
+                    tn[2 * at + 1] = i;
+                }
+        free(fill);
+    }
+    if (tn_max) *tn_max = maxc;
+    return 0;
+}
+
 /* ------------------------------------------------------------------------------ */
 /* element masks                                                                    */
 static int keep_elem(int pred, uint32_t ctx, uint32_t bs, uint32_t bi, uint32_t bj, uint32_t r, uint32_t c)
@@ -458,3 +496,95 @@ void orc_magicu64(uint32_t d, uint32_t *magic, uint32_t *shift)
     *magic = 0;
     *shift = 0;
 }
+
+/* ------------------------------------------------------------------------------ */
+/* backward of the block-sparse path                                               */
+
+/* dx = (dy - sum over the query row of dy*y) * y * scale on the concatenated blocks of every query
+ * row (bst_masked_softmax_grad, blocksparse.h:1045-1157; CPU twin softmax_grad, ewops.h:103-122:
+ * float accumulation over the keys in ascending order). */
+void orc_softmax_grad(const float *dy, const float *y, const uint32_t *nn_lut,
+                      uint32_t B, uint32_t H, uint32_t nb, uint32_t bs, uint32_t blocks,
+                      uint32_t lut_heads, float scale, float *dx)
+{
+    const size_t blk = (size_t)bs * bs;
+#pragma omp parallel for schedule(static) collapse(2)
+    for (uint32_t b = 0; b < B; b++)
+        for (uint32_t h = 0; h < H; h++) {
+            const uint32_t *nn = nn_lut + (lut_heads > 1 ? (size_t)h * (nb + blocks) * 2 : 0);
+            const size_t base = ((size_t)b * H + h) * blocks * blk;
+            for (uint32_t i = 0; i < nb; i++) {
+                const uint32_t off = nn[2 * i], cnt = nn[2 * i + 1];
+                for (uint32_t r = 0; r < bs; r++) {
+                    float sum = 0.f;
+                    for (uint32_t e = 0; e < cnt; e++) {
+                        const size_t at = base + (size_t)nn[2 * (off + e)] * blk + (size_t)r * bs;
+                        for (uint32_t c = 0; c < bs; c++) sum += dy[at + c] * y[at + c];
+                    }
+                    for (uint32_t e = 0; e < cnt; e++) {
+                        const size_t at = base + (size_t)nn[2 * (off + e)] * blk + (size_t)r * bs;
+                        for (uint32_t c = 0; c < bs; c++) dx[at + c] = (dy[at + c] - sum) * y[at + c] * scale;
+                    }
+                }
+            }
+        }
+}
+
+/* C[b, rows of block COLUMN j, h, :] = sum over the blocks k of column j of A[b,h,k]^T . B[b, rows of
+ * row(k), h, :]  (bst_sgemm_xn with TN_OP, blocksparse.h:1005-1010; CPU twin multiheadmatmulTN,
+ * matmul.h:81-99: float accumulation over the query rows in ascending order).  a is
+ * [B,H,blocks,bs,bs], b and c are [B,L,H,d]; columns without blocks give zeros. */
+void orc_spmm_tn(const float *a, const float *bm, const uint32_t *tn_lut,
+                 uint32_t B, uint32_t H, uint32_t nb, uint32_t bs, uint32_t d, uint32_t blocks,
+                 uint32_t lut_heads, float *c)
+{
+    const size_t blk = (size_t)bs * bs, L = (size_t)nb * bs;
+#pragma omp parallel for schedule(static) collapse(2)
+    for (uint32_t b = 0; b < B; b++)
+        for (uint32_t h = 0; h < H; h++) {
+            const uint32_t *tn = tn_lut + (lut_heads > 1 ? (size_t)h * (nb + blocks) * 2 : 0);
+            for (uint32_t j = 0; j < nb; j++) {
+                const uint32_t off = tn[2 * j], cnt = tn[2 * j + 1];
+                for (uint32_t cc = 0; cc < bs; cc++)
+                    for (uint32_t x = 0; x < d; x++) {
+                        float sum = 0.f;
+                        for (uint32_t e = 0; e < cnt; e++) {
+                            const float *ab = a + (((size_t)b * H + h) * blocks + tn[2 * (off + e)]) * blk;
+                            const size_t row0 = (size_t)tn[2 * (off + e) + 1] * bs;
+                            for (uint32_t r = 0; r < bs; r++)
+                                sum += ab[(size_t)r * bs + cc] * bm[(((size_t)b * L + row0 + r) * H + h) * d + x];
+                        }
+                        c[(((size_t)b * L + (size_t)j * bs + cc) * H + h) * d + x] = sum;
+                    }
+            }
+        }
+}
+
+/* C[b, rows of block row i, h, :] = sum over the blocks k of row i of A[b,h,k] . B[b, rows of col(k), h, :]
+ * (bst_sgemm_xn with NN_OP, blocksparse.h:996-1003; CPU twin multiheadmatmulNN, matmul.h:6-20). */
+void orc_spmm_nn(const float *a, const float *bm, const uint32_t *nn_lut,
+                 uint32_t B, uint32_t H, uint32_t nb, uint32_t bs, uint32_t d, uint32_t blocks,
+                 uint32_t lut_heads, float *c)
+{
+    const size_t blk = (size_t)bs * bs, L = (size_t)nb * bs;
+#pragma omp parallel for schedule(static) collapse(2)
+    for (uint32_t b = 0; b < B; b++)
+        for (uint32_t h = 0; h < H; h++) {
+            const uint32_t *nn = nn_lut + (lut_heads > 1 ? (size_t)h * (nb + blocks) * 2 : 0);
+            for (uint32_t i = 0; i < nb; i++) {
+                const uint32_t off = nn[2 * i], cnt = nn[2 * i + 1];
+                for (uint32_t r = 0; r < bs; r++)
+                    for (uint32_t x = 0; x < d; x++) {
+                        float sum = 0.f;
+                        for (uint32_t e = 0; e < cnt; e++) {
+                            const float *ab = a + (((size_t)b * H + h) * blocks + nn[2 * (off + e)]) * blk + (size_t)r * bs;
+                            const size_t col0 = (size_t)nn[2 * (off + e) + 1] * bs;
+                            for (uint32_t cc = 0; cc < bs; cc++)
+                                sum += ab[cc] * bm[(((size_t)b * L + col0 + cc) * H + h) * d + x];
+                        }
+                        c[(((size_t)b * L + (size_t)i * bs + r) * H + h) * d + x] = sum;
+                    }
+            }
+        }
+}
+

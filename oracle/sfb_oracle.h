@@ -69,6 +69,12 @@ int orc_lut_count(const uint8_t *layout, uint32_t heads, uint32_t nb, uint32_t *
 int orc_lut_build(const uint8_t *layout, uint32_t heads, uint32_t nb, uint32_t blocks,
                   uint32_t *nt_lut, uint32_t *nn_lut, uint32_t *rblk_lut, uint32_t *nn_max);
 
+/* tn_lut [heads][nb+blocks][2]: the same structure walked by block COLUMN -- header (x = offset, y = count),
+ * entries (x = block id, y = row block), rows ascending (generate_tn_lut, ewops.h:675-701, which covers the
+ * dense causal layout only).  tn_max = largest column count over all heads. */
+int orc_lut_build_tn(const uint8_t *layout, uint32_t heads, uint32_t nb, uint32_t blocks,
+                     uint32_t *tn_lut, uint32_t *tn_max);
+
 /* ---- element masks (stride_fusion_test.cu:142-179, no_fusion_test.cu:124-165,
  *      local_fusion_test.cu:146-202) ------------------------------------------------ */
 enum {
@@ -120,6 +126,26 @@ void orc_bias_residual_layernorm(float *out, float *sum_out, float *mean, float 
 /* out = t * (1 / (exp(-1.702 t) + 1)), t = x + bias (ewops.h:10-17 then ewops.h:32-43: the exponential in
  * double of the float product, the reciprocal and the result in float).  bias may be NULL. */
 void orc_bias_gelu(float *out, const float *x, const float *bias, uint32_t m, uint32_t n);
+
+/* ---- backward of the block-sparse path (call order transformer_attention_optimize.cu:924-964) ---- */
+
+/* dx = (dy - sum_row(dy*y)) * y * scale over the concatenated blocks of every query row; dy, y, dx are
+ * [B][H][blocks][bs][bs] (bst_masked_softmax_grad, blocksparse.h:1045-1157; softmax_grad, ewops.h:103-122). */
+void orc_softmax_grad(const float *dy, const float *y, const uint32_t *nn_lut,
+                      uint32_t B, uint32_t H, uint32_t nb, uint32_t bs, uint32_t blocks,
+                      uint32_t lut_heads, float scale, float *dx);
+
+/* C = A^T . B walked by block column with the tn_lut (bst_sgemm_xn TN_OP, blocksparse.h:1005-1010;
+ * multiheadmatmulTN, matmul.h:81-99): dV = P^T dO and dK = dS^T Q. */
+void orc_spmm_tn(const float *a, const float *b, const uint32_t *tn_lut,
+                 uint32_t B, uint32_t H, uint32_t nb, uint32_t bs, uint32_t d, uint32_t blocks,
+                 uint32_t lut_heads, float *c);
+
+/* C = A . B walked by block row with the nn_lut (bst_sgemm_xn NN_OP; multiheadmatmulNN, matmul.h:6-20):
+ * O = P V and dQ = dS K. */
+void orc_spmm_nn(const float *a, const float *b, const uint32_t *nn_lut,
+                 uint32_t B, uint32_t H, uint32_t nb, uint32_t bs, uint32_t d, uint32_t blocks,
+                 uint32_t lut_heads, float *c);
 
 /* magic-number division constants (blocksparse.h:1016-1043) */
 void orc_magicu64(uint32_t d, uint32_t *magic, uint32_t *shift);

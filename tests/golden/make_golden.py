@@ -1,4 +1,4 @@
-"""Regenerates tests/golden/ref_uploads.npz and tests/golden/ref_cpu_attention.npz.
+"""Regenerates tests/golden/ref_uploads.npz, tests/golden/ref_cpu_attention.npz and tests/golden/ref_cpu_backward.npz.
 
 Needs the reference tree (read-only) and a C/CUDA toolchain, but no GPU:
 
@@ -12,6 +12,8 @@ Needs the reference tree (read-only) and a C/CUDA toolchain, but no GPU:
    from a variable it never initialises (fixed_fusion_test.cu:46,109-115) and crashes.
 2. ref_cpu_attention.npz -- outputs of the reference's own CPU operators (matmul.h,
    ewops.h, layernorm.h through oracle/_ref/libsfb_ref.so) on small seeded inputs.
+3. ref_cpu_backward.npz -- the same operators run in the backward order of transformer.cpp:676-688
+   (multiheadmatmulNT, multiheadmatmulTN, softmax_grad, multiheadmatmulNN, multiheadmatmulTN).
 """
 import os
 import re
@@ -90,8 +92,23 @@ def cpu_reference():
     return out
 
 
+def cpu_reference_backward():
+    """Backward of attention by the reference's own CPU operators (transformer.cpp:676-688): the forward
+    probabilities come from the same operators, dO from the seeded generator."""
+    import oracle_lib as O
+    B, L, H, d = 1, 96, 2, 32
+    q, k, v, do = (O.fill_normal((B, L, H, d), s) for s in (41, 42, 43, 44))
+    scale = np.float32(1.0 / np.sqrt(d))
+    _, p, _ = O.ref_dense_causal_attention(q, k, v, scale)
+    t = lambda a: np.ascontiguousarray(a.transpose(0, 2, 1, 3))     # [B,L,H,d] -> [B,H,L,d]
+    dp, ds, dq, dk, dv = O.ref_dense_backward(p, t(do), t(q), t(k), t(v), scale)
+    return {"bwd/shape": np.array([B, L, H, d]), "bwd/seeds": np.array([41, 42, 43, 44]), "bwd/p": p, "bwd/dp": dp,
+            "bwd/ds": ds, "bwd/dq": dq, "bwd/dk": dk, "bwd/dv": dv}
+
+
 if __name__ == "__main__":
     ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     np.savez_compressed(os.path.join(HERE, "ref_uploads.npz"), **capture(ref))
     np.savez_compressed(os.path.join(HERE, "ref_cpu_attention.npz"), **cpu_reference())
+    np.savez_compressed(os.path.join(HERE, "ref_cpu_backward.npz"), **cpu_reference_backward())
     print("wrote", os.listdir(HERE))

@@ -110,6 +110,19 @@ def lut_build(lay):
     return dict(nt=nt, nn=nn, rblk=rb, nn_max=mx.value, blocks=blocks)
 
 
+def lut_build_tn(lay):
+    """-> dict(tn [heads, nb+blocks, 2], tn_max, blocks): the LUT of the backward (TN) matmuls."""
+    lay = np.ascontiguousarray(lay, dtype=np.uint8)
+    heads, nb, _ = lay.shape
+    blocks = lut_count(lay)
+    tn = np.zeros((heads, nb + blocks, 2), np.uint32)
+    mx = C.c_uint32(0)
+    rc = lib().orc_lut_build_tn(_ptr(lay, _u8p), C.c_uint32(heads), C.c_uint32(nb), C.c_uint32(blocks),
+                                _ptr(tn, _u32p), C.byref(mx))
+    assert rc == 0
+    return dict(tn=tn, tn_max=mx.value, blocks=blocks)
+
+
 _WORD = {8: np.uint8, 16: np.uint16, 32: np.uint32, 64: np.uint64}
 
 
@@ -148,6 +161,41 @@ def attention(q, k, v, luts, bs, scale, mask_np=None, eps=1e-6, round_s_bf16=Fal
                         C.c_float(scale), C.c_float(eps), C.c_int(int(round_s_bf16)),
                         _ptr(s, _f32p), _ptr(p, _f32p), _ptr(o, _f32p))
     return dict(s=s, p=p, o=o)
+
+
+def softmax_grad(dy, y, luts, bs, scale):
+    """dy, y float32 [B,H,blocks,bs,bs] -> dx, same shape."""
+    dy = np.ascontiguousarray(dy, np.float32)
+    y = np.ascontiguousarray(y, np.float32)
+    B, H, blocks, _, _ = dy.shape
+    nn = luts["nn"]
+    nb = nn.shape[1] - blocks
+    dx = np.zeros_like(dy)
+    lib().orc_softmax_grad(_ptr(dy, _f32p), _ptr(y, _f32p), _ptr(nn, _u32p), C.c_uint32(B), C.c_uint32(H),
+                           C.c_uint32(nb), C.c_uint32(bs), C.c_uint32(blocks), C.c_uint32(nn.shape[0]),
+                           C.c_float(scale), _ptr(dx, _f32p))
+    return dx
+
+
+def _spmm(fn, a, b, lut, bs):
+    a = np.ascontiguousarray(a, np.float32)
+    b = np.ascontiguousarray(b, np.float32)
+    B, H, blocks, _, _ = a.shape
+    _, L, _, d = b.shape
+    c = np.zeros_like(b)
+    fn(_ptr(a, _f32p), _ptr(b, _f32p), _ptr(lut, _u32p), C.c_uint32(B), C.c_uint32(H), C.c_uint32(L // bs),
+       C.c_uint32(bs), C.c_uint32(d), C.c_uint32(blocks), C.c_uint32(lut.shape[0]), _ptr(c, _f32p))
+    return c
+
+
+def spmm_tn(a, b, tn, bs):
+    """a [B,H,blocks,bs,bs], b [B,L,H,d] -> c [B,L,H,d] = A^T . B by block column."""
+    return _spmm(lib().orc_spmm_tn, a, b, tn, bs)
+
+
+def spmm_nn(a, b, nn, bs):
+    """a [B,H,blocks,bs,bs], b [B,L,H,d] -> c [B,L,H,d] = A . B by block row."""
+    return _spmm(lib().orc_spmm_nn, a, b, nn, bs)
 
 
 def bias_residual_layernorm(x, bias, resid, gain, beta):
@@ -231,6 +279,28 @@ def ref_dense_causal_attention(q, k, v, scale):
     o = np.zeros((B, L, H, d), np.float32)
     R.ref_transpose_0123to0213(_ptr(to, _f32p), _ptr(o, _f32p), C.c_int(B), C.c_int(H), C.c_int(L), C.c_int(d))
     return s, p, o
+
+
+def ref_dense_backward(p, do, q, k, v, scale):
+    """The reference's own CPU backward of attention (transformer.cpp:676-688 order) on dense [B,H,L,*]
+    operands: dP = dO V^T, dV = P^T dO, dS = softmax_grad(dP, P), dQ = dS K, dK = dS^T Q.
+    p [B,H,L,L]; do, q, k, v [B,H,L,d].  Returns (dp, ds, dq, dk, dv)."""
+    R = ref()
+    assert R is not None, "oracle/_ref/libsfb_ref.so not built"
+    B, H, L, d = q.shape
+    p, do, q, k, v = (np.ascontiguousarray(t, np.float32) for t in (p, do, q, k, v))
+    i = C.c_int
+    dp = np.zeros((B, H, L, L), np.float32)
+    R.ref_multiheadmatmulNT(_ptr(dp, _f32p), _ptr(do, _f32p), _ptr(v, _f32p), i(B), i(H), i(L), i(d), i(L))
+    dv = np.zeros((B, H, L, d), np.float32)
+    R.ref_multiheadmatmulTN(_ptr(dv, _f32p), _ptr(p, _f32p), _ptr(do, _f32p), i(B), i(H), i(L), i(L), i(d))
+    ds = np.zeros((B, H, L, L), np.float32)
+    R.ref_softmax_grad(_ptr(ds, _f32p), _ptr(dp, _f32p), _ptr(p, _f32p), C.c_float(scale), i(B), i(H), i(L))
+    dq = np.zeros((B, H, L, d), np.float32)
+    R.ref_multiheadmatmulNN(_ptr(dq, _f32p), _ptr(ds, _f32p), _ptr(k, _f32p), i(B), i(H), i(L), i(L), i(d))
+    dk = np.zeros((B, H, L, d), np.float32)
+    R.ref_multiheadmatmulTN(_ptr(dk, _f32p), _ptr(ds, _f32p), _ptr(q, _f32p), i(B), i(H), i(L), i(L), i(d))
+    return dp, ds, dq, dk, dv
 
 
 def ref_bias_residual_layernorm(x, bias, resid, gain, beta):

@@ -166,3 +166,87 @@ def test_gelu_matches_live_reference_when_built(oracle):
     x = oracle.fill_normal((7, 96), 41, 2.0)
     b = oracle.fill_normal((96,), 42, 0.5)
     assert np.array_equal(oracle.bias_gelu(x, b), oracle.ref_bias_gelu(x, b))
+
+
+def test_tn_lut_matches_reference_generator():
+    """generate_tn_lut (ewops.h:675-701; inlined in test.cu:139-170) writes, for the dense causal
+    layout, header[c] = (running offset starting at nb, nb - c) and entries (row*(row+1)/2 + col, row)
+    column by column.  The layout-driven builder must reproduce exactly that."""
+    import oracle_lib as O
+    nb = 10
+    got = O.lut_build_tn(O.layout("full", 1, nb, causal=1))
+    blocks = nb * (nb + 1) // 2
+    want = np.zeros((nb + blocks, 2), np.uint32)
+    total, cnt = nb, nb
+    for c in range(nb):
+        want[c] = (total, cnt)
+        total += cnt
+        cnt -= 1
+    at = nb
+    for col in range(nb):
+        for row in range(col, nb):
+            want[at] = (row * (row + 1) // 2 + col, row)
+            at += 1
+    assert got["blocks"] == blocks and got["tn_max"] == nb
+    assert np.array_equal(got["tn"][0], want)
+
+
+@pytest.mark.parametrize("kind,kw", [("stride", dict(band=4, every=8)), ("bigbird", dict(window=1, g_first=1, g_last=1, nrand=3, seed=7)),
+                                     ("fixed", dict(stride=4))])
+def test_tn_lut_is_the_transpose_of_nn_lut(kind, kw):
+    """Every block appears once in each LUT with the same id; tn walks columns, nn walks rows."""
+    import oracle_lib as O
+    heads, nb = (4, 16) if kind == "fixed" else (1, 16)
+    lay = O.layout(kind, heads, nb, **kw)
+    nn, tn = O.lut_build(lay), O.lut_build_tn(lay)
+    for h in range(heads):
+        seen = {}
+        for i in range(nb):
+            off, cnt = nn["nn"][h, i]
+            for e in range(cnt):
+                blk, col = nn["nn"][h, off + e]
+                seen[int(blk)] = (i, int(col))
+        back = {}
+        for j in range(nb):
+            off, cnt = tn["tn"][h, j]
+            rows = [int(tn["tn"][h, off + e, 1]) for e in range(cnt)]
+            assert rows == sorted(rows)
+            for e in range(cnt):
+                blk, row = tn["tn"][h, off + e]
+                back[int(blk)] = (int(row), j)
+        assert seen == back and len(seen) == nn["blocks"]
+        assert tn["tn_max"] == int(lay.sum(axis=1).max())
+
+
+def test_backward_matches_reference_cpu_operators(oracle):
+    """softmax grad, TN and NN products of the oracle against the reference's own CPU operators on the
+    dense causal layout (fixture made by tests/golden/make_golden.py): bit-exact, same operation order."""
+    g = np.load(os.path.join(GOLD, "ref_cpu_backward.npz"))
+    B, L, H, d = (int(x) for x in g["bwd/shape"])
+    q, k, v, do = (oracle.fill_normal((B, L, H, d), int(s)) for s in g["bwd/seeds"])
+    bs, nb = 32, L // 32
+    lay = oracle.layout("full", 1, nb, causal=1)
+    luts, tn = oracle.lut_build(lay), oracle.lut_build_tn(lay)["tn"]
+    scale = np.float32(1.0 / np.sqrt(d))
+
+    def to_blocks(dense):          # [B,H,L,L] -> [B,H,blocks,bs,bs]
+        out = np.zeros((B, H, luts["blocks"], bs, bs), np.float32)
+        for kk, (i, j) in enumerate(luts["nt"][0]):
+            out[:, :, kk] = dense[:, :, i * bs:(i + 1) * bs, j * bs:(j + 1) * bs]
+        return out
+
+    bhld = lambda a: a.transpose(0, 2, 1, 3)    # [B,H,L,d] <-> [B,L,H,d]
+    p_blk = to_blocks(g["bwd/p"])
+    # dP = dO V^T on the kept blocks: the scores of the forward oracle with (q, k) := (dO, V)
+    dp = oracle.attention(do, v, v, luts, bs, scale, want=("s",))["s"]
+    tri = np.tril(np.ones((L, L), bool))
+    assert np.array_equal(np.where(tri, oracle.blocks_to_dense(dp, luts["nt"], nb, bs), 0), np.where(tri, g["bwd/dp"], 0))
+    # dV = P^T dO
+    assert np.array_equal(bhld(oracle.spmm_tn(p_blk, do, tn, bs)), g["bwd/dv"])
+    # dS: the reference sums dy*y over the whole dense row; the products outside the triangle are exact zeros
+    ds = oracle.softmax_grad(to_blocks(g["bwd/dp"]), p_blk, luts, bs, scale)
+    assert np.array_equal(oracle.blocks_to_dense(ds, luts["nt"], nb, bs), g["bwd/ds"])
+    # dQ = dS K, dK = dS^T Q
+    assert np.array_equal(bhld(oracle.spmm_nn(ds, k, luts["nn"], bs)), g["bwd/dq"])
+    assert np.array_equal(bhld(oracle.spmm_tn(ds, q, tn, bs)), g["bwd/dk"])
+
