@@ -256,6 +256,20 @@ def run_bandwidth_kernel(args):
         fn = lambda: sfb.masked_softmax(x, lay, 0.125, torch.bfloat16)
         nbytes = x.numel() * 2 * 2
         name, unit_name = "softmax_kernel", "bf16 scores read + bf16 probabilities written"
+    elif args.kernel == "softmax_grad":
+        lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
+        dy = torch.randn(B, H, lay.blocks, bs, bs, device="cuda").to(torch.bfloat16)
+        y = torch.rand(B, H, lay.blocks, bs, bs, device="cuda").to(torch.bfloat16)
+        fn = lambda: sfb.masked_softmax_grad(dy, y, lay, 0.125)
+        nbytes = dy.numel() * 2 * 3
+        name, unit_name = "softmax_grad_kernel", "bf16 dy and y read + bf16 dx written"
+    elif args.kernel == "spmm_tn":
+        lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
+        pblk = torch.rand(B, H, lay.blocks, bs, bs, device="cuda").to(torch.bfloat16)
+        do = torch.randn(B, L, H, d, device="cuda")
+        fn = lambda: sfb.bst_sgemm_tn(pblk, do, lay)
+        nbytes = pblk.numel() * 2 + 2 * do.numel() * 4
+        name, unit_name = "spmm_nn_kernel<TRANS>", "bf16 blocks read + fp32 B read once + fp32 C written (the reference's types)"
     elif args.kernel in ("sddmm", "spmm", "fused_p"):
         tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.bfloat16}[cfg["dtype"]]
         lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
@@ -298,9 +312,9 @@ def run_bandwidth_kernel(args):
     print(json.dumps({
         "metric": args.kernel + " GB/s (algorithmic bytes)", "value": round(gbs, 1), "unit": "GB/s", "n_gpus": 1,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5), "higher_is_better": True,
-        "dtype": "bf16" if args.kernel == "softmax" else cfg["dtype"], "data": "synthetic",
+        "dtype": "bf16" if args.kernel in ("softmax", "softmax_grad", "spmm_tn") else cfg["dtype"], "data": "synthetic",
         "tflops_on_kept_blocks": (round(2.0 * bs * bs * d * lay.blocks * B * H / (ms * 1e-3) / 1e12, 1)
-                                  if args.kernel in ("sddmm", "spmm", "fused_p") else None),
+                                  if args.kernel in ("sddmm", "spmm", "fused_p", "spmm_tn") else None),
         "config": {"workload": args.config, "kernel": name, "bytes": unit_name, "l2": "flushed between timed steps"},
         "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm"], "unit": "GB/s",
                      "frac": round(gbs / pk["hbm"], 4), "traffic": None, "peak_source": pk["source"] + " copy bandwidth",
@@ -422,7 +436,7 @@ if __name__ == "__main__":
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="stride_bertbase", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer"],
+    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer", "softmax_grad", "spmm_tn"],
                     help="fused = the headline fused attention; softmax / layernorm = the bandwidth kernels (N=1)")
     a = ap.parse_args()
     if a.impl == "reference":

@@ -70,7 +70,7 @@ bool BlocksparseMaskedSoftmax_nosl(CUstream stream, const uint2 *lut, const uint
                                           lut_heads, lut_dim, max_lut, mask_heads, scale);
 }
 
-/* blocksparse.h:965-972 (op = NN_OP; the backward TN_OP is rejected) */
+/* blocksparse.h:965-972 (op = NN_OP with the nn_lut, or TN_OP with the tn_lut for the backward products) */
 inline bool bst_sgemm_xn(CUstream stream, const uint2 *lut, const bhalf *a, const float *b, float *c,
                          uint block_size, uint blocks, uint batch_dim, uint ctx_blks_b, uint ctx_blks_c,
                          uint head_dim, uint state_dim, uint lut_heads, uint lut_dim, uint op, uint magic,
@@ -78,6 +78,16 @@ inline bool bst_sgemm_xn(CUstream stream, const uint2 *lut, const bhalf *a, cons
 {
     return sfb_bst_sgemm_xn(stream, lut, a, b, c, SFB_BF16, SFB_F32, block_size, blocks, batch_dim, ctx_blks_b,
                             ctx_blks_c, head_dim, state_dim, lut_heads, lut_dim, op, magic, shift, max_lut) == 0;
+}
+
+/* blocksparse.h:1164-1173; V is the reference's vector type of T and plays no role here.  lut is the nn_lut. */
+template <typename T, typename V>
+bool BlocksparseMaskedSoftmaxGrad(CUstream stream, const uint2 *lut, const T *dy, const T *y, T *dx, uint block_size,
+                                  uint blocks, uint batch_dim, uint head_dim, uint ctx_blks, uint lut_heads,
+                                  uint lut_dim, uint max_lut, float scale)
+{
+    return sfb_masked_softmax_grad(stream, lut, dy, y, dx, sfb_dropin::dtype_of<T>::value, block_size, blocks, batch_dim,
+                                   head_dim, ctx_blks, lut_heads, lut_dim, max_lut, scale) == 0;
 }
 
 /* blocksparse.h:1016 */

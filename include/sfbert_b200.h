@@ -78,6 +78,16 @@ int sfb_lut_build(sfb_stream_t stream, const uint8_t *layout, uint32_t heads, ui
                   uint32_t blocks, void *nt_lut, void *nn_lut, void *rblk_lut,
                   uint32_t *nn_max, uint32_t *status);
 
+/* Builds, in device memory, the LUT the backward matmuls walk (sfb_bst_sgemm_xn with SFB_TN_OP):
+ *   tn_lut   uint2 [heads][nb + blocks]  header per block COLUMN (x = offset, y = count), then
+ *                                        (x = block id, y = row block), rows ascending
+ *   tn_max   uint32 [1]                  longest column over all heads            (may be NULL)
+ * Block ids are those of sfb_lut_build (row-major scan).  Replaces generate_tn_lut (ewops.h:675-701,
+ * inlined in test.cu:139-170), which the reference has for the dense causal layout only.  status as in
+ * sfb_lut_build. */
+int sfb_lut_build_tn(sfb_stream_t stream, const uint8_t *layout, uint32_t heads, uint32_t nb,
+                     uint32_t blocks, void *tn_lut, uint32_t *tn_max, uint32_t *status);
+
 /* Packs element masks: bit c of word r of block k = keep(r, c).
  *   mask_np [heads][blocks][block_size]  (the fused kernels' order, fusion_blocksparse.h:690)
  *   mask_t  [heads][block_size][blocks]  (the unfused softmax's order, blocksparse.h:482)
@@ -110,14 +120,27 @@ int sfb_masked_softmax(sfb_stream_t stream, const void *lut, const void *mask, c
                        uint32_t lut_heads, uint32_t lut_dim, uint32_t max_lut,
                        uint32_t mask_heads, float scale);
 
-/* SpMM: O[b, rows of block-row i, h, :] = sum over the row's blocks k of P[b,h,k] . V[b, rows of
- * column block of k, h, :].  op must be SFB_NN_OP.  magic/shift are accepted and ignored.
- * Replaces bst_sgemm_xn (blocksparse.h:965-1014) for the forward (NN) case. */
+/* SpMM.  op = SFB_NN_OP (forward, lut = nn_lut): O[b, rows of block-row i, h, :] = sum over the row's
+ * blocks k of P[b,h,k] . V[b, rows of column block of k, h, :]; also dQ = dS K.
+ * op = SFB_TN_OP (backward, lut = tn_lut of sfb_lut_build_tn): C[b, rows of block COLUMN j, h, :] = sum over
+ * the column's blocks k of A[b,h,k]^T . B[b, rows of row block of k, h, :]: dV = P^T dO, dK = dS^T Q
+ * (call sites transformer_attention_optimize.cu:924,954,964).  magic/shift are accepted and ignored.
+ * Replaces bst_sgemm_xn (blocksparse.h:965-1014). */
 int sfb_bst_sgemm_xn(sfb_stream_t stream, const void *lut, const void *a, const void *b, void *c,
                      int a_dtype, int bc_dtype, uint32_t block_size, uint32_t blocks,
                      uint32_t batch_dim, uint32_t ctx_blks_b, uint32_t ctx_blks_c,
                      uint32_t head_dim, uint32_t state_dim, uint32_t lut_heads, uint32_t lut_dim,
                      uint32_t op, uint32_t magic, uint32_t shift, uint32_t max_lut);
+
+/* dx = (dy - sum over the query row of dy*y) * y * scale on the concatenated blocks of every query row;
+ * dy, y and dx are [B, H, blocks, block_size, block_size] of one type (the reference has bf16 and fp32).
+ * lut is the nn_lut, lut_dim its per-head stride; max_lut as for sfb_masked_softmax (0 = unknown).
+ * Replaces BlocksparseMaskedSoftmaxGrad<T,V> (blocksparse.h:1164-1227; call site
+ * transformer_attention_optimize.cu:944); CPU twin softmax_grad, ewops.h:103-122. */
+int sfb_masked_softmax_grad(sfb_stream_t stream, const void *lut, const void *dy, const void *y, void *dx,
+                            int dtype, uint32_t block_size, uint32_t blocks, uint32_t batch_dim,
+                            uint32_t head_dim, uint32_t ctx_blks, uint32_t lut_heads, uint32_t lut_dim,
+                            uint32_t max_lut, float scale);
 
 /* ---- fused, synchronisation-free operators -------------------------------------------- */
 

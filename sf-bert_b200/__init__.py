@@ -22,7 +22,8 @@ NT_OP, NN_OP, TN_OP = 0, 1, 2
 SYMBOLS = [
     "sfb_last_error", "sfb_version", "sfb_layout_generate", "sfb_lut_count", "sfb_lut_build", "sfb_mask_pack",
     "sfb_magicu64", "sfb_bst_sgemm_nt", "sfb_masked_softmax", "sfb_bst_sgemm_xn", "sfb_fused_sddmm_softmax",
-    "sfb_fused_attention", "sfb_bias_residual_layernorm", "sfb_device_status", "sfb_bias_gelu",
+    "sfb_fused_attention", "sfb_bias_residual_layernorm", "sfb_device_status", "sfb_bias_gelu", "sfb_lut_build_tn",
+    "sfb_masked_softmax_grad",
 ]
 
 if not os.path.exists(LIB_PATH):
@@ -42,6 +43,8 @@ lib.sfb_magicu64.restype = None
 lib.sfb_bst_sgemm_nt.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 9
 lib.sfb_masked_softmax.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 9 + [_f32]
 lib.sfb_bst_sgemm_xn.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 13
+lib.sfb_lut_build_tn.argtypes = [_vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp]
+lib.sfb_masked_softmax_grad.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32] + [_u32] * 8 + [_f32]
 lib.sfb_fused_sddmm_softmax.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 10 + [_f32]
 lib.sfb_fused_attention.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32] + [_u32] * 9 + [_f32, _u32]
 lib.sfb_bias_residual_layernorm.argtypes = [_vp] * 10 + [_u32, _u32, _i32]
@@ -117,6 +120,29 @@ class BlockLayout:
         self.nn_max = int(nn_max.item())
         self.mask_np = None
         self.mask_t = None
+        self._tn = None
+
+    def _build_tn(self):
+        """The column-major LUT of the backward matmuls, built on first use."""
+        if self._tn is None:
+            dev = self.layout.device
+            tn = torch.zeros(self.heads, self.nb + self.blocks, 2, dtype=torch.int32, device=dev)
+            tn_max = torch.zeros(1, dtype=torch.int32, device=dev)
+            status = torch.zeros(1, dtype=torch.int32, device=dev)
+            _check(lib.sfb_lut_build_tn(_stream(), _p(self.layout), self.heads, self.nb, self.blocks, _p(tn), _p(tn_max),
+                                        _p(status)))
+            if int(status.item()) != 0:
+                raise SfbError("sfb_lut_build_tn: block count mismatch")
+            self._tn = (tn, int(tn_max.item()))
+        return self._tn
+
+    @property
+    def tn_lut(self):
+        return self._build_tn()[0]
+
+    @property
+    def tn_max(self):
+        return self._build_tn()[1]
 
     @classmethod
     def generate(cls, kind, heads, nb, block_size, p0=0, p1=0, p2=0, p3=0, causal=0, seed=0, device="cuda"):
@@ -178,6 +204,39 @@ def bst_sgemm_xn(p, v, lay):
                                 lay.blocks, B, lay.nb, lay.nb, H, d, lay.heads, lay.nn_lut_dim, NN_OP, magic, shift,
                                 lay.nn_max))
     return o
+
+
+def bst_sgemm_tn(a, b, lay):
+    """C = A^T.B over each block column (bst_sgemm_xn with TN_OP, blocksparse.h:1005-1010): dV = P^T.dO and
+    dK = dS^T.Q of the backward pass (transformer_attention_optimize.cu:924,954)."""
+    B, L, H, d = _dims(b, lay)
+    c = torch.empty_like(b)
+    magic, shift = magicu64((d + 63) // 64)
+    _check(lib.sfb_bst_sgemm_xn(_stream(), _p(lay.tn_lut), _p(a), _p(b), _p(c), dtype_tag(a), dtype_tag(b), lay.block_size,
+                                lay.blocks, B, lay.nb, lay.nb, H, d, lay.heads, lay.nn_lut_dim, TN_OP, magic, shift,
+                                lay.tn_max))
+    return c
+
+
+def masked_softmax_grad(dy, y, lay, scale):
+    """dx = (dy - sum_row(dy*y)) * y * scale (BlocksparseMaskedSoftmaxGrad<T,V>, blocksparse.h:1164-1227)."""
+    assert dy.dtype == y.dtype and dy.shape == y.shape
+    B, H = y.shape[:2]
+    dx = torch.empty_like(y)
+    _check(lib.sfb_masked_softmax_grad(_stream(), _p(lay.nn_lut), _p(dy), _p(y), _p(dx), dtype_tag(y), lay.block_size,
+                                       lay.blocks, B, H, lay.nb, lay.heads, lay.nn_lut_dim, lay.nn_max, scale))
+    return dx
+
+
+def attention_backward(q, k, v, p, do, lay, scale, s_dtype=torch.bfloat16):
+    """The reference's backward sequence (transformer_attention_optimize.cu:924-964) from the saved probabilities:
+    dV = P^T.dO, dP = dO.V^T, dS = softmax_grad(dP, P), dK = dS^T.Q, dQ = dS.K.  Returns (dq, dk, dv)."""
+    dv = bst_sgemm_tn(p, do, lay)
+    dp = bst_sgemm_nt(do, v, lay, s_dtype)
+    ds = masked_softmax_grad(dp, p.to(s_dtype) if p.dtype != s_dtype else p, lay, scale)
+    dk = bst_sgemm_tn(ds, q, lay)
+    dq = bst_sgemm_xn(ds, k, lay)
+    return dq, dk, dv
 
 
 def fused_sddmm_softmax(q, k, lay, scale, out_dtype=torch.float32, use_mask=False):

@@ -16,7 +16,9 @@ int simt_sddmm_nt(cudaStream_t s, const void *lut, const void *a, const void *b,
 int simt_softmax(cudaStream_t s, const void *lut, const void *mask, const void *x, void *y, int x_dtype, int y_dtype,
                  uint32_t bs, const AttnDims &p, float scale, uint32_t max_lut);
 int simt_spmm_nn(cudaStream_t s, const void *lut, const void *a, const void *b, void *c, int a_dtype, int bc_dtype,
-                 uint32_t bs, const AttnDims &p);
+                 uint32_t bs, const AttnDims &p, bool trans);
+int simt_softmax_grad(cudaStream_t s, const void *lut, const void *dy, const void *y, void *dx, int dtype, uint32_t bs,
+                      const AttnDims &p, float scale, uint32_t max_lut);
 int simt_fused_sddmm_softmax(cudaStream_t s, const void *nn_lut, const void *a, const void *b, const void *mask, void *y,
                              int ab_dtype, int y_dtype, uint32_t bs, const AttnDims &p, float scale);
 int simt_fused_attention(cudaStream_t s, const void *nn_lut, const void *q, const void *k, const void *v, void *o,

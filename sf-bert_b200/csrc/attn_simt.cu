@@ -351,8 +351,90 @@ __global__ void __launch_bounds__(BS * BS / 8) softmax_kernel(const uint2 *__res
 }
 
 // ------------------------------------------------------------------------------------------------
-// SpMM (NN): one CTA per (block-row, 64-wide slice of d)
-template <int BS, int A_DT, int BC_DT>
+// Softmax gradient: dx = (dy - sum over the query row of dy*y) * y * scale.  Same decomposition as the forward
+// softmax: one CTA per block-row, a lane owns 8 consecutive keys of one query row of one block.
+// NB > 0: the row has at most NB blocks; dy and y of all of them are loaded up front and stay in registers
+// (one pass over HBM).  NB == 0: any length; the second sweep re-reads what the first pulled through L2.
+template <int BS, int DT, int NB>
+__global__ void __launch_bounds__(BS * BS / 8) softmax_grad_kernel(const uint2 *__restrict__ lut, const void *__restrict__ DY,
+                                                             const void *__restrict__ Y, void *__restrict__ DX, AttnDims p,
+                                                             float scale)
+{
+    constexpr int LPR = BS / 8;  // lanes per query row
+    const uint32_t i = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
+    const uint2 *nn = lut + (size_t)h * p.lut_stride;
+    const uint2 head = nn[i];
+    const uint32_t off = head.x, cnt = head.y;
+    if (cnt == 0) return;
+    const uint32_t r = threadIdx.x / LPR;
+    const uint32_t c0 = (threadIdx.x % LPR) * 8;
+    const size_t base = ((size_t)b * p.H + h) * p.blocks * BS * BS + (size_t)r * BS + c0;
+
+    if (NB > 0) {
+        constexpr int N = NB > 0 ? NB : 1;
+        Raw8<DT> rdy[N], ry[N];
+        uint32_t blks[N];
+#pragma unroll
+        for (int j = 0; j < N; j++) {
+            blks[j] = 0;
+            if (j < (int)cnt) {
+                blks[j] = nn[off + j].x;
+                rdy[j] = load_raw8<DT>(DY, base + (size_t)blks[j] * BS * BS);
+                ry[j] = load_raw8<DT>(Y, base + (size_t)blks[j] * BS * BS);
+            }
+        }
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < N; j++)
+            if (j < (int)cnt) {
+                float a[8], c[8];
+                unpack8<DT>(a, rdy[j]);
+                unpack8<DT>(c, ry[j]);
+#pragma unroll
+                for (int t = 0; t < 8; t++) sum = fmaf(a[t], c[t], sum);
+            }
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+        for (int j = 0; j < N; j++)
+            if (j < (int)cnt) {
+                float a[8], c[8];
+                unpack8<DT>(a, rdy[j]);
+                unpack8<DT>(c, ry[j]);
+#pragma unroll
+                for (int t = 0; t < 8; t++) a[t] = (a[t] - sum) * c[t] * scale;
+                store8<DT>(DX, base + (size_t)blks[j] * BS * BS, a);
+            }
+        return;
+    }
+    float sum = 0.f;
+    for (uint32_t e = 0; e < cnt; e++) {
+        const size_t at = base + (size_t)nn[off + e].x * BS * BS;
+        float a[8], c[8];
+        unpack8<DT>(a, load_raw8<DT>(DY, at));
+        unpack8<DT>(c, load_raw8<DT>(Y, at));
+#pragma unroll
+        for (int t = 0; t < 8; t++) sum = fmaf(a[t], c[t], sum);
+    }
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    for (uint32_t e = 0; e < cnt; e++) {
+        const size_t at = base + (size_t)nn[off + e].x * BS * BS;
+        float a[8], c[8];
+        unpack8<DT>(a, load_raw8<DT>(DY, at));
+        unpack8<DT>(c, load_raw8<DT>(Y, at));
+#pragma unroll
+        for (int t = 0; t < 8; t++) a[t] = (a[t] - sum) * c[t] * scale;
+        store8<DT>(DX, at, a);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// SpMM: one CTA per (block-row, 64-wide slice of d).  TRANS = false: O = sum over the row's blocks of P . V (NN, the
+// lut is the nn_lut).  TRANS = true: the backward products dV = P^T dO and dK = dS^T Q -- the lut is the tn_lut,
+// "row" i is a block COLUMN, an entry names a block of that column and the block-row its B rows come from, and
+// the block is used transposed.
+template <int BS, int A_DT, int BC_DT, bool TRANS>
 __global__ void __launch_bounds__(256) spmm_nn_kernel(const uint2 *__restrict__ lut, const void *__restrict__ Pm,
                                                      const void *__restrict__ V, void *__restrict__ O, AttnDims p)
 {
@@ -387,7 +469,7 @@ __global__ void __launch_bounds__(256) spmm_nn_kernel(const uint2 *__restrict__ 
         for (int c = 0; c < BS; c++) {
             float a[TM], bb[TN];
 #pragma unroll
-            for (int m = 0; m < TM; m++) a[m] = Ps[ty + 16 * m][c];
+            for (int m = 0; m < TM; m++) a[m] = TRANS ? Ps[c][ty + 16 * m] : Ps[ty + 16 * m][c];
 #pragma unroll
             for (int n = 0; n < TN; n++) bb[n] = Vs[c][tx + 16 * n];
 #pragma unroll
@@ -673,13 +755,28 @@ int simt_softmax(cudaStream_t s, const void *lut, const void *mask, const void *
 }
 
 int simt_spmm_nn(cudaStream_t s, const void *lut, const void *a, const void *b, void *c, int a_dtype, int bc_dtype,
-                 uint32_t bs, const AttnDims &p)
+                 uint32_t bs, const AttnDims &p, bool trans)
 {
     dim3 grid(p.nb_a * ((p.d + 63) / 64), p.B, p.H);
     DISPATCH_BS(bs, DISPATCH_DT(a_dtype, AD, DISPATCH_DT(bc_dtype, BD, {
-        spmm_nn_kernel<BS, AD, BD><<<grid, 256, 0, s>>>((const uint2 *)lut, a, b, c, p);
+        if (trans) spmm_nn_kernel<BS, AD, BD, true><<<grid, 256, 0, s>>>((const uint2 *)lut, a, b, c, p);
+        else spmm_nn_kernel<BS, AD, BD, false><<<grid, 256, 0, s>>>((const uint2 *)lut, a, b, c, p);
     })))
     return check_launch("sfb_bst_sgemm_xn");
+}
+
+int simt_softmax_grad(cudaStream_t s, const void *lut, const void *dy, const void *y, void *dx, int dtype, uint32_t bs,
+                      const AttnDims &p, float scale, uint32_t max_lut)
+{
+    dim3 grid(p.nb_a, p.B, p.H);
+    // rows of up to 8 blocks (the caller's max_lut says so) stay in registers: one pass over HBM; 0 = unknown, stream
+    const int nb = (max_lut >= 1 && max_lut <= 4) ? 4 : (max_lut >= 5 && max_lut <= 8) ? 8 : 0;
+#define SG_LAUNCH(NBV) DISPATCH_DT(dtype, DT, { softmax_grad_kernel<BS, DT, NBV><<<grid, BS * BS / 8, 0, s>>>((const uint2 *)lut, dy, y, dx, p, scale); })
+    DISPATCH_BS(bs, {
+        if (nb == 4) { SG_LAUNCH(4) } else if (nb == 8) { SG_LAUNCH(8) } else { SG_LAUNCH(0) }
+    })
+#undef SG_LAUNCH
+    return check_launch("sfb_masked_softmax_grad");
 }
 
 template <typename K>

@@ -141,6 +141,60 @@ __global__ void lut_build_kernel(const uint8_t *layout, uint32_t nb, uint32_t bl
     }
 }
 
+// The column-major twin for the backward matmuls; one CTA of 256 threads per head; dynamic smem: uint32
+// cursor[nb].  Block ids are positions in the row-major scan, so the rows are walked in order by the whole CTA
+// (a ballot scan gives every kept block of the row its id) while each thread appends to its own columns.
+__global__ void lut_build_tn_kernel(const uint8_t *layout, uint32_t nb, uint32_t blocks, uint2 *tn_lut, uint32_t *tn_max,
+                                    uint32_t *status)
+{
+    extern __shared__ uint32_t cursor[];
+    __shared__ uint32_t total, warp_sum[8];
+    const uint32_t h = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const uint8_t *lay = layout + (size_t)h * nb * nb;
+
+    for (uint32_t j = threadIdx.x; j < nb; j += blockDim.x) {
+        uint32_t c = 0;
+        for (uint32_t i = 0; i < nb; i++) c += lay[(size_t)i * nb + j] != 0;
+        cursor[j] = c;
+    }
+    __syncthreads();
+    uint2 *tn = tn_lut + (size_t)h * (nb + blocks);
+    if (threadIdx.x == 0) {
+        uint32_t run = 0, mx = 0;
+        for (uint32_t j = 0; j < nb; j++) {
+            const uint32_t c = cursor[j];
+            if (run + c <= blocks) tn[j] = make_uint2(nb + run, c);   // header: offsets start at nb
+            cursor[j] = nb + run;
+            run += c;
+            mx = max(mx, c);
+        }
+        total = run;
+        if (run == blocks && tn_max) atomicMax(tn_max, mx);
+    }
+    __syncthreads();
+    if (total != blocks) {
+        if (threadIdx.x == 0 && status) atomicExch(status, 1u);
+        return;
+    }
+    uint32_t id_base = 0;
+    for (uint32_t i = 0; i < nb; i++)
+        for (uint32_t c0 = 0; c0 < nb; c0 += blockDim.x) {
+            const uint32_t j = c0 + threadIdx.x;
+            const bool kept = j < nb && lay[(size_t)i * nb + j] != 0;
+            const uint32_t votes = __ballot_sync(0xffffffffu, kept);
+            if (lane == 0) warp_sum[wid] = __popc(votes);
+            __syncthreads();
+            uint32_t before = 0, all = 0;
+            for (uint32_t w2 = 0; w2 < blockDim.x / 32; w2++) {
+                before += w2 < wid ? warp_sum[w2] : 0;
+                all += warp_sum[w2];
+            }
+            if (kept) tn[cursor[j]++] = make_uint2(id_base + before + __popc(votes & ((1u << lane) - 1u)), i);   // (block id, row block)
+            id_base += all;
+            __syncthreads();
+        }
+}
+
 template <typename W>
 __global__ void mask_pack_kernel(const uint2 *nt_lut, uint32_t blocks, uint32_t bs, int pred, uint32_t ctx,
                                  W *mask_np, W *mask_t)
@@ -198,6 +252,18 @@ extern "C" int sfb_lut_build(sfb_stream_t stream, const uint8_t *layout, uint32_
     lut_build_kernel<<<heads, 256, 2 * nb * sizeof(uint32_t), s>>>(layout, nb, blocks, (uint2 *)nt_lut, (uint2 *)nn_lut,
                                                                  (uint2 *)rblk_lut, nn_max, status);
     return check_launch("sfb_lut_build");
+}
+
+extern "C" int sfb_lut_build_tn(sfb_stream_t stream, const uint8_t *layout, uint32_t heads, uint32_t nb, uint32_t blocks,
+                                void *tn_lut, uint32_t *tn_max, uint32_t *status)
+{
+    SFB_REQUIRE(layout && tn_lut, "sfb_lut_build_tn: NULL pointer");
+    SFB_REQUIRE(heads >= 1 && nb >= 1 && nb <= 4096, "sfb_lut_build_tn: bad heads=%u nb=%u (nb <= 4096)", heads, nb);
+    cudaStream_t s = as_stream(stream);
+    if (tn_max) cudaMemsetAsync(tn_max, 0, sizeof(uint32_t), s);
+    if (status) cudaMemsetAsync(status, 0, sizeof(uint32_t), s);
+    lut_build_tn_kernel<<<heads, 256, nb * sizeof(uint32_t), s>>>(layout, nb, blocks, (uint2 *)tn_lut, tn_max, status);
+    return check_launch("sfb_lut_build_tn");
 }
 
 extern "C" int sfb_mask_pack(sfb_stream_t stream, const void *nt_lut, uint32_t heads, uint32_t blocks,

@@ -59,14 +59,30 @@ extern "C" int sfb_bst_sgemm_xn(sfb_stream_t stream, const void *lut, const void
     const char *who = "sfb_bst_sgemm_xn";
     (void)magic; (void)shift;
     SFB_REQUIRE(lut && a && b && c, "%s: NULL pointer", who);
-    SFB_REQUIRE(op == SFB_NN_OP, "%s: op %u not supported (forward NN only)", who, op);
+    SFB_REQUIRE(op == SFB_NN_OP || op == SFB_TN_OP, "%s: op %u not supported (NN_OP or TN_OP)", who, op);
     SFB_REQUIRE(valid_dtype(a_dtype) && valid_dtype(bc_dtype), "%s: unknown dtype", who);
     if (check_common(who, block_size, batch_dim, head_dim, state_dim, lut_heads)) return 1;
     SFB_REQUIRE(lut_heads == 1 || lut_dim >= blocks + ctx_blks_c, "%s: lut_dim %u smaller than blocks+ctx_blks", who, lut_dim);
     if (ctx_blks_c == 0) { clear_error(); return 0; }
     AttnDims p = {batch_dim, head_dim, state_dim, ctx_blks_c, ctx_blks_b, blocks, lut_heads > 1 ? lut_dim : 0, 0};
+    if (op == SFB_TN_OP) return simt_spmm_nn(as_stream(stream), lut, a, b, c, a_dtype, bc_dtype, block_size, p, true);
     if (tc_spmm_supported(a_dtype, bc_dtype, block_size, p, max_lut)) return tc_spmm(as_stream(stream), lut, a, b, c, a_dtype, p);
-    return simt_spmm_nn(as_stream(stream), lut, a, b, c, a_dtype, bc_dtype, block_size, p);
+    return simt_spmm_nn(as_stream(stream), lut, a, b, c, a_dtype, bc_dtype, block_size, p, false);
+}
+
+extern "C" int sfb_masked_softmax_grad(sfb_stream_t stream, const void *lut, const void *dy, const void *y, void *dx, int dtype,
+                                       uint32_t block_size, uint32_t blocks, uint32_t batch_dim, uint32_t head_dim,
+                                       uint32_t ctx_blks, uint32_t lut_heads, uint32_t lut_dim, uint32_t max_lut, float scale)
+{
+    const char *who = "sfb_masked_softmax_grad";
+    SFB_REQUIRE(lut && dy && y && dx, "%s: NULL pointer", who);
+    SFB_REQUIRE(valid_dtype(dtype), "%s: unknown dtype", who);
+    if (check_common(who, block_size, batch_dim, head_dim, 1, lut_heads)) return 1;
+    SFB_REQUIRE(lut_heads == 1 || lut_dim >= blocks + ctx_blks, "%s: lut_dim %u smaller than blocks+ctx_blks", who, lut_dim);
+    SFB_REQUIRE(aligned16(dy) && aligned16(y) && aligned16(dx), "%s: dy, y and dx must be 16-byte aligned", who);
+    if (blocks == 0 || ctx_blks == 0) { clear_error(); return 0; }
+    AttnDims p = {batch_dim, head_dim, 0, ctx_blks, ctx_blks, blocks, lut_heads > 1 ? lut_dim : 0, 0};
+    return simt_softmax_grad(as_stream(stream), lut, dy, y, dx, dtype, block_size, p, scale, max_lut);
 }
 
 extern "C" int sfb_fused_sddmm_softmax(sfb_stream_t stream, const void *nn_lut, const void *a, const void *b, const void *mask,

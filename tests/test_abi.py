@@ -61,8 +61,8 @@ def test_bad_arguments_are_rejected_with_a_message(lib):
     rc = lib.sfb_fused_attention(None, one, one, one, one, one, None, 0, u(32), u(4), u(1), u(2), u(4), u(64), u(3), u(4),
                                  u(1), C.c_float(0.125), u(2))
     assert rc != 0 and b"lut_heads" in lib.sfb_last_error()
-    # backward op is not part of the forward path
-    rc = lib.sfb_bst_sgemm_xn(None, one, one, one, one, 1, 0, u(32), u(4), u(1), u(2), u(2), u(1), u(64), u(1), u(6), u(2),
+    # an op that is neither NN_OP nor TN_OP
+    rc = lib.sfb_bst_sgemm_xn(None, one, one, one, one, 1, 0, u(32), u(4), u(1), u(2), u(2), u(1), u(64), u(1), u(6), u(0),
                               u(1), u(0), u(2))
     assert rc != 0 and b"op" in lib.sfb_last_error()
     rc = lib.sfb_mask_pack(None, one, u(1), u(4), u(48), 0, u(0), one, one)
