@@ -266,10 +266,10 @@ def run_bandwidth_kernel(args):
     elif args.kernel == "spmm_tn":
         lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
         pblk = torch.rand(B, H, lay.blocks, bs, bs, device="cuda").to(torch.bfloat16)
-        do = torch.randn(B, L, H, d, device="cuda")
+        do = torch.randn(B, L, H, d, device="cuda").to(torch.bfloat16)
         fn = lambda: sfb.bst_sgemm_tn(pblk, do, lay)
-        nbytes = pblk.numel() * 2 + 2 * do.numel() * 4
-        name, unit_name = "spmm_nn_kernel<TRANS>", "bf16 blocks read + fp32 B read once + fp32 C written (the reference's types)"
+        nbytes = pblk.numel() * 2 + 2 * do.numel() * 2
+        name, unit_name = "spmm_tc_kernel (transposed)", "bf16 blocks read + bf16 B read once + bf16 C written"
     elif args.kernel in ("sddmm", "spmm", "fused_p"):
         tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.bfloat16}[cfg["dtype"]]
         lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])

@@ -28,6 +28,7 @@ struct UParams {
     int out_dtype;             // SFB_F32 / SFB_BF16 / SFB_F16
     int is_bf16;               // operand format
     uint32_t p_rows;           // spmm: rows of the 2-D view of P (= B*H*blocks*64); a coordinate beyond it reads zeros
+    int trans;                 // spmm: 1 = the blocks are used transposed and the LUT walks block columns (TN_OP)
 };
 
 constexpr int kSdStages = 3;
@@ -214,7 +215,10 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
 
 // ---- SpMM -----------------------------------------------------------------------------------------
 // warp 0: TMA (per key block: the two 64-row halves of the P tile -- a half whose block-row does not keep the
-// block is fetched from beyond the tensor and arrives as zeros -- and the V tile); warp 1: MMA; warps 2-5: epilogue
+// block is fetched from beyond the tensor and arrives as zeros -- and the V tile); warp 1: MMA; warps 2-5: epilogue.
+// With p.trans the same kernel does the backward products C = A^T . B: the CTA owns two block COLUMNS, the LUT is
+// the tn_lut, and the two blocks of a step are read as ONE MN-major A operand (M = the 2 x 64 key positions,
+// contiguous inside a shared-memory row; K = the 64 query rows, 2048 bytes per 16) instead of a K-major one.
 __global__ void __launch_bounds__(192, 2)
 spmm_tc_kernel(const __grid_constant__ CUtensorMap pmap, const __grid_constant__ CUtensorMap vmap, const UParams p)
 {
@@ -270,15 +274,18 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap pmap, const __grid_constant__
         }
     } else if (warp == 1) {
         if (lane == 0 && T > 0) {
-            const uint32_t idesc = instr_desc(fmt, fmt, 128, 64, 1);
+            const uint32_t idesc = instr_desc(fmt, fmt, 128, 64, 1) | (p.trans ? 1u << 15 : 0u);   // bit 15: A is MN-major
+            const uint32_t a_step = p.trans ? 128u : 2u;   // descriptor units of 16 bytes per 16 of K
             for (uint32_t t = 0; t < T; t++) {
                 const uint32_t s = t % kUStages;
                 if (!mbar_wait(&st->in_full[s], (t / kUStages) & 1, abort_flag, 33)) break;
                 tcgen05_fence_after();
-                const uint64_t p_desc = smem_desc_sw128(smem_u32(tiles + s * kStageBytes));
+                const uint32_t p_addr = smem_u32(tiles + s * kStageBytes);
+                // transposed: the second block is the next group of 64 along M, one tile further on
+                const uint64_t p_desc = p.trans ? smem_desc_sw128(p_addr, kTileBytes) : smem_desc_sw128(p_addr);
                 const uint64_t v_desc = smem_desc_sw128(smem_u32(tiles + s * kStageBytes + kQBytes));
 #pragma unroll
-                for (uint32_t kk = 0; kk < 4; kk++) umma_f16(tmem, p_desc + 2 * kk, v_desc + 128 * kk, idesc, (t | kk) ? 1u : 0u);
+                for (uint32_t kk = 0; kk < 4; kk++) umma_f16(tmem, p_desc + a_step * kk, v_desc + 128 * kk, idesc, (t | kk) ? 1u : 0u);
                 umma_commit(&st->in_empty[s]);
                 if (t + 1 == T) umma_commit(&st->o_final);
             }
@@ -578,7 +585,7 @@ bool tc_spmm_supported(int a_dtype, int bc_dtype, uint32_t bs, const AttnDims &p
     return a_dtype == bc_dtype && (a_dtype == SFB_BF16 || a_dtype == SFB_F16) && p.blocks > 0 && tc_shape_ok(bs, p, max_lut);
 }
 
-int tc_spmm(cudaStream_t s, const void *nn_lut, const void *a, const void *b, void *c, int dtype, const AttnDims &p)
+int tc_spmm(cudaStream_t s, const void *nn_lut, const void *a, const void *b, void *c, int dtype, const AttnDims &p, bool trans)
 {
     using namespace tc;
     SFB_REQUIRE((((uintptr_t)a | (uintptr_t)b) & 15) == 0 && ((uintptr_t)c & 31) == 0, "sfb_bst_sgemm_xn: a, b must be 16-byte and c 32-byte aligned");
@@ -586,7 +593,7 @@ int tc_spmm(cudaStream_t s, const void *nn_lut, const void *a, const void *b, vo
     const uint64_t prow = (uint64_t)p.B * p.H * p.blocks * 64;
     CUtensorMap pm, vm;
     if (make_p_map(&pm, a, prow, is_bf16) || make_map(&vm, b, (uint64_t)p.B * p.nb_b * 64, p.H, is_bf16, 64)) return 1;
-    UParams prm = {(const uint2 *)nn_lut, c, p.B, p.H, p.nb_a, p.blocks, p.lut_stride, dtype, is_bf16, (uint32_t)prow};
+    UParams prm = {(const uint2 *)nn_lut, c, p.B, p.H, p.nb_a, p.blocks, p.lut_stride, dtype, is_bf16, (uint32_t)prow, trans ? 1 : 0};
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(spmm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSpmmSmem) != cudaSuccess)

@@ -65,9 +65,9 @@ extern "C" int sfb_bst_sgemm_xn(sfb_stream_t stream, const void *lut, const void
     SFB_REQUIRE(lut_heads == 1 || lut_dim >= blocks + ctx_blks_c, "%s: lut_dim %u smaller than blocks+ctx_blks", who, lut_dim);
     if (ctx_blks_c == 0) { clear_error(); return 0; }
     AttnDims p = {batch_dim, head_dim, state_dim, ctx_blks_c, ctx_blks_b, blocks, lut_heads > 1 ? lut_dim : 0, 0};
-    if (op == SFB_TN_OP) return simt_spmm_nn(as_stream(stream), lut, a, b, c, a_dtype, bc_dtype, block_size, p, true);
-    if (tc_spmm_supported(a_dtype, bc_dtype, block_size, p, max_lut)) return tc_spmm(as_stream(stream), lut, a, b, c, a_dtype, p);
-    return simt_spmm_nn(as_stream(stream), lut, a, b, c, a_dtype, bc_dtype, block_size, p, false);
+    const bool trans = op == SFB_TN_OP;
+    if (tc_spmm_supported(a_dtype, bc_dtype, block_size, p, max_lut)) return tc_spmm(as_stream(stream), lut, a, b, c, a_dtype, p, trans);
+    return simt_spmm_nn(as_stream(stream), lut, a, b, c, a_dtype, bc_dtype, block_size, p, trans);
 }
 
 extern "C" int sfb_masked_softmax_grad(sfb_stream_t stream, const void *lut, const void *dy, const void *y, void *dx, int dtype,

@@ -68,6 +68,44 @@ def test_spmm_tn(sfb, oracle, case, dtype):
     np.testing.assert_allclose(got, want, rtol=0, atol=2e-5 * np.sqrt(bs * tn[..., :L // bs, 1].max()) * 4)
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("H_lut,nb,kind,kw,dev", [
+    (1, 16, "stride", dict(band=4, every=8), ("LAYOUT_STRIDE", dict(p0=4, p1=8))),
+    (1, 5, "full", dict(causal=1), ("LAYOUT_FULL", dict(causal=1))),            # odd number of block columns
+    (1, 9, "local", dict(left=1, right=2), ("LAYOUT_LOCAL", dict(p0=1, p1=2))),
+    (4, 16, "fixed", dict(stride=4), ("LAYOUT_FIXED", dict(p0=4))),             # per-head LUTs
+    (1, 16, "bigbird", dict(window=1, g_first=1, g_last=1, nrand=3, seed=3), ("LAYOUT_BIGBIRD", dict(p0=1, p1=1, p2=1, p3=3, seed=3))),
+    (1, 64, "full", dict(), ("LAYOUT_FULL", dict())),                           # columns of 64 blocks
+])
+def test_spmm_tn_on_tensor_cores(sfb, oracle, dtype, H_lut, nb, kind, kw, dev):
+    """16-bit operands, 64x64 blocks, 64-wide heads: the tcgen05 kernel with the blocks as an MN-major A operand."""
+    B, H, bs, d = 2, 4, 64, 64
+    lay, ref_layout, luts = _make(sfb, oracle, kind, kw, dev, H_lut, nb, bs)
+    tn = oracle.lut_build_tn(ref_layout)["tn"]
+    a, an = _blocks(oracle, (B, H, luts["blocks"], bs, bs), 350, dtype)
+    b, bn = _blocks(oracle, (B, nb * bs, H, d), 351, dtype)
+    want = oracle.spmm_tn(an, bn, tn, bs)
+    got = sfb.bst_sgemm_tn(a, b, lay)
+    assert sfb.device_status() == 0
+    assert got.dtype == TD[dtype]
+    assert np.abs(got.float().cpu().numpy() - want).max() <= 2e-2 * np.abs(want).max()
+
+
+def test_spmm_tn_empty_columns_on_tensor_cores(sfb, oracle):
+    bs, nb = 64, 6
+    layout = np.zeros((1, nb, nb), np.uint8)
+    layout[0, :, 0] = 1
+    layout[0, 2, 3] = 1                       # columns 1, 2, 4, 5 have no block; the pair (2, 3) is half empty
+    lay = sfb.BlockLayout(torch.from_numpy(layout).cuda(), bs)
+    a, an = _blocks(oracle, (1, 2, lay.blocks, bs, bs), 360, "bf16")
+    b, bn = _blocks(oracle, (1, nb * bs, 2, 64), 361, "bf16")
+    got = sfb.bst_sgemm_tn(a, b, lay).float().cpu().numpy()
+    want = oracle.spmm_tn(an, bn, oracle.lut_build_tn(layout)["tn"], bs)
+    assert np.abs(got - want).max() <= 2e-2 * np.abs(want).max()
+    for c in (1, 2, 4, 5):
+        assert float(np.abs(got[:, c * bs:(c + 1) * bs]).max()) == 0.0
+
+
 def test_spmm_tn_empty_columns_give_zeros(sfb, oracle):
     bs, nb = 32, 6
     layout = np.zeros((1, nb, nb), np.uint8)
@@ -146,6 +184,13 @@ def test_backward_at_benchmark_size_properties(sfb, oracle):
     counts = ref_layout[0].sum(axis=0).astype(np.float32) * bs
     got = dv1[b0, :, h0, 0].cpu().numpy().reshape(nb, bs)
     assert np.array_equal(got, np.repeat(counts[:, None], bs, axis=1))
+    # the same product on the tensor cores (16-bit B and C): exact for ones
+    dv1h = sfb.bst_sgemm_tn(ones_p, ones_o.to(torch.bfloat16), lay)
+    assert np.array_equal(dv1h[b0, :, h0, 5].float().cpu().numpy().reshape(nb, bs), np.repeat(counts[:, None], bs, axis=1))
+    dkh = sfb.bst_sgemm_tn(ds, q.to(torch.bfloat16), lay)
+    want_dkh = oracle.spmm_tn(dsn, q.to(torch.bfloat16)[b0:b0 + 1, :, h0:h0 + 1].float().cpu().numpy(), tn, bs)
+    assert np.abs(dkh[b0:b0 + 1, :, h0:h0 + 1].float().cpu().numpy() - want_dkh).max() <= 2e-2 * np.abs(want_dkh).max()
+    assert sfb.device_status() == 0
     # one slice of dK = dS^T Q against the oracle
     dk = sfb.bst_sgemm_tn(ds, q, lay)
     want_dk = oracle.spmm_tn(dsn, q[b0:b0 + 1, :, h0:h0 + 1].cpu().numpy(), tn, bs)
