@@ -250,6 +250,8 @@ def run_bandwidth_kernel(args):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     if args.kernel == "encoder_layer":
         return run_encoder_layer(args, sfb, cfg, pk, flush)
+    if args.kernel == "linear":
+        return run_linear(args, sfb, cfg, pk, flush)
     if args.kernel == "softmax":
         lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
         x = torch.randn(B, H, lay.blocks, bs, bs, device="cuda").to(torch.bfloat16)
@@ -320,6 +322,58 @@ def run_bandwidth_kernel(args):
                      "frac": round(gbs / pk["hbm"], 4), "traffic": None, "peak_source": pk["source"] + " copy bandwidth",
                      "algorithmic_bytes": nbytes},
         "gpu_launches": args.steps, "clocks": clocks}), flush=True)
+
+
+def run_linear(args, sfb, cfg, pk, flush):
+    """The dense projections of one encoder layer at the workload's shape on the tcgen05 kernel (N=1): QKV as one
+    [hidden, 3 hidden] product, the output projection, FFN up (with GELU) and FFN down; the GEMM library's time on
+    the same products is printed beside it."""
+    import torch
+    B, H, L, d = cfg["B"], cfg["H"], cfg["L"], cfg["d"]
+    tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.bfloat16}[cfg["dtype"]]
+    hidden, ffn, m = H * d, 4 * H * d, B * L
+    shapes = [("qkv", hidden, 3 * hidden, 0), ("out", hidden, hidden, 0), ("ffn_up_gelu", hidden, ffn, 1), ("ffn_down", ffn, hidden, 0)]
+    res, total_ms, total_lib, flops = {}, 0.0, 0.0, 0.0
+    sampler = ClockSampler(0)
+    for name, k, n, act in shapes:
+        x = torch.randn(m, k, device="cuda").to(tdt)
+        w = (0.02 * torch.randn(k, n, device="cuda")).to(tdt)
+        b = torch.randn(n, device="cuda")
+        ours = lambda: sfb.linear(x, w, b, act)
+        if act:
+            libf = lambda: torch.nn.functional.gelu(torch.addmm(b.to(tdt), x, w))
+        else:
+            libf = lambda: torch.addmm(b.to(tdt), x, w)
+        t = []
+        for fn in (ours, libf):
+            for _ in range(max(args.warmup, 3)):
+                fn()
+            torch.cuda.synchronize()
+            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+            for a, b_ in ev:
+                flush.fill_(1)
+                a.record()
+                fn()
+                b_.record()
+            torch.cuda.synchronize()
+            t.append(sum(a.elapsed_time(b_) for a, b_ in ev) / args.steps)
+        f = 2.0 * m * n * k
+        res[name] = {"m": m, "n": n, "k": k, "ms": round(t[0], 4), "tflops": round(f / (t[0] * 1e-3) / 1e12, 1),
+                     "library_ms": round(t[1], 4), "library_tflops": round(f / (t[1] * 1e-3) / 1e12, 1)}
+        total_ms += t[0]
+        total_lib += t[1]
+        flops += f
+    clocks = sampler.stop()
+    tf = flops / (total_ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "projection TFLOP/s", "value": round(tf, 1), "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(total_ms, 4), "higher_is_better": True, "dtype": cfg["dtype"],
+        "data": "synthetic",
+        "config": {"workload": args.config, "kernel": "linear_tc_kernel", "products": res, "library": "torch.addmm (+ gelu) on cuBLAS",
+                   "library_ms": round(total_lib, 4), "l2": "flushed between timed steps"},
+        "roofline": {"bound": "tensor", "achieved": round(tf, 1), "peak": pk["tensor"], "unit": "TFLOP/s", "frac": round(tf / pk["tensor"], 4),
+                     "traffic": None, "peak_source": pk["source"] + " cuBLAS bf16 burst"},
+        "gpu_launches": args.steps * 4, "clocks": clocks}), flush=True)
 
 
 def run_encoder_layer(args, sfb, cfg, pk, flush):
@@ -436,7 +490,7 @@ if __name__ == "__main__":
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="stride_bertbase", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer", "softmax_grad", "spmm_tn"],
+    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer", "softmax_grad", "spmm_tn", "linear"],
                     help="fused = the headline fused attention; softmax / layernorm = the bandwidth kernels (N=1)")
     a = ap.parse_args()
     if a.impl == "reference":

@@ -45,6 +45,9 @@ enum {
 /* element-mask predicates for sfb_mask_pack */
 enum { SFB_MASK_ALL = 0, SFB_MASK_CAUSAL_DIAG = 1, SFB_MASK_CAUSAL_ALL = 2, SFB_MASK_LOCAL = 3 };
 
+/* activations of sfb_linear */
+enum { SFB_ACT_NONE = 0, SFB_ACT_GELU = 1 };
+
 /* block-sparse matmul variants (gpu_types.h:135-137) */
 enum { SFB_NT_OP = 0, SFB_NN_OP = 1, SFB_TN_OP = 2 };
 
@@ -190,6 +193,18 @@ int sfb_bias_residual_layernorm(sfb_stream_t stream, void *out, void *sum_out, f
  * transformer_attention_optimize.cu:781-785); CPU twin gelu, ewops.h:32-43. */
 int sfb_bias_gelu(sfb_stream_t stream, void *out, const void *x, const float *bias, uint32_t m,
                   uint32_t n, int dtype);
+
+/* ---- dense projections around the attention --------------------------------------------- */
+
+/* out[m, n] = act(x[m, k] . w[k, n] + bias[n]) on the tensor cores: x, w, out row-major 16-bit (dtype SFB_BF16 or
+ * SFB_F16), fp32 accumulation, bias fp32 [n] (may be NULL), act SFB_ACT_NONE or SFB_ACT_GELU (t * sigmoid(1.702 t),
+ * gelu_gpu_v2).  n must be a multiple of 16, k of 8.  w is laid out as the reference keeps its weights: its
+ * cublasSgemm(OP_N, OP_N, n, m, k, W, n, X, k, C, n) calls are out = x . w with w row-major [k, n].
+ * Replaces cublasSgemm + tensor_add_vector_gpu (transformer_attention_optimize.cu:693-716, 755-763) and
+ * cublasSgemm + tensor_add_vector_gpu_2048 + gelu_gpu_v2 (:773-785) for 16-bit operands; fp32 products are
+ * rejected (they stay with the GEMM library: tensor-core arithmetic cannot meet fp32 parity). */
+int sfb_linear(sfb_stream_t stream, void *out, const void *x, const void *w, const float *bias, uint32_t m,
+               uint32_t n, uint32_t k, int dtype, int act);
 
 #ifdef __cplusplus
 }

@@ -471,6 +471,26 @@ void orc_bias_gelu(float *out, const float *x, const float *bias, uint32_t m, ui
         }
 }
 
+/* out = act(x . w + bias): matrixMulNNCPU (matmul.h:101-118: double accumulation over k in ascending order),
+ * then bias (ewops.h:10-17) and, for act = 1, gelu (ewops.h:32-43) -- the projections of the encoder layer
+ * (transformer_inference_part.cpp:213-234 makes them with cblas_sgemm).  x [m,k], w [k,n] row-major. */
+void orc_linear(float *out, const float *x, const float *w, const float *bias, uint32_t m, uint32_t n, uint32_t k, int act)
+{
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < (long long)m; i++)
+        for (uint32_t j = 0; j < n; j++) {
+            double sum = 0;
+            for (uint32_t t = 0; t < k; t++) sum += (double)x[(size_t)i * k + t] * (double)w[(size_t)t * n + j];
+            out[(size_t)i * n + j] = (float)sum;
+        }
+    if (act == 1) orc_bias_gelu(out, out, bias, m, n);
+    else if (bias) {
+#pragma omp parallel for schedule(static)
+        for (long long i = 0; i < (long long)m; i++)
+            for (uint32_t j = 0; j < n; j++) out[(size_t)i * n + j] = out[(size_t)i * n + j] + bias[j];
+    }
+}
+
 /* ------------------------------------------------------------------------------ */
 void orc_magicu64(uint32_t d, uint32_t *magic, uint32_t *shift)
 {

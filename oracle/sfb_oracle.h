@@ -147,6 +147,10 @@ void orc_spmm_nn(const float *a, const float *b, const uint32_t *nn_lut,
                  uint32_t B, uint32_t H, uint32_t nb, uint32_t bs, uint32_t d, uint32_t blocks,
                  uint32_t lut_heads, float *c);
 
+/* out = act(x . w + bias), x [m,k], w [k,n], out [m,n] row-major, act 0 = none, 1 = the reference's GELU
+ * (matrixMulNNCPU matmul.h:101-118, bias ewops.h:10-17, gelu ewops.h:32-43).  bias may be NULL. */
+void orc_linear(float *out, const float *x, const float *w, const float *bias, uint32_t m, uint32_t n, uint32_t k, int act);
+
 /* magic-number division constants (blocksparse.h:1016-1043) */
 void orc_magicu64(uint32_t d, uint32_t *magic, uint32_t *shift);
 

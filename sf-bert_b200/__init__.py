@@ -17,13 +17,14 @@ F32, BF16, F16 = 0, 1, 2
 LAYOUT_FULL, LAYOUT_FIXED, LAYOUT_STRIDE, LAYOUT_SAWTOOTH, LAYOUT_LOCAL, LAYOUT_BIGBIRD = range(6)
 MASK_ALL, MASK_CAUSAL_DIAG, MASK_CAUSAL_ALL, MASK_LOCAL = range(4)
 NT_OP, NN_OP, TN_OP = 0, 1, 2
+ACT_NONE, ACT_GELU = 0, 1
 
 # every symbol include/sfbert_b200.h declares
 SYMBOLS = [
     "sfb_last_error", "sfb_version", "sfb_layout_generate", "sfb_lut_count", "sfb_lut_build", "sfb_mask_pack",
     "sfb_magicu64", "sfb_bst_sgemm_nt", "sfb_masked_softmax", "sfb_bst_sgemm_xn", "sfb_fused_sddmm_softmax",
     "sfb_fused_attention", "sfb_bias_residual_layernorm", "sfb_device_status", "sfb_bias_gelu", "sfb_lut_build_tn",
-    "sfb_masked_softmax_grad",
+    "sfb_masked_softmax_grad", "sfb_linear",
 ]
 
 if not os.path.exists(LIB_PATH):
@@ -45,6 +46,7 @@ lib.sfb_masked_softmax.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32]
 lib.sfb_bst_sgemm_xn.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 13
 lib.sfb_lut_build_tn.argtypes = [_vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp]
 lib.sfb_masked_softmax_grad.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32] + [_u32] * 8 + [_f32]
+lib.sfb_linear.argtypes = [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _i32, _i32]
 lib.sfb_fused_sddmm_softmax.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 10 + [_f32]
 lib.sfb_fused_attention.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32] + [_u32] * 9 + [_f32, _u32]
 lib.sfb_bias_residual_layernorm.argtypes = [_vp] * 10 + [_u32, _u32, _i32]
@@ -203,6 +205,18 @@ def bst_sgemm_xn(p, v, lay):
     _check(lib.sfb_bst_sgemm_xn(_stream(), _p(lay.nn_lut), _p(p), _p(v), _p(o), dtype_tag(p), dtype_tag(v), lay.block_size,
                                 lay.blocks, B, lay.nb, lay.nb, H, d, lay.heads, lay.nn_lut_dim, NN_OP, magic, shift,
                                 lay.nn_max))
+    return o
+
+
+def linear(x, w, bias=None, act=ACT_NONE, out=None):
+    """out = act(x . w + bias) on the tensor cores: x [..., k], w [k, n] row-major, 16-bit; bias fp32 [n].
+    The projections of the encoder layer with their bias add / GELU folded in
+    (transformer_attention_optimize.cu:693-716, 755-763, 773-793)."""
+    k, n = w.shape
+    assert x.shape[-1] == k and x.dtype == w.dtype and x.is_contiguous() and w.is_contiguous()
+    m = x.numel() // k
+    o = torch.empty(*x.shape[:-1], n, dtype=x.dtype, device=x.device) if out is None else out
+    _check(lib.sfb_linear(_stream(), _p(o), _p(x), _p(w), _p(bias), m, n, k, dtype_tag(x), act))
     return o
 
 

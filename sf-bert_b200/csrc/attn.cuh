@@ -38,4 +38,9 @@ int tc_fused_p(cudaStream_t s, const void *nn_lut, const void *a, const void *b,
                int y_dtype, const AttnDims &p, float scale);
 int tc_status_unfused(uint32_t *out);
 
+// tcgen05 dense projection (gemm_tc.cu)
+int tc_linear(cudaStream_t s, void *out, const void *x, const void *w, const float *bias, uint32_t m, uint32_t n, uint32_t k,
+              int dtype, int act);
+int tc_status_gemm(uint32_t *out);
+
 }  // namespace sfb

@@ -1,0 +1,244 @@
+// Dense projection on the 5th-generation tensor cores: out[m, n] = act(x[m, k] . w[k, n] + bias[n]) for 16-bit
+// x, w and out (fp32 accumulation, fp32 bias).  This is the product the encoder layer makes six times around the
+// block-sparse attention (Q/K/V/output projections, the two FFN matrices), with the bias add and the GELU that
+// the reference launches as separate kernels folded into the epilogue.
+//
+// Persistent, one CTA per SM.  A CTA tile is 128 rows x 256 columns: x arrives by TMA as a K-major A operand
+// (128 x 64 per stage), w -- row-major [k, n], so n is the contiguous direction -- as an MN-major B operand
+// (four 64 x 64 boxes per stage, one 128-byte swizzle span each; the descriptor's leading-dimension offset
+// steps from one to the next), four stages of 48 KB.  One thread issues M128 N256 K16 tcgen05.mma into one of
+// two 256-column accumulators in TMEM; eight epilogue warps drain the other one (tcgen05.ld, bias, activation,
+// 32-byte stores), so the epilogue of a tile runs under the MMAs of the next.
+// Every wait on an mbarrier is bounded; on a timeout the CTA records a status word and leaves through the
+// common teardown.
+#include "tc_common.cuh"
+
+namespace sfb {
+namespace tc {
+
+constexpr int kGStages = 4;
+constexpr uint32_t kGBM = 128, kGBN = 256, kGBK = 64;
+constexpr uint32_t kGABytes = kGBM * kGBK * 2;           // 16 KB
+constexpr uint32_t kGBBytes = kGBK * kGBN * 2;           // 32 KB: four 64 x 64 boxes
+constexpr uint32_t kGStageBytes = kGABytes + kGBBytes;
+
+struct GShared {
+    uint64_t full[kGStages], empty[kGStages], acc_full[2], acc_empty[2], drained;
+    uint32_t tmem_base, abort_flag;
+};
+constexpr size_t kGemmSmem = 1024 + kGStages * kGStageBytes + sizeof(GShared);
+
+struct GParams {
+    void *out;
+    const float *bias;
+    uint32_t M, N, K, tiles_m, tiles_n;
+    int is_bf16, act;
+};
+
+__device__ __forceinline__ float gelu_ref(float t)
+{
+    // x * sigmoid(1.702 x), the reference's GELU (gelu_gpu_v2, cuda_kernels.h:561-581)
+    return t / (1.f + __expf(-1.702f * t));
+}
+
+__global__ void __launch_bounds__(320, 1)
+linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const GParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *tiles = smem;                                   // stage s: A (16 KB) then B (32 KB)
+    GShared *st = (GShared *)(tiles + kGStages * kGStageBytes);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile uint32_t *abort_flag = &st->abort_flag;
+    const uint32_t fmt = p.is_bf16 ? 1u : 0u;
+    const uint32_t n_tiles = p.tiles_m * p.tiles_n;
+    const uint32_t kblocks = (p.K + kGBK - 1) / kGBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kGStages; s++) { mbar_init(&st->full[s], 1); mbar_init(&st->empty[s], 1); }
+        for (int s = 0; s < 2; s++) { mbar_init(&st->acc_full[s], 1); mbar_init(&st->acc_empty[s], 256); }
+        mbar_init(&st->drained, 1);
+        st->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&st->tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem = st->tmem_base;
+
+    if (warp == 0) {
+        // ===== TMA producer =====
+        if (lane == 0) {
+            uint32_t g = 0;   // k-blocks loaded so far (ring position)
+            for (uint32_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+                const int32_t m0 = (int32_t)((t % p.tiles_m) * kGBM), n0 = (int32_t)((t / p.tiles_m) * kGBN);
+                bool alive = true;
+                for (uint32_t kb = 0; kb < kblocks; kb++, g++) {
+                    const uint32_t s = g % kGStages;
+                    if (g >= kGStages && !mbar_wait(&st->empty[s], ((g / kGStages) - 1) & 1, abort_flag, 41)) { alive = false; break; }
+                    const uint32_t base = smem_u32(tiles + s * kGStageBytes);
+                    mbar_expect_tx(&st->full[s], kGStageBytes);   // boxes beyond the tensor arrive as zeros and still count
+                    tma_load_2d(base, &amap, &st->full[s], (int32_t)(kb * kGBK), m0);
+#pragma unroll
+                    for (uint32_t j = 0; j < 4; j++)
+                        tma_load_2d(base + kGABytes + j * kTileBytes, &bmap, &st->full[s], n0 + (int32_t)(j * 64), (int32_t)(kb * kGBK));
+                }
+                if (!alive) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer =====
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(fmt, fmt, kGBM, kGBN, 1);
+            uint32_t g = 0, i = 0;
+            for (uint32_t t = blockIdx.x; t < n_tiles; t += gridDim.x, i++) {
+                const uint32_t buf = i & 1;
+                bool alive = true;
+                if (i >= 2 && !mbar_wait(&st->acc_empty[buf], ((i >> 1) - 1) & 1, abort_flag, 42)) break;
+                tcgen05_fence_after();
+                for (uint32_t kb = 0; kb < kblocks; kb++, g++) {
+                    const uint32_t s = g % kGStages;
+                    if (!mbar_wait(&st->full[s], (g / kGStages) & 1, abort_flag, 43)) { alive = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t base = smem_u32(tiles + s * kGStageBytes);
+                    const uint64_t a_desc = smem_desc_sw128(base);
+                    const uint64_t b_desc = smem_desc_sw128(base + kGABytes, kTileBytes);   // next 64 columns: one box further on
+#pragma unroll
+                    for (uint32_t kk = 0; kk < 4; kk++)   // 16 of K per MMA: +32 bytes in A's swizzled rows, +16 rows (2048 bytes) in B
+                        umma_f16(tmem + buf * kGBN, a_desc + 2 * kk, b_desc + 128 * kk, idesc, (kb | kk) ? 1u : 0u);
+                    umma_commit(&st->empty[s]);
+                }
+                if (!alive) break;
+                umma_commit(&st->acc_full[buf]);
+            }
+        }
+    } else {
+        // ===== epilogue: eight warps; a thread takes one output row and half of the tile's 256 columns, 32 at a time =====
+        const uint32_t quarter = warp & 3;                 // TMEM lanes this warp may touch
+        const uint32_t chalf = (warp - 2) >> 2;            // which 128 columns
+        const uint32_t r = quarter * 32 + lane;
+        const uint32_t lane_field = (quarter * 32) << 16;
+        uint32_t i = 0;
+        for (uint32_t t = blockIdx.x; t < n_tiles; t += gridDim.x, i++) {
+            const uint32_t buf = i & 1;
+            const uint32_t m0 = (t % p.tiles_m) * kGBM, n0 = (t / p.tiles_m) * kGBN + chalf * 128;
+            if (!mbar_wait_warp(&st->acc_full[buf], (i >> 1) & 1, abort_flag, 44)) break;
+            tcgen05_fence_after();
+            const bool row_ok = m0 + r < p.M;
+            const size_t off = (size_t)(m0 + r) * p.N + n0;
+            const uint32_t tcol = tmem + buf * kGBN + chalf * 128 + lane_field;
+            uint32_t v[2][32];
+            TMEM_LD_32((v[0]), tcol);
+#pragma unroll
+            for (uint32_t c = 0; c < 4; c++) {
+                const uint32_t c0 = c * 32;
+                tmem_wait_ld();
+                if (c + 1 < 4) TMEM_LD_32((v[(c + 1) & 1]), tcol + c0 + 32);   // the next 32 columns travel while these are written
+                uint32_t(&cur)[32] = v[c & 1];
+#pragma unroll
+                for (uint32_t q = 0; q < 2; q++) {
+                    const uint32_t col = n0 + c0 + q * 16;
+                    if (row_ok && col < p.N) {      // N is a multiple of 16: a group of 16 is inside or outside as a whole
+                        float x[16];
+#pragma unroll
+                        for (int j = 0; j < 16; j++) x[j] = __uint_as_float(cur[q * 16 + j]);
+                        if (p.bias) {
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                const float4 bb = __ldg((const float4 *)(p.bias + col) + j);   // the same address in every lane: one broadcast
+                                x[4 * j] += bb.x; x[4 * j + 1] += bb.y; x[4 * j + 2] += bb.z; x[4 * j + 3] += bb.w;
+                            }
+                        }
+                        if (p.act == 1) {
+#pragma unroll
+                            for (int j = 0; j < 16; j++) x[j] = gelu_ref(x[j]);
+                        }
+                        uint32_t w[8];
+#pragma unroll
+                        for (int j = 0; j < 8; j++) w[j] = pack2(x[2 * j], x[2 * j + 1], p.is_bf16);
+                        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"((uint16_t *)p.out + off + c0 + q * 16),
+                                     "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                                     : "memory");
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            mbar_arrive(&st->acc_empty[buf]);
+        }
+    }
+
+    // ---- teardown (also the way out after a timeout) ----
+    tcgen05_fence_before();
+    __syncthreads();
+    if (st->abort_flag) {
+        if (warp == 1 && lane == 0) {
+            umma_commit(&st->drained);
+            for (uint32_t k = 0; k < kWaitLimit && !mbar_try_wait(&st->drained, 0); k++) {}
+        }
+        if (warp == 0 && lane == 0) {
+            const uint64_t t0 = clock64();
+            while (clock64() - t0 < 2000000ull) {}
+        }
+        __syncthreads();
+    }
+    if (warp == 0) {
+        __syncwarp();
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// [rows, cols] 16-bit row-major tensor, boxes of box_rows x 64 elements, 128-byte swizzle
+static int make_map_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, int is_bf16, uint32_t box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail("cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)base, dims,
+                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+}  // namespace tc
+
+int tc_linear(cudaStream_t s, void *out, const void *x, const void *w, const float *bias, uint32_t m, uint32_t n, uint32_t k,
+              int dtype, int act)
+{
+    using namespace tc;
+    const int is_bf16 = dtype == SFB_BF16;
+    CUtensorMap am, bm;
+    if (make_map_2d(&am, x, m, k, is_bf16, kGBM) || make_map_2d(&bm, w, k, n, is_bf16, kGBK)) return 1;
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+            return fail("sfb_linear: cannot read the SM count");
+        if (cudaFuncSetAttribute(linear_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem) != cudaSuccess)
+            return fail("sfb_linear: cannot reserve %zu bytes of shared memory", kGemmSmem);
+        sms = v;
+    }
+    GParams prm = {out, bias, m, n, k, (m + kGBM - 1) / kGBM, (n + kGBN - 1) / kGBN, is_bf16, act};
+    const uint32_t tiles = prm.tiles_m * prm.tiles_n;
+    linear_tc_kernel<<<tiles < (uint32_t)sms ? tiles : (uint32_t)sms, 320, kGemmSmem, s>>>(am, bm, prm);
+    return check_launch("sfb_linear");
+}
+
+int tc_status_gemm(uint32_t *out)
+{
+    cudaError_t e = cudaMemcpyFromSymbol(out, tc::g_status, sizeof(uint32_t));
+    if (e != cudaSuccess) return fail("sfb_device_status: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+}  // namespace sfb

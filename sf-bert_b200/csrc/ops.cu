@@ -126,12 +126,27 @@ extern "C" int sfb_fused_attention(sfb_stream_t stream, const void *nn_lut, cons
     return simt_fused_attention(as_stream(stream), nn_lut, q, k, v, o, mask, dtype, block_size, p, scale);
 }
 
+extern "C" int sfb_linear(sfb_stream_t stream, void *out, const void *x, const void *w, const float *bias, uint32_t m, uint32_t n,
+                          uint32_t k, int dtype, int act)
+{
+    const char *who = "sfb_linear";
+    SFB_REQUIRE(out && x && w, "%s: NULL pointer", who);
+    SFB_REQUIRE(dtype == SFB_BF16 || dtype == SFB_F16, "%s: x, w and out must be bf16 or fp16 (fp32 products stay with the GEMM library)", who);
+    SFB_REQUIRE(act == SFB_ACT_NONE || act == SFB_ACT_GELU, "%s: unknown activation %d", who, act);
+    SFB_REQUIRE(n % 16 == 0 && k % 8 == 0, "%s: n=%u must be a multiple of 16 and k=%u of 8", who, n, k);
+    SFB_REQUIRE(aligned16(x) && aligned16(w) && ((uintptr_t)out & 31) == 0, "%s: x, w must be 16-byte and out 32-byte aligned", who);
+    SFB_REQUIRE((uint64_t)m < (1ull << 31) && (uint64_t)n < (1ull << 31) && (uint64_t)k < (1ull << 31), "%s: dimension too large", who);
+    if (m == 0 || n == 0) { clear_error(); return 0; }
+    SFB_REQUIRE(k > 0, "%s: k is 0", who);
+    return tc_linear(as_stream(stream), out, x, w, bias, m, n, k, dtype, act);
+}
+
 extern "C" int sfb_device_status(uint32_t *status)
 {
     SFB_REQUIRE(status, "sfb_device_status: NULL pointer");
-    uint32_t a = 0, b = 0;
-    if (tc_status_fused(&a) || tc_status_unfused(&b)) return 1;
-    *status = a ? a : b;
+    uint32_t a = 0, b = 0, c = 0;
+    if (tc_status_fused(&a) || tc_status_unfused(&b) || tc_status_gemm(&c)) return 1;
+    *status = a ? a : b ? b : c;
     clear_error();
     return 0;
 }

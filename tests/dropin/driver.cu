@@ -3,6 +3,9 @@
 // (include/blocksparse.h, include/fusion_blocksparse.h) with the reference's argument order.  Inputs are
 // all ones, the reference's own known answer (fixed_fusion_test.cu:263-268, test.cu:382-386): every score
 // equals d, every probability 1 / (kept keys of the row), every output 1.
+// The backward follows with the reference's call order (transformer_attention_optimize.cu:924-964) and dO = 1:
+// dV[key j] = sum over the rows r >= j of 1/(r+1), dP = d everywhere, and dS, dQ, dK vanish up to the bf16
+// rounding of P (a softmax whose upstream gradient is constant along the row has none).
 // Prints "PASS" and returns 0 when all of that holds on the GPU.
 #include <cstdio>
 #include <cstdlib>
@@ -96,6 +99,40 @@ int main()
     ok = ok && fusion_attention<float, float2>(custream, d_nt, a_ptr, b_ptr, c_ptr, d_nn, flag, flag1, d_mask_np, Max, Sum, y_ptr,
                                                v_ptr, o2_ptr, blk_size_, blocks, batch_dim, ctx_blks_, ctx_blks_, ctx_blks_, heads_,
                                                head_state_, lut_heads, blocks, mask_heads, scale, nn_max);
+    // the backward, as transformer_attention_optimize.cu:924-964 calls it; tn_lut as generate_tn_lut builds it (ewops.h:675-701)
+    std::vector<uint2> tn(ctx_blks_ + blocks, make_uint2(0, 0));
+    {
+        uint sum = ctx_blks_, cnt = ctx_blks_, at = ctx_blks_;
+        for (uint c = 0; c < ctx_blks_; c++) {
+            tn[c] = make_uint2(sum, cnt);
+            sum += cnt;
+            cnt--;
+        }
+        for (uint col = 0; col < ctx_blks_; col++)
+            for (uint row = col; row < ctx_blks_; row++) tn[at++] = make_uint2(row * (row + 1) / 2 + col, row);
+    }
+    uint2 *d_tn;
+    float *dv_ptr, *dk_ptr, *dq_ptr;
+    bhalf *dw_ptr, *dx_ptr;
+    cudaMalloc(&d_tn, sizeof(uint2) * tn.size());
+    cudaMalloc(&dv_ptr, sizeof(float) * n_in);
+    cudaMalloc(&dk_ptr, sizeof(float) * n_in);
+    cudaMalloc(&dq_ptr, sizeof(float) * n_in);
+    cudaMalloc(&dw_ptr, sizeof(bhalf) * n_blk);
+    cudaMalloc(&dx_ptr, sizeof(bhalf) * n_blk);
+    cudaMemcpy(d_tn, tn.data(), sizeof(uint2) * tn.size(), cudaMemcpyHostToDevice);
+    const uint tn_max = ctx_blks_;
+    float *do_ptr = v_ptr;   // all ones
+    ok = ok && bst_sgemm_xn(custream, d_tn, y2_ptr, do_ptr, dv_ptr, blk_size_, blocks, batch_dim, ctx_blks_, ctx_blks_, heads_,
+                            head_state_, lut_heads, blocks + ctx_blks_, TN_OP, magic_, shift_, tn_max);
+    ok = ok && bst_sgemm_nt(custream, d_nt, do_ptr, v_ptr, dw_ptr, blk_size_, blocks, batch_dim, ctx_blks_, ctx_blks_, heads_,
+                            head_state_, lut_heads, blocks);
+    ok = ok && BlocksparseMaskedSoftmaxGrad<bhalf, bhalf2>(custream, d_nn, dw_ptr, y2_ptr, dx_ptr, blk_size_, blocks, batch_dim,
+                                                           heads_, ctx_blks_, lut_heads, blocks + ctx_blks_, nn_max, scale);
+    ok = ok && bst_sgemm_xn(custream, d_tn, dx_ptr, a_ptr, dk_ptr, blk_size_, blocks, batch_dim, ctx_blks_, ctx_blks_, heads_,
+                            head_state_, lut_heads, blocks + ctx_blks_, TN_OP, magic_, shift_, tn_max);
+    ok = ok && bst_sgemm_xn(custream, d_nn, dx_ptr, b_ptr, dq_ptr, blk_size_, blocks, batch_dim, ctx_blks_, ctx_blks_, heads_,
+                            head_state_, lut_heads, blocks + ctx_blks_, NN_OP, magic_, shift_, nn_max);
     // an unsupported block size is reported, not silently ignored
     const bool rejected = !bst_sgemm_nt(custream, d_nt, a_ptr, b_ptr, c_ptr, 16, blocks, batch_dim, ctx_blks_, ctx_blks_, heads_,
                                         head_state_, lut_heads, blocks);
@@ -125,6 +162,22 @@ int main()
             }
     for (size_t i = 0; i < n_in; i++) bad += fabsf(o_h[i] - 1.0f) > 1e-2f;   // bf16 probabilities on this path
     for (size_t i = 0; i < n_in; i++) bad += fabsf(o2_h[i] - 1.0f) > 1e-5f;
+    std::vector<float> dv_h(n_in), dk_h(n_in), dq_h(n_in);
+    std::vector<bhalf> dw_h(n_blk);
+    cudaMemcpy(dv_h.data(), dv_ptr, sizeof(float) * n_in, cudaMemcpyDeviceToHost);
+    cudaMemcpy(dk_h.data(), dk_ptr, sizeof(float) * n_in, cudaMemcpyDeviceToHost);
+    cudaMemcpy(dq_h.data(), dq_ptr, sizeof(float) * n_in, cudaMemcpyDeviceToHost);
+    cudaMemcpy(dw_h.data(), dw_ptr, sizeof(bhalf) * n_blk, cudaMemcpyDeviceToHost);
+    for (size_t i = 0; i < n_blk; i++) bad += bf(dw_h[i].x) != (float)head_state_;
+    std::vector<double> tail(seq_len + 1, 0.0);   // tail[j] = sum over r >= j of 1/(r+1)
+    for (int r = (int)seq_len - 1; r >= 0; r--) tail[r] = tail[r + 1] + 1.0 / (r + 1);
+    const size_t row_elems = (size_t)heads_ * head_state_;
+    for (size_t i = 0; i < n_in; i++) {
+        const size_t key = (i / row_elems) % seq_len;
+        bad += fabs(dv_h[i] - tail[key]) > 2e-2 * tail[key];
+        bad += fabsf(dk_h[i]) > 0.5f;
+        bad += fabsf(dq_h[i]) > 0.5f;
+    }
     printf(bad ? "FAIL: %zu wrong values\n" : "PASS\n", bad);
     return bad ? 1 : 0;
 }

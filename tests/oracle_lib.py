@@ -198,6 +198,30 @@ def spmm_nn(a, b, nn, bs):
     return _spmm(lib().orc_spmm_nn, a, b, nn, bs)
 
 
+def linear(x, w, bias=None, act=0):
+    """out = act(x . w + bias), x [m,k], w [k,n]; act 1 = the reference's GELU."""
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    m, k = x.shape
+    n = w.shape[1]
+    out = np.zeros((m, n), np.float32)
+    b = None if bias is None else np.ascontiguousarray(bias, np.float32)
+    lib().orc_linear(_ptr(out, _f32p), _ptr(x, _f32p), _ptr(w, _f32p), None if b is None else _ptr(b, _f32p),
+                     C.c_uint32(m), C.c_uint32(n), C.c_uint32(k), C.c_int(act))
+    return out
+
+
+def ref_matmul_nn(a, b):
+    """matrixMulNNCPU of the reference (matmul.h:101-118)."""
+    R = ref()
+    assert R is not None
+    a = np.ascontiguousarray(a, np.float32)
+    b = np.ascontiguousarray(b, np.float32)
+    c = np.zeros((a.shape[0], b.shape[1]), np.float32)
+    R.ref_matrixMulNNCPU(_ptr(c, _f32p), _ptr(a, _f32p), _ptr(b, _f32p), C.c_int(a.shape[0]), C.c_int(a.shape[1]), C.c_int(b.shape[1]))
+    return c
+
+
 def bias_residual_layernorm(x, bias, resid, gain, beta):
     x = np.ascontiguousarray(x, np.float32)
     m, hidden = x.shape

@@ -250,3 +250,15 @@ def test_backward_matches_reference_cpu_operators(oracle):
     assert np.array_equal(bhld(oracle.spmm_nn(ds, k, luts["nn"], bs)), g["bwd/dq"])
     assert np.array_equal(bhld(oracle.spmm_tn(ds, q, tn, bs)), g["bwd/dk"])
 
+
+def test_linear_matches_live_reference_when_built(oracle):
+    """orc_linear against the reference's matrixMulNNCPU (+ its bias and gelu, pinned above) -- bit-exact."""
+    if oracle.ref() is None:
+        pytest.skip("oracle/_ref not built on this machine")
+    x = oracle.fill_normal((37, 72), 51)
+    w = oracle.fill_normal((72, 48), 52, 0.02)
+    b = oracle.fill_normal((48,), 53, 0.1)
+    plain = oracle.ref_matmul_nn(x, w)
+    assert np.array_equal(oracle.linear(x, w), plain)
+    assert np.array_equal(oracle.linear(x, w, b, act=1), oracle.ref_bias_gelu(plain, b))
+
