@@ -390,7 +390,8 @@ def run_encoder_layer(args, sfb, cfg, pk, flush):
     lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
     w = enc.EncoderLayerWeights(hidden, ffn, tdt, seed=1)
     x = torch.randn(B, L, hidden, device="cuda").to(tdt)
-    fn = lambda: enc.encoder_layer(sfb, x, w, lay, H, "post")
+    proj = "tensor" if args.projections == "tensor" and tdt != torch.float32 else "library"
+    fn = lambda: enc.encoder_layer(sfb, x, w, lay, H, "post", proj)
     for _ in range(max(args.warmup, 3)):
         fn()
     torch.cuda.synchronize()
@@ -411,7 +412,8 @@ def run_encoder_layer(args, sfb, cfg, pk, flush):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": True,
         "dtype": cfg["dtype"], "data": "synthetic",
         "config": {"workload": args.config, "B": B, "L": L, "hidden": hidden, "ffn": ffn, "heads": H, "ln": "post",
-                   "projections": "torch.matmul (cuBLAS)", "l2": "flushed between timed steps"},
+                   "projections": "sfb_linear (tcgen05, bias/GELU in the epilogue)" if proj == "tensor" else "torch.matmul (cuBLAS)",
+                   "l2": "flushed between timed steps"},
         "tflops_total": round((gemm_flops + attn_flops) / (ms * 1e-3) / 1e12, 1),
         "gpu_launches": args.steps * 4, "clocks": clocks}), flush=True)
 
@@ -492,6 +494,8 @@ if __name__ == "__main__":
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer", "softmax_grad", "spmm_tn", "linear"],
                     help="fused = the headline fused attention; softmax / layernorm = the bandwidth kernels (N=1)")
+    ap.add_argument("--projections", default="tensor", choices=["tensor", "library"],
+                    help="--kernel encoder_layer: the layer's GEMMs on this library's tcgen05 kernel or on the GEMM library")
     a = ap.parse_args()
     if a.impl == "reference":
         run_reference(a)

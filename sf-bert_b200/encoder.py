@@ -5,9 +5,10 @@ reference's driver (transformer_attention_optimize.cu:688-801 / transformer_infe
                               h2 = LN(x1); x2 = x1 + GELU(h2 W1 + b1) W2 + b2
     post-LN (BERT):           x1 = LN(x + Attn(...)Wo + bo); x2 = LN(x1 + GELU(x1 W1 + b1) W2 + b2)
 
-The dense projections are plain library GEMMs (torch.matmul -> cuBLAS; the reference calls cublasSgemm
-there).  Everything else -- attention, bias + residual + LayerNorm, bias + GELU -- is this library's
-kernels.  Dropout is off (keep probability 1), as in every parity run."""
+The dense projections are either plain library GEMMs (projections="library": torch.matmul -> cuBLAS; the
+reference calls cublasSgemm there) or this library's tcgen05 kernel with the bias add / GELU in its epilogue
+(projections="tensor", 16-bit operands).  Everything else -- attention, bias + residual + LayerNorm, bias +
+GELU -- is this library's kernels.  Dropout is off (keep probability 1), as in every parity run."""
 import math
 
 import torch
@@ -26,13 +27,15 @@ class EncoderLayerWeights:
         self.be1, self.be2 = z(hidden), z(hidden)
 
 
-def encoder_layer(sfb, x, w, lay, heads, ln_order="post"):
+def encoder_layer(sfb, x, w, lay, heads, ln_order="post", projections="library"):
     """x [B, L, hidden] -> [B, L, hidden].  `sfb` is the loaded package, `lay` a BlockLayout."""
     B, L, hidden = x.shape
     d = hidden // heads
     m = B * L
     x2d = x.reshape(m, hidden)
     scale = 1.0 / math.sqrt(d)
+    if projections == "tensor":
+        return _encoder_layer_tensor(sfb, x2d, w, lay, heads, ln_order, scale).view(B, L, hidden)
 
     def attn(h2d):
         q = torch.addmm(w.bq.to(h2d.dtype), h2d, w.wq).view(B, L, heads, d)
@@ -53,3 +56,32 @@ def encoder_layer(sfb, x, w, lay, heads, ln_order="post"):
     y = torch.mm(f, w.w2)
     out, _, _, _ = sfb.bias_residual_layernorm(y, w.b2, x1, w.g2, w.be2)
     return out.view(B, L, hidden)
+
+
+def _encoder_layer_tensor(sfb, x2d, w, lay, heads, ln_order, scale):
+    """The same layer with every projection on sfb.linear: biases and the GELU ride in the GEMM epilogues, so the
+    layer is 3 + 1 + 2 projections, the attention and two LayerNorm launches."""
+    m, hidden = x2d.shape
+    d = hidden // heads
+    L = lay.nb * lay.block_size
+    B = m // L
+
+    def attn(h2d):
+        q = sfb.linear(h2d, w.wq, w.bq).view(B, L, heads, d)
+        k = sfb.linear(h2d, w.wk, w.bk).view(B, L, heads, d)
+        v = sfb.linear(h2d, w.wv, w.bv).view(B, L, heads, d)
+        return sfb.fused_attention(q, k, v, lay, scale).view(m, hidden)
+
+    if ln_order == "pre":
+        h, _, _, _ = sfb.bias_residual_layernorm(x2d, None, None, w.g1, w.be1)
+        a = sfb.linear(attn(h), w.wo)
+        h2, x1, _, _ = sfb.bias_residual_layernorm(a, w.bo, x2d, w.g2, w.be2, want_sum=True)
+        f = sfb.linear(h2, w.w1, w.b1, sfb.ACT_GELU)
+        return x1 + sfb.linear(f, w.w2, w.b2)
+    a = sfb.linear(attn(x2d), w.wo)
+    x1, _, _, _ = sfb.bias_residual_layernorm(a, w.bo, x2d, w.g1, w.be1)
+    f = sfb.linear(x1, w.w1, w.b1, sfb.ACT_GELU)
+    y = sfb.linear(f, w.w2)
+    out, _, _, _ = sfb.bias_residual_layernorm(y, w.b2, x1, w.g2, w.be2)
+    return out
+

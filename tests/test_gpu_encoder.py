@@ -1,5 +1,5 @@
 """The encoder layer built around the path (attention + bias/residual/LayerNorm + bias/GELU from this
-library, projections from the GEMM library) against the CPU oracle: the reference's operator order
+library, projections from the GEMM library or from this library's tcgen05 kernel) against the CPU oracle: the reference's operator order
 (transformer_inference_part.cpp:210-239) with its matrixMulNNCPU standing in for cblas_sgemm."""
 import importlib.util
 import os
@@ -44,10 +44,11 @@ def _cpu_layer(O, x, w, luts, heads, bs, order):
 
 
 @pytest.mark.parametrize("order", ["pre", "post"])
-@pytest.mark.parametrize("dtype,bs,tol", [("f32", 32, 2e-4), ("bf16", 64, 3e-2)])
-def test_encoder_layer(sfb, oracle, order, dtype, bs, tol):
+@pytest.mark.parametrize("dtype,bs,tol,proj", [("f32", 32, 2e-4, "library"), ("bf16", 64, 3e-2, "library"), ("bf16", 64, 3e-2, "tensor"),
+                                               ("f16", 64, 3e-2, "tensor")])
+def test_encoder_layer(sfb, oracle, order, dtype, bs, tol, proj):
     enc = _encoder()
-    tdt = {"f32": torch.float32, "bf16": torch.bfloat16}[dtype]
+    tdt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[dtype]
     B, L, heads, hidden, ffn = 2, 256, 4, 256, 512
     nb = L // bs
     lay = sfb.BlockLayout.generate(sfb.LAYOUT_STRIDE, 1, nb, bs, p0=2, p1=4)
@@ -56,7 +57,7 @@ def test_encoder_layer(sfb, oracle, order, dtype, bs, tol):
     for name in ("bq", "bk", "bv", "bo", "b1", "b2", "be1", "be2"):
         getattr(w, name).copy_(torch.from_numpy(oracle.fill_normal(tuple(getattr(w, name).shape), hash(name) % 1000, 0.1)))
     x = torch.from_numpy(oracle.fill_normal((B, L, hidden), 77)).cuda().to(tdt)
-    y = enc.encoder_layer(sfb, x, w, lay, heads, order).float().cpu().numpy()
+    y = enc.encoder_layer(sfb, x, w, lay, heads, order, proj).float().cpu().numpy()
     assert sfb.device_status() == 0
     want = _cpu_layer(oracle, x.float().cpu().numpy(), w, luts, heads, bs, order)
     assert np.abs(y - want).max() <= tol * max(1.0, np.abs(want).max())
