@@ -12,21 +12,30 @@
 // Every wait on an mbarrier is bounded; on a timeout the CTA records a status word and leaves through the
 // common teardown.
 #include "tc_common.cuh"
+#include <cstdlib>
 
 namespace sfb {
 namespace tc {
 
-constexpr int kGStages = 4;
 constexpr uint32_t kGBM = 128, kGBN = 256, kGBK = 64;
-constexpr uint32_t kGABytes = kGBM * kGBK * 2;           // 16 KB
+constexpr uint32_t kGABytes = kGBM * kGBK * 2;           // 16 KB per 128 rows
 constexpr uint32_t kGBBytes = kGBK * kGBN * 2;           // 32 KB: four 64 x 64 boxes
-constexpr uint32_t kGStageBytes = kGABytes + kGBBytes;
+// MT = row sub-tiles of 128 per CTA tile.  MT = 1: 128 x 256 tiles, two accumulators, the epilogue of a tile runs
+// under the MMAs of the next.  MT = 2: 256 x 256 tiles -- both sub-tiles multiply the same w boxes, so a third less
+// travels from L2 per flop, which is what long-k products are bound by -- at the price of a single accumulator set.
+template <int MT> struct GCfg {
+    static constexpr int stages = MT == 1 ? 4 : 3;
+    static constexpr int acc_bufs = MT == 1 ? 2 : 1;
+    static constexpr uint32_t stage_bytes = MT * kGABytes + kGBBytes;
+    static constexpr size_t smem = 1024 + stages * stage_bytes + 256;
+};
+constexpr int kGMaxStages = 4;
 
 struct GShared {
-    uint64_t full[kGStages], empty[kGStages], acc_full[2], acc_empty[2], drained;
+    uint64_t full[kGMaxStages], empty[kGMaxStages], acc_full[2], acc_empty[2], drained;
     uint32_t tmem_base, abort_flag;
 };
-constexpr size_t kGemmSmem = 1024 + kGStages * kGStageBytes + sizeof(GShared);
+static_assert(sizeof(GShared) <= 256, "GShared outgrew its slot");
 
 struct GParams {
     void *out;
@@ -38,12 +47,15 @@ struct GParams {
 __device__ __forceinline__ float gelu_ref(float t)
 {
     // x * sigmoid(1.702 x), the reference's GELU (gelu_gpu_v2, cuda_kernels.h:561-581)
-    return t / (1.f + __expf(-1.702f * t));
+    return __fdividef(t, 1.f + __expf(-1.702f * t));
 }
 
+template <int MT>
 __global__ void __launch_bounds__(320, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const GParams p)
 {
+    constexpr int kGStages = GCfg<MT>::stages, kBufs = GCfg<MT>::acc_bufs;
+    constexpr uint32_t kGStageBytes = GCfg<MT>::stage_bytes, kBBase = MT * kGABytes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *tiles = smem;                                   // stage s: A (16 KB) then B (32 KB)
@@ -77,17 +89,19 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
         if (lane == 0) {
             uint32_t g = 0;   // k-blocks loaded so far (ring position)
             for (uint32_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-                const int32_t m0 = (int32_t)((t % p.tiles_m) * kGBM), n0 = (int32_t)((t / p.tiles_m) * kGBN);
+                const int32_t m0 = (int32_t)((t % p.tiles_m) * (MT * kGBM)), n0 = (int32_t)((t / p.tiles_m) * kGBN);
                 bool alive = true;
                 for (uint32_t kb = 0; kb < kblocks; kb++, g++) {
                     const uint32_t s = g % kGStages;
                     if (g >= kGStages && !mbar_wait(&st->empty[s], ((g / kGStages) - 1) & 1, abort_flag, 41)) { alive = false; break; }
                     const uint32_t base = smem_u32(tiles + s * kGStageBytes);
                     mbar_expect_tx(&st->full[s], kGStageBytes);   // boxes beyond the tensor arrive as zeros and still count
-                    tma_load_2d(base, &amap, &st->full[s], (int32_t)(kb * kGBK), m0);
+#pragma unroll
+                    for (uint32_t mt = 0; mt < MT; mt++)
+                        tma_load_2d(base + mt * kGABytes, &amap, &st->full[s], (int32_t)(kb * kGBK), m0 + (int32_t)(mt * kGBM));
 #pragma unroll
                     for (uint32_t j = 0; j < 4; j++)
-                        tma_load_2d(base + kGABytes + j * kTileBytes, &bmap, &st->full[s], n0 + (int32_t)(j * 64), (int32_t)(kb * kGBK));
+                        tma_load_2d(base + kBBase + j * kTileBytes, &bmap, &st->full[s], n0 + (int32_t)(j * 64), (int32_t)(kb * kGBK));
                 }
                 if (!alive) break;
             }
@@ -98,20 +112,23 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
             const uint32_t idesc = instr_desc(fmt, fmt, kGBM, kGBN, 1);
             uint32_t g = 0, i = 0;
             for (uint32_t t = blockIdx.x; t < n_tiles; t += gridDim.x, i++) {
-                const uint32_t buf = i & 1;
+                const uint32_t buf = i % kBufs;
                 bool alive = true;
-                if (i >= 2 && !mbar_wait(&st->acc_empty[buf], ((i >> 1) - 1) & 1, abort_flag, 42)) break;
+                if (i >= (uint32_t)kBufs && !mbar_wait(&st->acc_empty[buf], ((i / kBufs) - 1) & 1, abort_flag, 42)) break;
                 tcgen05_fence_after();
                 for (uint32_t kb = 0; kb < kblocks; kb++, g++) {
                     const uint32_t s = g % kGStages;
                     if (!mbar_wait(&st->full[s], (g / kGStages) & 1, abort_flag, 43)) { alive = false; break; }
                     tcgen05_fence_after();
                     const uint32_t base = smem_u32(tiles + s * kGStageBytes);
-                    const uint64_t a_desc = smem_desc_sw128(base);
-                    const uint64_t b_desc = smem_desc_sw128(base + kGABytes, kTileBytes);   // next 64 columns: one box further on
+                    const uint64_t b_desc = smem_desc_sw128(base + kBBase, kTileBytes);   // next 64 columns: one box further on
 #pragma unroll
-                    for (uint32_t kk = 0; kk < 4; kk++)   // 16 of K per MMA: +32 bytes in A's swizzled rows, +16 rows (2048 bytes) in B
-                        umma_f16(tmem + buf * kGBN, a_desc + 2 * kk, b_desc + 128 * kk, idesc, (kb | kk) ? 1u : 0u);
+                    for (uint32_t mt = 0; mt < MT; mt++) {
+                        const uint64_t a_desc = smem_desc_sw128(base + mt * kGABytes);
+#pragma unroll
+                        for (uint32_t kk = 0; kk < 4; kk++)   // 16 of K per MMA: +32 bytes in A's swizzled rows, +16 rows (2048 bytes) in B
+                            umma_f16(tmem + (buf * MT + mt) * kGBN, a_desc + 2 * kk, b_desc + 128 * kk, idesc, (kb | kk) ? 1u : 0u);
+                    }
                     umma_commit(&st->empty[s]);
                 }
                 if (!alive) break;
@@ -126,13 +143,16 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
         const uint32_t lane_field = (quarter * 32) << 16;
         uint32_t i = 0;
         for (uint32_t t = blockIdx.x; t < n_tiles; t += gridDim.x, i++) {
-            const uint32_t buf = i & 1;
-            const uint32_t m0 = (t % p.tiles_m) * kGBM, n0 = (t / p.tiles_m) * kGBN + chalf * 128;
-            if (!mbar_wait_warp(&st->acc_full[buf], (i >> 1) & 1, abort_flag, 44)) break;
+            const uint32_t buf = i % kBufs;
+            const uint32_t n0 = (t / p.tiles_m) * kGBN + chalf * 128;
+            if (!mbar_wait_warp(&st->acc_full[buf], (i / kBufs) & 1, abort_flag, 44)) break;
             tcgen05_fence_after();
+#pragma unroll 1
+            for (uint32_t mt = 0; mt < MT; mt++) {
+            const uint32_t m0 = (t % p.tiles_m) * (MT * kGBM) + mt * kGBM;
             const bool row_ok = m0 + r < p.M;
             const size_t off = (size_t)(m0 + r) * p.N + n0;
-            const uint32_t tcol = tmem + buf * kGBN + chalf * 128 + lane_field;
+            const uint32_t tcol = tmem + (buf * MT + mt) * kGBN + chalf * 128 + lane_field;
             uint32_t v[2][32];
             TMEM_LD_32((v[0]), tcol);
 #pragma unroll
@@ -167,6 +187,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
                                      : "memory");
                     }
                 }
+            }
             }
             tcgen05_fence_before();
             mbar_arrive(&st->acc_empty[buf]);
@@ -224,13 +245,20 @@ int tc_linear(cudaStream_t s, void *out, const void *x, const void *w, const flo
         int dev = 0, v = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
             return fail("sfb_linear: cannot read the SM count");
-        if (cudaFuncSetAttribute(linear_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem) != cudaSuccess)
-            return fail("sfb_linear: cannot reserve %zu bytes of shared memory", kGemmSmem);
+        if (cudaFuncSetAttribute(linear_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GCfg<1>::smem) != cudaSuccess ||
+            cudaFuncSetAttribute(linear_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GCfg<2>::smem) != cudaSuccess)
+            return fail("sfb_linear: cannot reserve %zu bytes of shared memory", GCfg<1>::smem);
         sms = v;
     }
-    GParams prm = {out, bias, m, n, k, (m + kGBM - 1) / kGBM, (n + kGBN - 1) / kGBN, is_bf16, act};
+    // long-k products are bound by what travels from L2: 256-row tiles, as long as they still fill the SMs twice over
+    const uint32_t tiles_n = (n + kGBN - 1) / kGBN;
+    int mt = (k >= 2048 && (uint64_t)((m + 255) / 256) * tiles_n >= 2ull * sms) ? 2 : 1;
+    if (const char *force = getenv("SFB_LINEAR_MT")) mt = force[0] == '2' ? 2 : 1;
+    GParams prm = {out, bias, m, n, k, (m + mt * kGBM - 1) / (mt * kGBM), tiles_n, is_bf16, act};
     const uint32_t tiles = prm.tiles_m * prm.tiles_n;
-    linear_tc_kernel<<<tiles < (uint32_t)sms ? tiles : (uint32_t)sms, 320, kGemmSmem, s>>>(am, bm, prm);
+    const uint32_t grid = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
+    if (mt == 2) linear_tc_kernel<2><<<grid, 320, GCfg<2>::smem, s>>>(am, bm, prm);
+    else linear_tc_kernel<1><<<grid, 320, GCfg<1>::smem, s>>>(am, bm, prm);
     return check_launch("sfb_linear");
 }
 
