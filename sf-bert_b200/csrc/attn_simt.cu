@@ -162,20 +162,22 @@ __device__ __forceinline__ float ex2_fast(float x)
 // lane in flight) and stay in registers: one pass over HBM, one exponential per element.
 // NB == 0: rows of any length.  Pass 1 finds the row maximum, pass 2 the sum of exponentials, pass 3 writes;
 // passes 2 and 3 re-read scores this CTA has just pulled through L2.
-template <int BS, int X_DT, int Y_DT, int NB>
-__global__ void __launch_bounds__(BS * BS / 8) softmax_kernel(const uint2 *__restrict__ lut,
-                                                        const typename MaskWord<BS>::type *__restrict__ mask,
-                                                        const void *__restrict__ X, void *__restrict__ Y, AttnDims p,
-                                                        float scale_log2e, int rescale_in_place)
+// SPLIT > 1: the block-row is shared by SPLIT CTAs of BS/SPLIT query rows each (more registers per thread for the
+// register-resident variant of longer rows).
+template <int BS, int X_DT, int Y_DT, int NB, int SPLIT>
+__global__ void __launch_bounds__(BS * BS / 8 / SPLIT) softmax_kernel(const uint2 *__restrict__ lut,
+                                                                const typename MaskWord<BS>::type *__restrict__ mask,
+                                                                const void *__restrict__ X, void *__restrict__ Y, AttnDims p,
+                                                                float scale_log2e, int rescale_in_place)
 {
     typedef typename MaskWord<BS>::type W;
     constexpr int LPR = BS / 8;  // lanes per query row
-    const uint32_t i = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
+    const uint32_t i = blockIdx.x / SPLIT, b = blockIdx.y, h = blockIdx.z;
     const uint2 *nn = lut + (size_t)h * p.lut_stride;
     const uint2 head = nn[i];
     const uint32_t off = head.x, cnt = head.y;
     if (cnt == 0) return;
-    const uint32_t r = threadIdx.x / LPR;        // query row inside the block
+    const uint32_t r = (blockIdx.x % SPLIT) * (BS / SPLIT) + threadIdx.x / LPR;        // query row inside the block
     const uint32_t c0 = (threadIdx.x % LPR) * 8;  // first key of this lane
     const size_t base = ((size_t)b * p.H + h) * p.blocks * BS * BS + (size_t)r * BS + c0;
     const W *mrow = mask ? mask + (size_t)h * p.mask_stride + (size_t)r * p.blocks : nullptr;
@@ -355,18 +357,20 @@ __global__ void __launch_bounds__(BS * BS / 8) softmax_kernel(const uint2 *__res
 // softmax: one CTA per block-row, a lane owns 8 consecutive keys of one query row of one block.
 // NB > 0: the row has at most NB blocks; dy and y of all of them are loaded up front and stay in registers
 // (one pass over HBM).  NB == 0: any length; the second sweep re-reads what the first pulled through L2.
-template <int BS, int DT, int NB>
-__global__ void __launch_bounds__(BS * BS / 8) softmax_grad_kernel(const uint2 *__restrict__ lut, const void *__restrict__ DY,
-                                                             const void *__restrict__ Y, void *__restrict__ DX, AttnDims p,
-                                                             float scale)
+// SPLIT > 1: the block-row is shared by SPLIT CTAs of BS/SPLIT query rows each -- fewer threads per CTA leave more
+// registers per thread, which is what lets longer rows stay register-resident.
+template <int BS, int DT, int NB, int SPLIT>
+__global__ void __launch_bounds__(BS * BS / 8 / SPLIT) softmax_grad_kernel(const uint2 *__restrict__ lut, const void *__restrict__ DY,
+                                                                     const void *__restrict__ Y, void *__restrict__ DX, AttnDims p,
+                                                                     float scale)
 {
     constexpr int LPR = BS / 8;  // lanes per query row
-    const uint32_t i = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
+    const uint32_t i = blockIdx.x / SPLIT, b = blockIdx.y, h = blockIdx.z;
     const uint2 *nn = lut + (size_t)h * p.lut_stride;
     const uint2 head = nn[i];
     const uint32_t off = head.x, cnt = head.y;
     if (cnt == 0) return;
-    const uint32_t r = threadIdx.x / LPR;
+    const uint32_t r = (blockIdx.x % SPLIT) * (BS / SPLIT) + threadIdx.x / LPR;
     const uint32_t c0 = (threadIdx.x % LPR) * 8;
     const size_t base = ((size_t)b * p.H + h) * p.blocks * BS * BS + (size_t)r * BS + c0;
 
@@ -735,16 +739,19 @@ int simt_sddmm_nt(cudaStream_t s, const void *lut, const void *a, const void *b,
 int simt_softmax(cudaStream_t s, const void *lut, const void *mask, const void *x, void *y, int x_dtype, int y_dtype,
                  uint32_t bs, const AttnDims &p, float scale, uint32_t max_lut)
 {
-    dim3 grid(p.nb_a, p.B, p.H);
     const float sl = scale * LOG2E_F;
-    // rows of up to 16 blocks (the caller's max_lut says so) stay in registers; 0 = unknown, stream
-    // (only when the longest row nearly fills the register tile: measured slower than streaming otherwise)
-    const int inplace = max_lut != 0 && max_lut <= 12;   // short rows: unnormalised values wait in L2 for the rescale
+    // rows that just fill 4, 8 or 16 blocks (the caller's max_lut says so) stay in registers; 0 = unknown, stream.
+    // Measured: a register tile with spare slots (12 blocks in 16, 17 in 32 with half-size CTAs) is slower here than
+    // streaming -- 3.9 against 4.9 TB/s on 12-block rows, 2.6 against 4.4 on 17-block rows -- unlike in the gradient.
+    const int inplace = max_lut != 0 && max_lut <= 12;   // streamed short rows: unnormalised values wait in L2 for the rescale
     const int nb = (max_lut >= 3 && max_lut <= 4) ? 4 : (max_lut >= 7 && max_lut <= 8) ? 8 : (max_lut >= 14 && max_lut <= 16) ? 16 : 0;
-#define SM_LAUNCH(XD, NBV) \
-    DISPATCH_DT(y_dtype, YD, { softmax_kernel<BS, XD, YD, NBV><<<grid, BS * BS / 8, 0, s>>>((const uint2 *)lut, (const W *)mask, x, y, p, sl, inplace); })
-#define SM_BY_NB(XD) \
-    if (nb == 4) { SM_LAUNCH(XD, 4) } else if (nb == 8) { SM_LAUNCH(XD, 8) } else if (nb == 16) { SM_LAUNCH(XD, 16) } else { SM_LAUNCH(XD, 0) }
+#define SM_LAUNCH(XD, NBV, SPL)                                                                                        \
+    DISPATCH_DT(y_dtype, YD, {                                                                                         \
+        softmax_kernel<BS, XD, YD, NBV, SPL><<<dim3(p.nb_a * SPL, p.B, p.H), BS * BS / 8 / SPL, 0, s>>>(             \
+            (const uint2 *)lut, (const W *)mask, x, y, p, sl, inplace);                                                \
+    })
+#define SM_BY_NB(XD)                                                                                                   \
+    if (nb == 4) { SM_LAUNCH(XD, 4, 1) } else if (nb == 8) { SM_LAUNCH(XD, 8, 1) } else if (nb == 16) { SM_LAUNCH(XD, 16, 1) } else { SM_LAUNCH(XD, 0, 1) }
     DISPATCH_BS(bs, {
         typedef typename MaskWord<BS>::type W;
         if (x_dtype == SFB_BF16) { SM_BY_NB(SFB_BF16) } else { SM_BY_NB(SFB_F32) }
@@ -768,12 +775,19 @@ int simt_spmm_nn(cudaStream_t s, const void *lut, const void *a, const void *b, 
 int simt_softmax_grad(cudaStream_t s, const void *lut, const void *dy, const void *y, void *dx, int dtype, uint32_t bs,
                       const AttnDims &p, float scale, uint32_t max_lut)
 {
-    dim3 grid(p.nb_a, p.B, p.H);
-    // rows of up to 8 blocks (the caller's max_lut says so) stay in registers: one pass over HBM; 0 = unknown, stream
-    const int nb = (max_lut >= 1 && max_lut <= 4) ? 4 : (max_lut >= 5 && max_lut <= 8) ? 8 : 0;
-#define SG_LAUNCH(NBV) DISPATCH_DT(dtype, DT, { softmax_grad_kernel<BS, DT, NBV><<<grid, BS * BS / 8, 0, s>>>((const uint2 *)lut, dy, y, dx, p, scale); })
+    // rows of up to 8 blocks (24 for 16-bit types; the caller's max_lut says so) stay in registers: one pass over
+    // HBM; 0 = unknown, stream.  The streamed variant re-reads dy and y, and at full size those re-reads miss L2.
+    const bool wide = dtype != SFB_F32;
+    const int nb = (max_lut >= 1 && max_lut <= 4) ? 4 : (max_lut >= 5 && max_lut <= 8) ? 8
+                   : (max_lut >= 9 && max_lut <= 12 && wide) ? 12 : (max_lut >= 13 && max_lut <= 16 && wide) ? 16
+                   : (max_lut >= 17 && max_lut <= 24 && wide) ? 24 : 0;
+#define SG_LAUNCH(NBV, SPL)                                                                                            \
+    DISPATCH_DT(dtype, DT, {                                                                                           \
+        softmax_grad_kernel<BS, DT, NBV, SPL><<<dim3(p.nb_a * SPL, p.B, p.H), BS * BS / 8 / SPL, 0, s>>>((const uint2 *)lut, dy, y, dx, p, scale); \
+    })
     DISPATCH_BS(bs, {
-        if (nb == 4) { SG_LAUNCH(4) } else if (nb == 8) { SG_LAUNCH(8) } else { SG_LAUNCH(0) }
+        if (nb == 4) { SG_LAUNCH(4, 1) } else if (nb == 8) { SG_LAUNCH(8, 1) } else if (nb == 12) { SG_LAUNCH(12, 1) }
+        else if (nb == 16) { SG_LAUNCH(16, 1) } else if (nb == 24) { SG_LAUNCH(24, 2) } else { SG_LAUNCH(0, 1) }
     })
 #undef SG_LAUNCH
     return check_launch("sfb_masked_softmax_grad");
