@@ -252,7 +252,19 @@ def run_bandwidth_kernel(args):
         return run_encoder_layer(args, sfb, cfg, pk, flush)
     if args.kernel == "linear":
         return run_linear(args, sfb, cfg, pk, flush)
-    if args.kernel == "softmax":
+    if args.kernel == "embedding":
+        tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[cfg["dtype"]]
+        vocab, hidden = 30522, H * d
+        table = (0.02 * torch.randn(vocab, hidden, device="cuda")).to(tdt)
+        pos = (0.02 * torch.randn(L, hidden, device="cuda")).to(tdt)
+        ids = torch.randint(0, vocab, (B, L), device="cuda", dtype=torch.int32)
+        fn = lambda: sfb.embedding(table, ids, pos)
+        nbytes = 2 * B * L * hidden * table.element_size() + B * L * 4
+        name, unit_name = "embedding_kernel", "one table row read + one output row written per token (+ ids); positions stay in L2"
+        lay = None
+    if args.kernel == "embedding":
+        pass
+    elif args.kernel == "softmax":
         lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
         x = torch.randn(B, H, lay.blocks, bs, bs, device="cuda").to(torch.bfloat16)
         fn = lambda: sfb.masked_softmax(x, lay, 0.125, torch.bfloat16)
@@ -332,18 +344,25 @@ def run_linear(args, sfb, cfg, pk, flush):
     B, H, L, d = cfg["B"], cfg["H"], cfg["L"], cfg["d"]
     tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.bfloat16}[cfg["dtype"]]
     hidden, ffn, m = H * d, 4 * H * d, B * L
-    shapes = [("qkv", hidden, 3 * hidden, 0), ("out", hidden, hidden, 0), ("ffn_up_gelu", hidden, ffn, 1), ("ffn_down", ffn, hidden, 0)]
+    shapes = [("qkv", hidden, 3 * hidden, 0), ("out", hidden, hidden, 0), ("ffn_up_gelu", hidden, ffn, 1), ("ffn_down", ffn, hidden, 0),
+              ("logits_tied", hidden, 30528, -1)]   # the vocabulary of 30522 padded to a multiple of 16; not part of the layer total
     res, total_ms, total_lib, flops = {}, 0.0, 0.0, 0.0
     sampler = ClockSampler(0)
     for name, k, n, act in shapes:
         x = torch.randn(m, k, device="cuda").to(tdt)
-        w = (0.02 * torch.randn(k, n, device="cuda")).to(tdt)
-        b = torch.randn(n, device="cuda")
-        ours = lambda: sfb.linear(x, w, b, act)
-        if act:
-            libf = lambda: torch.nn.functional.gelu(torch.addmm(b.to(tdt), x, w))
+        if act < 0:
+            wt = (0.02 * torch.randn(n, k, device="cuda")).to(tdt)
+            out = torch.empty(m, n, device="cuda", dtype=tdt)
+            ours = lambda: sfb.linear_nt(x, wt, None, 0, out=out)
+            libf = lambda: torch.matmul(x, wt.t(), out=out)
         else:
-            libf = lambda: torch.addmm(b.to(tdt), x, w)
+            w = (0.02 * torch.randn(k, n, device="cuda")).to(tdt)
+            b = torch.randn(n, device="cuda")
+            ours = lambda: sfb.linear(x, w, b, act)
+            if act:
+                libf = lambda: torch.nn.functional.gelu(torch.addmm(b.to(tdt), x, w))
+            else:
+                libf = lambda: torch.addmm(b.to(tdt), x, w)
         t = []
         for fn in (ours, libf):
             for _ in range(max(args.warmup, 3)):
@@ -360,9 +379,10 @@ def run_linear(args, sfb, cfg, pk, flush):
         f = 2.0 * m * n * k
         res[name] = {"m": m, "n": n, "k": k, "ms": round(t[0], 4), "tflops": round(f / (t[0] * 1e-3) / 1e12, 1),
                      "library_ms": round(t[1], 4), "library_tflops": round(f / (t[1] * 1e-3) / 1e12, 1)}
-        total_ms += t[0]
-        total_lib += t[1]
-        flops += f
+        if act >= 0:
+            total_ms += t[0]
+            total_lib += t[1]
+            flops += f
     clocks = sampler.stop()
     tf = flops / (total_ms * 1e-3) / 1e12
     print(json.dumps({
@@ -492,7 +512,7 @@ if __name__ == "__main__":
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="stride_bertbase", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer", "softmax_grad", "spmm_tn", "linear"],
+    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer", "softmax_grad", "spmm_tn", "linear", "embedding"],
                     help="fused = the headline fused attention; softmax / layernorm = the bandwidth kernels (N=1)")
     ap.add_argument("--projections", default="tensor", choices=["tensor", "library"],
                     help="--kernel encoder_layer: the layer's GEMMs on this library's tcgen05 kernel or on the GEMM library")

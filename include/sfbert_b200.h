@@ -206,6 +206,22 @@ int sfb_bias_gelu(sfb_stream_t stream, void *out, const void *x, const float *bi
 int sfb_linear(sfb_stream_t stream, void *out, const void *x, const void *w, const float *bias, uint32_t m,
                uint32_t n, uint32_t k, int dtype, int act);
 
+/* out[m, n] = act(x[m, k] . wt[n, k]^T + bias[n]): the same kernel with the weights stored row-major [n, k] -- the
+ * logits over the tied embedding table, cblas_sgemm(RowMajor, NoTrans, Trans, m, vocab, n, x, n, x_embed, n, logits, vocab)
+ * (transformer_inference_part.cpp:241); CPU twin matrixMulNTCPU, matmul.h:121-132.  n must be a multiple of 16 (pad the
+ * vocabulary), k of 8. */
+int sfb_linear_nt(sfb_stream_t stream, void *out, const void *x, const void *wt, const float *bias, uint32_t m,
+                  uint32_t n, uint32_t k, int dtype, int act);
+
+/* out[b, l, :] = table[ids[b, l], :] + pos[l, :]: the front of the encoder stack.  table [vocab, hidden], pos
+ * [seq_len, hidden] (may be NULL) and out [batch, seq_len, hidden] are of type dtype; ids are int32 in device memory.
+ * An id outside [0, vocab) gives a row of zeros and is counted in *bad_ids (device uint32, may be NULL) instead of
+ * being read out of bounds.  hidden must be a multiple of 8 (4 for fp32).
+ * Replaces embedding_lookup_gpu + tensor_add_matrix_gpu (cuda_kernels.h:210-221, 526-535); CPU twins embedding_lookup
+ * (embedding.h:5-12) and tensor_add_matrix (ewops.h:276-282); call site transformer_inference_part.cpp:201-209. */
+int sfb_embedding(sfb_stream_t stream, void *out, const void *table, const int32_t *ids, const void *pos,
+                  uint32_t batch, uint32_t seq_len, uint32_t hidden, uint32_t vocab, int dtype, uint32_t *bad_ids);
+
 #ifdef __cplusplus
 }
 #endif

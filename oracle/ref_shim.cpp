@@ -7,6 +7,7 @@
 #include "matmul.h"
 #include "ewops.h"
 #include "layernorm.h"
+#include "embedding.h"
 #ifdef _OPENMP
 #include <omp.h>
 #endif
@@ -73,6 +74,18 @@ void ref_matrixMulNNCPU(float *C, const float *A, const float *B, int mA, int nA
 {
     matrixMulNNCPU(C, A, B, mA, nA, nB);
 }
+
+/* matmul.h:121-132 */
+void ref_matrixMulNTCPU(float *C, const float *A, const float *B, int mA, int nA, int mB) { matrixMulNTCPU(C, A, B, mA, nA, mB); }
+
+/* embedding.h:5-12 */
+void ref_embedding_lookup(float *C, float *A, int *B, int batch, int seq_len, int heads, int per_head)
+{
+    embedding_lookup(C, A, B, batch, seq_len, heads, per_head);
+}
+
+/* ewops.h:276-282 */
+void ref_tensor_add_matrix(float *C, float *A, float *B, int d0, int d1, int d2) { tensor_add_matrix(C, A, B, d0, d1, d2); }
 
 int ref_num_threads(void)
 {

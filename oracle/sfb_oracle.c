@@ -491,6 +491,43 @@ void orc_linear(float *out, const float *x, const float *w, const float *bias, u
     }
 }
 
+/* out = act(x . wt^T + bias) with wt [n,k] row-major: matrixMulNTCPU (matmul.h:121-132: FLOAT accumulation over k
+ * in ascending order -- unlike the NN product, which accumulates in double), the logits product over the tied
+ * embedding table (transformer_inference_part.cpp:241). */
+void orc_linear_nt(float *out, const float *x, const float *wt, const float *bias, uint32_t m, uint32_t n, uint32_t k, int act)
+{
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < (long long)m; i++)
+        for (uint32_t j = 0; j < n; j++) {
+            float sum = 0.f;
+            for (uint32_t t = 0; t < k; t++) sum += x[(size_t)i * k + t] * wt[(size_t)j * k + t];
+            out[(size_t)i * n + j] = sum;
+        }
+    if (act == 1) orc_bias_gelu(out, out, bias, m, n);
+    else if (bias) {
+#pragma omp parallel for schedule(static)
+        for (long long i = 0; i < (long long)m; i++)
+            for (uint32_t j = 0; j < n; j++) out[(size_t)i * n + j] = out[(size_t)i * n + j] + bias[j];
+    }
+}
+
+/* out[b,l,:] = table[ids[b,l],:] + pos[l,:]: embedding_lookup (embedding.h:5-12) then tensor_add_matrix
+ * (ewops.h:276-282), the front of the encoder stack (transformer_inference_part.cpp:201-209, dropout off).
+ * pos may be NULL.  An id outside [0, vocab) gives a row of zeros (the reference would read out of bounds). */
+void orc_embedding(float *out, const float *table, const int32_t *ids, const float *pos, uint32_t batch, uint32_t seq_len,
+                   uint32_t hidden, uint32_t vocab)
+{
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < (long long)batch * seq_len; i++) {
+        const int32_t id = ids[i];
+        const uint32_t l = (uint32_t)(i % seq_len);
+        for (uint32_t j = 0; j < hidden; j++) {
+            const float e = (id >= 0 && (uint32_t)id < vocab) ? table[(size_t)id * hidden + j] : 0.f;
+            out[(size_t)i * hidden + j] = pos ? e + pos[(size_t)l * hidden + j] : e;
+        }
+    }
+}
+
 /* ------------------------------------------------------------------------------ */
 void orc_magicu64(uint32_t d, uint32_t *magic, uint32_t *shift)
 {

@@ -151,6 +151,15 @@ void orc_spmm_nn(const float *a, const float *b, const uint32_t *nn_lut,
  * (matrixMulNNCPU matmul.h:101-118, bias ewops.h:10-17, gelu ewops.h:32-43).  bias may be NULL. */
 void orc_linear(float *out, const float *x, const float *w, const float *bias, uint32_t m, uint32_t n, uint32_t k, int act);
 
+/* out = act(x . wt^T + bias), wt [n,k] row-major (matrixMulNTCPU, matmul.h:121-132; the tied-embedding logits,
+ * transformer_inference_part.cpp:241). */
+void orc_linear_nt(float *out, const float *x, const float *wt, const float *bias, uint32_t m, uint32_t n, uint32_t k, int act);
+
+/* out[b,l,:] = table[ids[b,l],:] + pos[l,:] (embedding.h:5-12, ewops.h:276-282); pos may be NULL; ids outside
+ * [0, vocab) give zero rows. */
+void orc_embedding(float *out, const float *table, const int32_t *ids, const float *pos, uint32_t batch, uint32_t seq_len,
+                   uint32_t hidden, uint32_t vocab);
+
 /* magic-number division constants (blocksparse.h:1016-1043) */
 void orc_magicu64(uint32_t d, uint32_t *magic, uint32_t *shift);
 

@@ -24,7 +24,7 @@ SYMBOLS = [
     "sfb_last_error", "sfb_version", "sfb_layout_generate", "sfb_lut_count", "sfb_lut_build", "sfb_mask_pack",
     "sfb_magicu64", "sfb_bst_sgemm_nt", "sfb_masked_softmax", "sfb_bst_sgemm_xn", "sfb_fused_sddmm_softmax",
     "sfb_fused_attention", "sfb_bias_residual_layernorm", "sfb_device_status", "sfb_bias_gelu", "sfb_lut_build_tn",
-    "sfb_masked_softmax_grad", "sfb_linear",
+    "sfb_masked_softmax_grad", "sfb_linear", "sfb_linear_nt", "sfb_embedding",
 ]
 
 if not os.path.exists(LIB_PATH):
@@ -47,6 +47,8 @@ lib.sfb_bst_sgemm_xn.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] *
 lib.sfb_lut_build_tn.argtypes = [_vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp]
 lib.sfb_masked_softmax_grad.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32] + [_u32] * 8 + [_f32]
 lib.sfb_linear.argtypes = [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _i32, _i32]
+lib.sfb_linear_nt.argtypes = [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _i32, _i32]
+lib.sfb_embedding.argtypes = [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _i32, _vp]
 lib.sfb_fused_sddmm_softmax.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 10 + [_f32]
 lib.sfb_fused_attention.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32] + [_u32] * 9 + [_f32, _u32]
 lib.sfb_bias_residual_layernorm.argtypes = [_vp] * 10 + [_u32, _u32, _i32]
@@ -218,6 +220,29 @@ def linear(x, w, bias=None, act=ACT_NONE, out=None):
     o = torch.empty(*x.shape[:-1], n, dtype=x.dtype, device=x.device) if out is None else out
     _check(lib.sfb_linear(_stream(), _p(o), _p(x), _p(w), _p(bias), m, n, k, dtype_tag(x), act))
     return o
+
+
+def linear_nt(x, wt, bias=None, act=ACT_NONE, out=None):
+    """out = act(x . wt^T + bias) with wt [n, k] row-major: the logits over the tied embedding table
+    (transformer_inference_part.cpp:241)."""
+    n, k = wt.shape
+    assert x.shape[-1] == k and x.dtype == wt.dtype and x.is_contiguous() and wt.is_contiguous()
+    m = x.numel() // k
+    o = torch.empty(*x.shape[:-1], n, dtype=x.dtype, device=x.device) if out is None else out
+    _check(lib.sfb_linear_nt(_stream(), _p(o), _p(x), _p(wt), _p(bias), m, n, k, dtype_tag(x), act))
+    return o
+
+
+def embedding(table, ids, pos=None):
+    """out[b, l, :] = table[ids[b, l], :] + pos[l, :] (embedding_lookup + tensor_add_matrix, embedding.h:5-12,
+    ewops.h:276-282).  Returns (out, number of ids that were outside the table)."""
+    B, L = ids.shape
+    vocab, hidden = table.shape
+    assert ids.dtype == torch.int32 and ids.is_contiguous() and table.is_contiguous()
+    out = torch.empty(B, L, hidden, dtype=table.dtype, device=table.device)
+    bad = torch.zeros(1, dtype=torch.int32, device=table.device)
+    _check(lib.sfb_embedding(_stream(), _p(out), _p(table), _p(ids), _p(pos), B, L, hidden, vocab, dtype_tag(table), _p(bad)))
+    return out, bad
 
 
 def bst_sgemm_tn(a, b, lay):

@@ -40,7 +40,9 @@ int tc_status_unfused(uint32_t *out);
 
 // tcgen05 dense projection (gemm_tc.cu)
 int tc_linear(cudaStream_t s, void *out, const void *x, const void *w, const float *bias, uint32_t m, uint32_t n, uint32_t k,
-              int dtype, int act);
+              int dtype, int act, bool w_transposed);
+int embedding_lookup(cudaStream_t s, void *out, const void *table, const int32_t *ids, const void *pos, uint32_t batch,
+                     uint32_t seq_len, uint32_t hidden, uint32_t vocab, int dtype, uint32_t *bad_ids);
 int tc_status_gemm(uint32_t *out);
 
 }  // namespace sfb

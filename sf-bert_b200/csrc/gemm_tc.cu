@@ -42,6 +42,7 @@ struct GParams {
     const float *bias;
     uint32_t M, N, K, tiles_m, tiles_n;
     int is_bf16, act;
+    int w_transposed;   // w is [n, k] row-major (out = x . w^T, the tied-embedding logits): its tile is a K-major B operand
 };
 
 __device__ __forceinline__ float gelu_ref(float t)
@@ -99,9 +100,14 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
 #pragma unroll
                     for (uint32_t mt = 0; mt < MT; mt++)
                         tma_load_2d(base + mt * kGABytes, &amap, &st->full[s], (int32_t)(kb * kGBK), m0 + (int32_t)(mt * kGBM));
+                    if (p.w_transposed) {
+                        // 256 rows of w, 64 of k: one box
+                        tma_load_2d(base + kBBase, &bmap, &st->full[s], (int32_t)(kb * kGBK), n0);
+                    } else {
 #pragma unroll
-                    for (uint32_t j = 0; j < 4; j++)
-                        tma_load_2d(base + kBBase + j * kTileBytes, &bmap, &st->full[s], n0 + (int32_t)(j * 64), (int32_t)(kb * kGBK));
+                        for (uint32_t j = 0; j < 4; j++)
+                            tma_load_2d(base + kBBase + j * kTileBytes, &bmap, &st->full[s], n0 + (int32_t)(j * 64), (int32_t)(kb * kGBK));
+                    }
                 }
                 if (!alive) break;
             }
@@ -109,7 +115,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
     } else if (warp == 1) {
         // ===== MMA issuer =====
         if (lane == 0) {
-            const uint32_t idesc = instr_desc(fmt, fmt, kGBM, kGBN, 1);
+            const uint32_t idesc = instr_desc(fmt, fmt, kGBM, kGBN, p.w_transposed ? 0 : 1);
+            const uint32_t b_step = p.w_transposed ? 2u : 128u;   // descriptor units of 16 bytes per 16 of K
             uint32_t g = 0, i = 0;
             for (uint32_t t = blockIdx.x; t < n_tiles; t += gridDim.x, i++) {
                 const uint32_t buf = i % kBufs;
@@ -121,13 +128,14 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
                     if (!mbar_wait(&st->full[s], (g / kGStages) & 1, abort_flag, 43)) { alive = false; break; }
                     tcgen05_fence_after();
                     const uint32_t base = smem_u32(tiles + s * kGStageBytes);
-                    const uint64_t b_desc = smem_desc_sw128(base + kBBase, kTileBytes);   // next 64 columns: one box further on
+                    // MN-major: the next 64 columns are one box further on; K-major: 256 rows of 128 bytes
+                    const uint64_t b_desc = p.w_transposed ? smem_desc_sw128(base + kBBase) : smem_desc_sw128(base + kBBase, kTileBytes);
 #pragma unroll
                     for (uint32_t mt = 0; mt < MT; mt++) {
                         const uint64_t a_desc = smem_desc_sw128(base + mt * kGABytes);
 #pragma unroll
                         for (uint32_t kk = 0; kk < 4; kk++)   // 16 of K per MMA: +32 bytes in A's swizzled rows, +16 rows (2048 bytes) in B
-                            umma_f16(tmem + (buf * MT + mt) * kGBN, a_desc + 2 * kk, b_desc + 128 * kk, idesc, (kb | kk) ? 1u : 0u);
+                            umma_f16(tmem + (buf * MT + mt) * kGBN, a_desc + 2 * kk, b_desc + b_step * kk, idesc, (kb | kk) ? 1u : 0u);
                     }
                     umma_commit(&st->empty[s]);
                 }
@@ -234,12 +242,13 @@ static int make_map_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64
 }  // namespace tc
 
 int tc_linear(cudaStream_t s, void *out, const void *x, const void *w, const float *bias, uint32_t m, uint32_t n, uint32_t k,
-              int dtype, int act)
+              int dtype, int act, bool w_transposed)
 {
     using namespace tc;
     const int is_bf16 = dtype == SFB_BF16;
     CUtensorMap am, bm;
-    if (make_map_2d(&am, x, m, k, is_bf16, kGBM) || make_map_2d(&bm, w, k, n, is_bf16, kGBK)) return 1;
+    if (make_map_2d(&am, x, m, k, is_bf16, kGBM)) return 1;
+    if (w_transposed ? make_map_2d(&bm, w, n, k, is_bf16, kGBN) : make_map_2d(&bm, w, k, n, is_bf16, kGBK)) return 1;
     static int sms = 0;
     if (!sms) {
         int dev = 0, v = 0;
@@ -254,7 +263,7 @@ int tc_linear(cudaStream_t s, void *out, const void *x, const void *w, const flo
     const uint32_t tiles_n = (n + kGBN - 1) / kGBN;
     int mt = (k >= 2048 && (uint64_t)((m + 255) / 256) * tiles_n >= 2ull * sms) ? 2 : 1;
     if (const char *force = getenv("SFB_LINEAR_MT")) mt = force[0] == '2' ? 2 : 1;
-    GParams prm = {out, bias, m, n, k, (m + mt * kGBM - 1) / (mt * kGBM), tiles_n, is_bf16, act};
+    GParams prm = {out, bias, m, n, k, (m + mt * kGBM - 1) / (mt * kGBM), tiles_n, is_bf16, act, w_transposed ? 1 : 0};
     const uint32_t tiles = prm.tiles_m * prm.tiles_n;
     const uint32_t grid = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
     if (mt == 2) linear_tc_kernel<2><<<grid, 320, GCfg<2>::smem, s>>>(am, bm, prm);

@@ -1,7 +1,7 @@
 // Fused bias + residual + LayerNorm: one pass over HBM (read x and resid, write out and,
 // optionally, the pre-norm sum), one warp per row with 16-byte accesses and the row held in
 // registers.  Replaces three launches of the reference (cuda_kernels.h:334-372,449-469).
-#include "common.cuh"
+#include "attn.cuh"
 
 namespace sfb {
 
@@ -207,6 +207,55 @@ __global__ void __launch_bounds__(256) bias_gelu_kernel(void *__restrict__ out, 
         }
         Vec8<DT>::store(out, i, v);
     }
+}
+
+// Embedding lookup + positional add: out[token, :] = table[ids[token], :] + pos[token % seq_len, :].  One 16-byte
+// access per thread and step; a warp covers 512 contiguous bytes of one row.  An id outside [0, vocab) gives a row of
+// zeros (plus pos) and is counted in *bad_ids -- no out-of-bounds read.
+template <int DT>
+__global__ void __launch_bounds__(256) embedding_kernel(void *__restrict__ out, const void *__restrict__ table,
+                                                       const int32_t *__restrict__ ids, const void *__restrict__ pos, size_t tokens,
+                                                       uint32_t seq_len, uint32_t hidden, uint32_t vocab, uint32_t *bad_ids)
+{
+    constexpr int N = Vec8<DT>::N;
+    const uint32_t per_row = hidden / N;                       // 16-byte pieces per row
+    const size_t total = tokens * per_row, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const size_t tok = i / per_row;
+        const uint32_t col = (uint32_t)(i % per_row) * N;
+        const int32_t id = __ldg(ids + tok);
+        const bool ok = id >= 0 && (uint32_t)id < vocab;
+        float v[N];
+        if (ok) {
+            Vec8<DT>::load(v, table, (size_t)id * hidden + col);
+        } else {
+#pragma unroll
+            for (int t = 0; t < N; t++) v[t] = 0.f;
+            if (col == 0 && bad_ids) atomicAdd(bad_ids, 1u);
+        }
+        if (pos) {
+            float q[N];
+            Vec8<DT>::load(q, pos, (size_t)(tok % seq_len) * hidden + col);
+#pragma unroll
+            for (int t = 0; t < N; t++) v[t] += q[t];
+        }
+        Vec8<DT>::store(out, tok * hidden + col, v);
+    }
+}
+
+int embedding_lookup(cudaStream_t s, void *out, const void *table, const int32_t *ids, const void *pos, uint32_t batch,
+                     uint32_t seq_len, uint32_t hidden, uint32_t vocab, int dtype, uint32_t *bad_ids)
+{
+    const size_t tokens = (size_t)batch * seq_len;
+    const int per = dtype == SFB_F32 ? 4 : 8;
+    if (hidden % per) return fail("sfb_embedding: hidden=%u must be a multiple of %d for this type", hidden, per);
+    if (bad_ids) cudaMemsetAsync(bad_ids, 0, sizeof(uint32_t), s);
+    size_t ctas = (tokens * (hidden / per) + 255) / 256;
+    if (ctas > 148 * 16) ctas = 148 * 16;
+    if (dtype == SFB_F32) embedding_kernel<SFB_F32><<<(unsigned)ctas, 256, 0, s>>>(out, table, ids, pos, tokens, seq_len, hidden, vocab, bad_ids);
+    else if (dtype == SFB_BF16) embedding_kernel<SFB_BF16><<<(unsigned)ctas, 256, 0, s>>>(out, table, ids, pos, tokens, seq_len, hidden, vocab, bad_ids);
+    else embedding_kernel<SFB_F16><<<(unsigned)ctas, 256, 0, s>>>(out, table, ids, pos, tokens, seq_len, hidden, vocab, bad_ids);
+    return check_launch("sfb_embedding");
 }
 
 }  // namespace sfb

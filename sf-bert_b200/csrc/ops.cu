@@ -126,10 +126,37 @@ extern "C" int sfb_fused_attention(sfb_stream_t stream, const void *nn_lut, cons
     return simt_fused_attention(as_stream(stream), nn_lut, q, k, v, o, mask, dtype, block_size, p, scale);
 }
 
+static int linear_common(const char *who, sfb_stream_t stream, void *out, const void *x, const void *w, const float *bias, uint32_t m,
+                         uint32_t n, uint32_t k, int dtype, int act, bool w_transposed);
+
 extern "C" int sfb_linear(sfb_stream_t stream, void *out, const void *x, const void *w, const float *bias, uint32_t m, uint32_t n,
                           uint32_t k, int dtype, int act)
 {
-    const char *who = "sfb_linear";
+    return linear_common("sfb_linear", stream, out, x, w, bias, m, n, k, dtype, act, false);
+}
+
+extern "C" int sfb_linear_nt(sfb_stream_t stream, void *out, const void *x, const void *wt, const float *bias, uint32_t m, uint32_t n,
+                             uint32_t k, int dtype, int act)
+{
+    return linear_common("sfb_linear_nt", stream, out, x, wt, bias, m, n, k, dtype, act, true);
+}
+
+extern "C" int sfb_embedding(sfb_stream_t stream, void *out, const void *table, const int32_t *ids, const void *pos, uint32_t batch,
+                             uint32_t seq_len, uint32_t hidden, uint32_t vocab, int dtype, uint32_t *bad_ids)
+{
+    const char *who = "sfb_embedding";
+    SFB_REQUIRE(out && table && ids, "%s: NULL pointer", who);
+    SFB_REQUIRE(valid_dtype(dtype), "%s: unknown dtype", who);
+    SFB_REQUIRE(hidden % 8 == 0, "%s: hidden=%u must be a multiple of 8", who, hidden);
+    SFB_REQUIRE(aligned16(out) && aligned16(table) && (!pos || aligned16(pos)), "%s: out, table and pos must be 16-byte aligned", who);
+    SFB_REQUIRE((uint64_t)batch * seq_len < (1ull << 31), "%s: too many tokens", who);
+    if (batch == 0 || seq_len == 0 || hidden == 0) { clear_error(); return 0; }
+    return embedding_lookup(as_stream(stream), out, table, ids, pos, batch, seq_len, hidden, vocab, dtype, bad_ids);
+}
+
+static int linear_common(const char *who, sfb_stream_t stream, void *out, const void *x, const void *w, const float *bias, uint32_t m,
+                         uint32_t n, uint32_t k, int dtype, int act, bool w_transposed)
+{
     SFB_REQUIRE(out && x && w, "%s: NULL pointer", who);
     SFB_REQUIRE(dtype == SFB_BF16 || dtype == SFB_F16, "%s: x, w and out must be bf16 or fp16 (fp32 products stay with the GEMM library)", who);
     SFB_REQUIRE(act == SFB_ACT_NONE || act == SFB_ACT_GELU, "%s: unknown activation %d", who, act);
@@ -138,7 +165,7 @@ extern "C" int sfb_linear(sfb_stream_t stream, void *out, const void *x, const v
     SFB_REQUIRE((uint64_t)m < (1ull << 31) && (uint64_t)n < (1ull << 31) && (uint64_t)k < (1ull << 31), "%s: dimension too large", who);
     if (m == 0 || n == 0) { clear_error(); return 0; }
     SFB_REQUIRE(k > 0, "%s: k is 0", who);
-    return tc_linear(as_stream(stream), out, x, w, bias, m, n, k, dtype, act);
+    return tc_linear(as_stream(stream), out, x, w, bias, m, n, k, dtype, act, w_transposed);
 }
 
 extern "C" int sfb_device_status(uint32_t *status)

@@ -211,6 +211,60 @@ def linear(x, w, bias=None, act=0):
     return out
 
 
+def linear_nt(x, wt, bias=None, act=0):
+    """out = act(x . wt^T + bias), x [m,k], wt [n,k]."""
+    x = np.ascontiguousarray(x, np.float32)
+    wt = np.ascontiguousarray(wt, np.float32)
+    m, k = x.shape
+    n = wt.shape[0]
+    out = np.zeros((m, n), np.float32)
+    b = None if bias is None else np.ascontiguousarray(bias, np.float32)
+    lib().orc_linear_nt(_ptr(out, _f32p), _ptr(x, _f32p), _ptr(wt, _f32p), None if b is None else _ptr(b, _f32p),
+                        C.c_uint32(m), C.c_uint32(n), C.c_uint32(k), C.c_int(act))
+    return out
+
+
+def embedding(table, ids, pos=None):
+    """table [vocab, hidden], ids int32 [B, L], pos [L, hidden] or None -> [B, L, hidden]."""
+    table = np.ascontiguousarray(table, np.float32)
+    ids = np.ascontiguousarray(ids, np.int32)
+    B, L = ids.shape
+    vocab, hidden = table.shape
+    out = np.zeros((B, L, hidden), np.float32)
+    p = None if pos is None else np.ascontiguousarray(pos, np.float32)
+    lib().orc_embedding(_ptr(out, _f32p), _ptr(table, _f32p), ids.ctypes.data_as(C.POINTER(C.c_int32)),
+                        None if p is None else _ptr(p, _f32p), C.c_uint32(B), C.c_uint32(L), C.c_uint32(hidden), C.c_uint32(vocab))
+    return out
+
+
+def ref_embedding(table, ids, pos):
+    """embedding_lookup + tensor_add_matrix of the reference (embedding.h:5-12, ewops.h:276-282)."""
+    R = ref()
+    assert R is not None
+    table = np.ascontiguousarray(table, np.float32)
+    ids = np.ascontiguousarray(ids, np.int32)
+    pos = np.ascontiguousarray(pos, np.float32)
+    B, L = ids.shape
+    hidden = table.shape[1]
+    looked = np.zeros((B, L, hidden), np.float32)
+    R.ref_embedding_lookup(_ptr(looked, _f32p), _ptr(table, _f32p), ids.ctypes.data_as(C.POINTER(C.c_int)), C.c_int(B), C.c_int(L),
+                           C.c_int(1), C.c_int(hidden))
+    out = np.zeros_like(looked)
+    R.ref_tensor_add_matrix(_ptr(out, _f32p), _ptr(looked, _f32p), _ptr(pos, _f32p), C.c_int(B), C.c_int(L), C.c_int(hidden))
+    return out
+
+
+def ref_matmul_nt(a, b):
+    """matrixMulNTCPU of the reference (matmul.h:121-132): a [m,k], b [n,k] -> a . b^T."""
+    R = ref()
+    assert R is not None
+    a = np.ascontiguousarray(a, np.float32)
+    b = np.ascontiguousarray(b, np.float32)
+    c = np.zeros((a.shape[0], b.shape[0]), np.float32)
+    R.ref_matrixMulNTCPU(_ptr(c, _f32p), _ptr(a, _f32p), _ptr(b, _f32p), C.c_int(a.shape[0]), C.c_int(a.shape[1]), C.c_int(b.shape[0]))
+    return c
+
+
 def ref_matmul_nn(a, b):
     """matrixMulNNCPU of the reference (matmul.h:101-118)."""
     R = ref()

@@ -1,4 +1,4 @@
-"""GPU parity of the tcgen05 dense projection (sfb_linear) against the CPU oracle.  Tolerance: 16-bit operands with
+"""GPU parity of the tcgen05 dense projection (sfb_linear, sfb_linear_nt) and of the embedding front end against the CPU oracle.  Tolerance: 16-bit operands with
 fp32 accumulation, 2e-2 relative to the largest reference value (the output itself is rounded to 16 bits)."""
 import numpy as np
 import pytest
@@ -59,3 +59,48 @@ def test_linear_rejects_what_it_cannot_do(sfb):
     xb, wb = x.to(torch.bfloat16), torch.zeros(64, 24, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(sfb.SfbError):
         sfb.linear(xb, wb)                                 # n not a multiple of 16
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("m,n,k,act", [(128, 256, 64, 0), (300, 1008, 768, 0), (257, 30528, 1024, 0), (64, 48, 40, 1)])
+def test_linear_nt_against_oracle(sfb, oracle, dtype, m, n, k, act):
+    """out = x . wt^T with wt [n, k] -- the logits over a (padded) tied embedding table."""
+    x, xn = _mk(oracle, (m, k), 410, dtype)
+    wt, wn = _mk(oracle, (n, k), 411, dtype, 0.05)
+    b = torch.from_numpy(oracle.fill_normal((n,), 412, 0.5)).cuda()
+    got = sfb.linear_nt(x, wt, b, act)
+    assert sfb.device_status() == 0
+    rows = np.arange(0, m, max(1, m // 40))
+    want = oracle.linear_nt(xn[rows], wn, b.cpu().numpy(), act)
+    assert got.shape == (m, n) and got.dtype == TD[dtype]
+    assert np.abs(got[rows].float().cpu().numpy() - want).max() <= 2e-2 * np.abs(want).max()
+    # the transposed-weight path and the plain one are the same product
+    same = sfb.linear(x, wt.t().contiguous(), b, act)
+    assert float((got.float() - same.float()).abs().max()) <= 2e-2 * float(same.float().abs().max())
+
+
+@pytest.mark.parametrize("dtype,hidden", [("f32", 768), ("bf16", 1024), ("f16", 40)])
+def test_embedding_bit_exact(sfb, oracle, dtype, hidden):
+    td = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[dtype]
+    vocab, B, L = 3000, 3, 257
+    table = torch.from_numpy(oracle.fill_normal((vocab, hidden), 420, 0.02)).cuda().to(td)
+    pos = torch.from_numpy(oracle.fill_normal((L, hidden), 421, 0.02)).cuda().to(td)
+    ids = torch.from_numpy((np.arange(B * L, dtype=np.int64) * 7919 % vocab).astype(np.int32).reshape(B, L)).cuda()
+    out, bad = sfb.embedding(table, ids, pos)
+    assert int(bad.item()) == 0
+    want = oracle.embedding(table.float().cpu().numpy(), ids.cpu().numpy(), pos.float().cpu().numpy())
+    if dtype == "f32":
+        assert np.array_equal(out.cpu().numpy(), want)
+    else:   # one rounding of the sum to 16 bits
+        assert np.array_equal(out.float().cpu().numpy(), torch.from_numpy(want).to(td).float().numpy())
+    plain, _ = sfb.embedding(table, ids)
+    assert torch.equal(plain, table[ids.long()])
+
+
+def test_embedding_ids_outside_the_table_are_counted_not_read(sfb):
+    table = torch.ones(10, 16, device="cuda", dtype=torch.bfloat16)
+    ids = torch.tensor([[0, 9, 10, -1, 5]], dtype=torch.int32, device="cuda")
+    out, bad = sfb.embedding(table, ids)
+    assert int(bad.item()) == 2
+    assert out[0, :, 0].float().cpu().tolist() == [1.0, 1.0, 0.0, 0.0, 1.0]
+

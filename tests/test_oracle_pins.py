@@ -262,3 +262,20 @@ def test_linear_matches_live_reference_when_built(oracle):
     assert np.array_equal(oracle.linear(x, w), plain)
     assert np.array_equal(oracle.linear(x, w, b, act=1), oracle.ref_bias_gelu(plain, b))
 
+
+def test_embedding_and_logits_match_live_reference_when_built(oracle):
+    """orc_embedding against embedding_lookup + tensor_add_matrix, orc_linear_nt against matrixMulNTCPU -- bit-exact."""
+    if oracle.ref() is None:
+        pytest.skip("oracle/_ref not built on this machine")
+    vocab, hidden, B, L = 97, 40, 3, 17
+    table = oracle.fill_normal((vocab, hidden), 61, 0.02)
+    pos = oracle.fill_normal((L, hidden), 62, 0.02)
+    ids = (np.arange(B * L, dtype=np.int64) * 37 % vocab).astype(np.int32).reshape(B, L)
+    assert np.array_equal(oracle.embedding(table, ids, pos), oracle.ref_embedding(table, ids, pos))
+    x = oracle.fill_normal((B * L, hidden), 63)
+    assert np.array_equal(oracle.linear_nt(x, table), oracle.ref_matmul_nt(x, table))
+    bad = ids.copy()
+    bad[0, 0], bad[1, 2] = -1, vocab
+    out = oracle.embedding(table, bad, None)
+    assert float(np.abs(out[0, 0]).max()) == 0.0 and float(np.abs(out[1, 2]).max()) == 0.0
+
