@@ -236,6 +236,139 @@ def run_ours(args):
 
 
 # ------------------------------------------------------------------------------------------------
+def run_encoder_stack(args):
+    """Sequences per second of the whole encoder forward at the workload's shape: embedding lookup + positions, then
+    `--layers` post-LN encoder layers (attention, projections, LayerNorm, GELU all from this library), one process per
+    GPU with its own slice of the batch (weights replicated, nothing exchanged inside the stack), and an all-gather
+    of the outputs afterwards, timed separately.  Weak scaling: the batch per GPU is the workload's batch divided by 8
+    (its 8-GPU split) when it is at least 8, else the whole batch."""
+    import importlib.util
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as ge
+    sfb = ge.load_package()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    spec = importlib.util.spec_from_file_location("sfb_encoder", os.path.join(ROOT, "sf-bert_b200", "encoder.py"))
+    enc = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(enc)
+    cfg = CONFIGS[args.config]
+    B, H, L, d, bs = cfg["B"], cfg["H"], cfg["L"], cfg["d"], cfg["bs"]
+    Bg = B // 8 if B >= 8 and B % 8 == 0 else B
+    tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[cfg["dtype"]]
+    hidden, ffn, vocab = H * d, 4 * H * d, 30522
+    proj = "tensor" if args.projections == "tensor" and tdt != torch.float32 else "library"
+    lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
+    layers = [enc.EncoderLayerWeights(hidden, ffn, tdt, seed=100 + i) for i in range(args.layers)]
+    g = torch.Generator(device="cuda").manual_seed(7)
+    table = (0.02 * torch.randn(vocab, hidden, device="cuda", generator=g)).to(tdt)
+    pos = (0.02 * torch.randn(L, hidden, device="cuda", generator=g)).to(tdt)
+    ids = torch.randint(0, vocab, (Bg, L), device="cuda", dtype=torch.int32, generator=torch.Generator(device="cuda").manual_seed(1234 + rank))
+    host_ids = ids.cpu().pin_memory()
+    dev_ids = torch.empty_like(ids)
+    host_out = torch.empty(Bg, L, hidden, dtype=tdt).pin_memory()
+
+    def forward(tok):
+        x, _ = sfb.embedding(table, tok, pos)
+        for w in layers:
+            x = enc.encoder_layer(sfb, x, w, lay, H, "post", proj)
+        return x
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        out = forward(ids)
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = forward(ids)
+    e1.record()
+    sync_all()
+    eager_ms = e0.elapsed_time(e1) / args.steps
+    # the forward is a few hundred short launches: captured once into a CUDA graph (on dev_ids, refreshed per step)
+    dev_ids.copy_(ids)
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        forward(dev_ids)
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.cuda.graph(graph):
+        graph_out = forward(dev_ids)
+    for _ in range(3):
+        graph.replay()
+    sync_all()
+    sampler = ClockSampler(local) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    sync_all()
+    ms = e0.elapsed_time(e1) / args.steps
+    out = graph_out
+    # end to end: token ids from pinned host memory in, the stack's output back to the host
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        dev_ids.copy_(host_ids, non_blocking=True)
+        graph.replay()
+        host_out.copy_(graph_out, non_blocking=True)
+    f1.record()
+    sync_all()
+    e2e_ms = f0.elapsed_time(f1) / args.steps
+    clocks = sampler.stop() if sampler else None
+    gather_ms = 0.0
+    if world > 1:
+        outs = torch.empty((world,) + tuple(out.shape), dtype=out.dtype, device="cuda")
+        for _ in range(3):
+            dist.all_gather_into_tensor(outs, out)
+        sync_all()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(5):
+            dist.all_gather_into_tensor(outs, out)
+        g1.record()
+        sync_all()
+        gather_ms = g0.elapsed_time(g1) / 5
+    status = sfb.device_status()
+    t = torch.tensor([ms, e2e_ms, gather_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms, gather_ms = (float(v) for v in t.cpu())
+    if rank == 0:
+        flops = args.layers * (2.0 * Bg * L * hidden * (4 * hidden + 2 * ffn) + attention_flops(dict(cfg, B=Bg), lay.blocks))
+        line = {
+            "metric": "encoder-stack sequences/s", "value": round(world * Bg / (ms * 1e-3), 2), "unit": "seq/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
+            "config": {"workload": args.config, "layers": args.layers, "B_per_gpu": Bg, "L": L, "hidden": hidden, "ffn": ffn, "heads": H,
+                       "vocab": vocab, "ln": "post", "layout": cfg["layout"][0],
+                       "projections": "sfb_linear (tcgen05)" if proj == "tensor" else "torch.matmul (cuBLAS)",
+                       "sharding": "batch, weights replicated, no collective inside the stack",
+                       "launch": "one CUDA graph replay per forward", "eager_ms_per_step": round(eager_ms, 4)},
+            "tflops_per_gpu": round(flops / (ms * 1e-3) / 1e12, 1),
+            "e2e": {"value": round(world * Bg / (e2e_ms * 1e-3), 2), "unit": "seq/s", "ms_per_step": round(e2e_ms, 4),
+                    "h2d_bytes_per_step": Bg * L * 4, "d2h_bytes_per_step": Bg * L * hidden * table.element_size()},
+            "gpu_launches": args.steps * (1 + args.layers * (9 if proj == "tensor" else 4)), "clocks": clocks, "device_status": status,
+        }
+        if world > 1:
+            line["gather_ms"] = round(gather_ms, 4)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------------
 def run_bandwidth_kernel(args):
     """Roofline lines of the two bandwidth-bound kernels of the path (N=1): `--kernel softmax` is the
     stand-alone masked softmax (bf16 scores in, bf16 probabilities out) on the workload's layout,
@@ -512,13 +645,16 @@ if __name__ == "__main__":
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="stride_bertbase", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer", "softmax_grad", "spmm_tn", "linear", "embedding"],
+    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer", "softmax_grad", "spmm_tn", "linear", "embedding", "encoder_stack"],
                     help="fused = the headline fused attention; softmax / layernorm = the bandwidth kernels (N=1)")
     ap.add_argument("--projections", default="tensor", choices=["tensor", "library"],
                     help="--kernel encoder_layer: the layer's GEMMs on this library's tcgen05 kernel or on the GEMM library")
+    ap.add_argument("--layers", type=int, default=24, help="--kernel encoder_stack: number of encoder layers")
     a = ap.parse_args()
     if a.impl == "reference":
         run_reference(a)
+    elif a.kernel == "encoder_stack":
+        run_encoder_stack(a)
     elif a.kernel != "fused":
         run_bandwidth_kernel(a)
     else:
