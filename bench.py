@@ -581,6 +581,11 @@ def cpu_reference_sample(cfg, budget_s, steps):
     import oracle_lib as O
     R = O.ref()
     kind = "reference"
+    # all the host threads this process may use: launchers such as torchrun hand their children OMP_NUM_THREADS=1
+    host = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    if R is not None:
+        R.ref_set_num_threads(host)
+    O.lib().orc_set_num_threads(host)
     threads = R.ref_num_threads() if R is not None else O.lib().orc_num_threads()
     if R is None:
         kind = "port"

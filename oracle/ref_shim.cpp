@@ -87,6 +87,13 @@ void ref_embedding_lookup(float *C, float *A, int *B, int batch, int seq_len, in
 /* ewops.h:276-282 */
 void ref_tensor_add_matrix(float *C, float *A, float *B, int d0, int d1, int d2) { tensor_add_matrix(C, A, B, d0, d1, d2); }
 
+void ref_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#endif
+}
+
 int ref_num_threads(void)
 {
 #ifdef _OPENMP

@@ -12,6 +12,11 @@
 #include <omp.h>
 #endif
 
+void orc_set_num_threads(int n)
+{
+    if (n > 0) omp_set_num_threads(n);
+}
+
 int orc_num_threads(void)
 {
 #ifdef _OPENMP

@@ -167,6 +167,8 @@ void orc_magicu64(uint32_t d, uint32_t *magic, uint32_t *shift);
 void orc_fill_normal(float *dst, size_t n, uint64_t seed, float stddev);
 
 int orc_num_threads(void);
+/* overrides OMP_NUM_THREADS (launchers such as torchrun set it to 1 for their children) */
+void orc_set_num_threads(int n);
 
 #ifdef __cplusplus
 }
