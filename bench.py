@@ -385,7 +385,16 @@ def run_bandwidth_kernel(args):
         return run_encoder_layer(args, sfb, cfg, pk, flush)
     if args.kernel == "linear":
         return run_linear(args, sfb, cfg, pk, flush)
-    if args.kernel == "embedding":
+    if args.kernel == "csr_attention":
+        tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[cfg["dtype"]]
+        lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), 1, L // bs, bs, **cfg["layout"][1])
+        rowptr, colidx = sfb.csr_from_layout(lay)
+        q, k, v = (torch.randn(B, L, H, d, device="cuda").to(tdt) for _ in range(3))
+        fn = lambda: sfb.csr_attention(q, k, v, rowptr, colidx, 0.125)
+        # what the format makes every query row gather: its keys' K and V rows (through L2), plus Q in and O out
+        nbytes = int(colidx.numel()) * B * H * 2 * d * q.element_size() + 2 * q.numel() * q.element_size()
+        name, unit_name = "csr_attention_kernel", "K and V rows gathered per query row (L2 traffic, not HBM) + Q read + O written"
+    elif args.kernel == "embedding":
         tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[cfg["dtype"]]
         vocab, hidden = 30522, H * d
         table = (0.02 * torch.randn(vocab, hidden, device="cuda")).to(tdt)
@@ -395,7 +404,7 @@ def run_bandwidth_kernel(args):
         nbytes = 2 * B * L * hidden * table.element_size() + B * L * 4
         name, unit_name = "embedding_kernel", "one table row read + one output row written per token (+ ids); positions stay in L2"
         lay = None
-    if args.kernel == "embedding":
+    if args.kernel in ("embedding", "csr_attention"):
         pass
     elif args.kernel == "softmax":
         lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
@@ -461,7 +470,8 @@ def run_bandwidth_kernel(args):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5), "higher_is_better": True,
         "dtype": "bf16" if args.kernel in ("softmax", "softmax_grad", "spmm_tn") else cfg["dtype"], "data": "synthetic",
         "tflops_on_kept_blocks": (round(2.0 * bs * bs * d * lay.blocks * B * H / (ms * 1e-3) / 1e12, 1)
-                                  if args.kernel in ("sddmm", "spmm", "fused_p", "spmm_tn") else None),
+                                  if args.kernel in ("sddmm", "spmm", "fused_p", "spmm_tn") else
+                                  round(4.0 * bs * bs * d * lay.blocks * B * H / (ms * 1e-3) / 1e12, 2) if args.kernel == "csr_attention" else None),
         "config": {"workload": args.config, "kernel": name, "bytes": unit_name, "l2": "flushed between timed steps"},
         "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm"], "unit": "GB/s",
                      "frac": round(gbs / pk["hbm"], 4), "traffic": None, "peak_source": pk["source"] + " copy bandwidth",
@@ -650,7 +660,7 @@ if __name__ == "__main__":
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="stride_bertbase", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer", "softmax_grad", "spmm_tn", "linear", "embedding", "encoder_stack"],
+    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer", "softmax_grad", "spmm_tn", "linear", "embedding", "encoder_stack", "csr_attention"],
                     help="fused = the headline fused attention; softmax / layernorm = the bandwidth kernels (N=1)")
     ap.add_argument("--projections", default="tensor", choices=["tensor", "library"],
                     help="--kernel encoder_layer: the layer's GEMMs on this library's tcgen05 kernel or on the GEMM library")

@@ -222,6 +222,22 @@ int sfb_linear_nt(sfb_stream_t stream, void *out, const void *x, const void *wt,
 int sfb_embedding(sfb_stream_t stream, void *out, const void *table, const int32_t *ids, const void *pos,
                   uint32_t batch, uint32_t seq_len, uint32_t hidden, uint32_t vocab, int dtype, uint32_t *bad_ids);
 
+/* ---- element-sparse (CSR) attention: the alternative format the reference prototypes ------------------ */
+
+/* The CSR pattern of a block layout (ONE head, uint8 [nb][nb]): every element of every kept block, columns ascending.
+ * rowptr int32 [nb*block_size + 1], colidx int32 [blocks*block_size^2], both in device memory.  The host-side
+ * generators it stands beside: generate_csr_full_mask / generate_csr_fixed_mask (ewops.h:430-443, 616-659). */
+int sfb_csr_from_layout(sfb_stream_t stream, const uint8_t *layout, uint32_t nb, uint32_t block_size, int32_t *rowptr,
+                        int32_t *colidx);
+
+/* O[b,i,h,:] = sum over the columns j of row i of softmax_j(scale * q_i . k_j) v_j, one CSR pattern (rowptr [seq_len+1],
+ * colidx [nnz]) for every (batch, head); q, k, v, o are [B, L, H, d] of type dtype, d = 32, 64 or 128.  Rows without
+ * entries give zeros; a column outside [0, seq_len) is skipped and counted in *bad_columns (device uint32, may be NULL).
+ * Replaces csr_sddmm + csr_softmax + csr_spmm and their one-kernel form fused_attention (cuda_kernels.h:976-1075). */
+int sfb_csr_attention(sfb_stream_t stream, const int32_t *rowptr, const int32_t *colidx, const void *q, const void *k,
+                      const void *v, void *o, int dtype, uint32_t batch_dim, uint32_t seq_len, uint32_t head_dim,
+                      uint32_t state_dim, float scale, uint32_t *bad_columns);
+
 #ifdef __cplusplus
 }
 #endif

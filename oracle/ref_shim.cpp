@@ -87,6 +87,12 @@ void ref_embedding_lookup(float *C, float *A, int *B, int batch, int seq_len, in
 /* ewops.h:276-282 */
 void ref_tensor_add_matrix(float *C, float *A, float *B, int d0, int d1, int d2) { tensor_add_matrix(C, A, B, d0, d1, d2); }
 
+/* ewops.h:430-443 */
+void ref_generate_csr_full_mask(int *rowptr, int *colidx, int batch, int heads, int seq_len)
+{
+    generate_csr_full_mask(rowptr, colidx, batch, heads, seq_len);
+}
+
 void ref_set_num_threads(int n)
 {
 #ifdef _OPENMP

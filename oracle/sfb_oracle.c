@@ -534,6 +534,81 @@ void orc_embedding(float *out, const float *table, const int32_t *ids, const flo
 }
 
 /* ------------------------------------------------------------------------------ */
+/* element-sparse (CSR) attention: the alternative format the reference prototypes    */
+
+/* one (batch, head) worth of generate_csr_full_mask (ewops.h:430-443): row i keeps the columns j <= i.
+ * rowptr [L+1], colidx [L(L+1)/2]. */
+void orc_csr_full_mask(int32_t *rowptr, int32_t *colidx, uint32_t L)
+{
+    uint32_t nnz = 0;
+    rowptr[0] = 0;
+    for (uint32_t i = 0; i < L; i++) {
+        for (uint32_t j = 0; j <= i; j++) colidx[nnz++] = (int32_t)j;
+        rowptr[i + 1] = (int32_t)nnz;
+    }
+}
+
+/* the element pattern of a block layout (one head, uint8 [nb][nb]): every element of every kept block, columns
+ * ascending.  rowptr [nb*bs+1], colidx [blocks*bs*bs].  Returns the number of nonzeros. */
+uint32_t orc_csr_from_layout(const uint8_t *layout, uint32_t nb, uint32_t bs, int32_t *rowptr, int32_t *colidx)
+{
+    uint32_t nnz = 0;
+    rowptr[0] = 0;
+    for (uint32_t i = 0; i < nb * bs; i++) {
+        const uint32_t bi = i / bs;
+        for (uint32_t bj = 0; bj < nb; bj++)
+            if (layout[(size_t)bi * nb + bj])
+                for (uint32_t c = 0; c < bs; c++) colidx[nnz++] = (int32_t)(bj * bs + c);
+        rowptr[i + 1] = (int32_t)nnz;
+    }
+    return nnz;
+}
+
+/* O[b,i,h,:] = sum over the columns j of row i of softmax_j(q_i . k_j) v_j with one CSR pattern for every (batch,
+ * head).  The arithmetic is the dense CPU path's (matmul.h:53-78 scores with float accumulation over d, ewops.h:64-98
+ * max of the unscaled kept scores, exp((x-max)*scale), divide by sum+1e-6, matmul.h:6-20 P.V over the kept keys in
+ * ascending order); the reference's GPU prototype of this format (csr_sddmm / csr_softmax / csr_spmm and
+ * fused_attention, cuda_kernels.h:976-1075) computes the same thing one thread per row, with a max that starts at
+ * 1e-20 instead of -1e6.  q, k, v, o are [B,L,H,d]; rows without entries give zeros. */
+void orc_csr_attention(const float *q, const float *k, const float *v, const int32_t *rowptr, const int32_t *colidx,
+                       uint32_t B, uint32_t H, uint32_t L, uint32_t d, float scale, float *o)
+{
+#pragma omp parallel for schedule(dynamic, 1) collapse(2)
+    for (uint32_t b = 0; b < B; b++)
+        for (uint32_t h = 0; h < H; h++) {
+            float *s = (float *)malloc(sizeof(float) * (L ? L : 1));
+            for (uint32_t i = 0; i < L; i++) {
+                const int32_t lo = rowptr[i], hi = rowptr[i + 1];
+                const float *qi = q + (((size_t)b * L + i) * H + h) * d;
+                float *oi = o + (((size_t)b * L + i) * H + h) * d;
+                for (uint32_t x = 0; x < d; x++) oi[x] = 0.f;
+                if (hi <= lo || !s) continue;
+                float mx = -1000000.0f;
+                for (int32_t e = lo; e < hi; e++) {
+                    const float *kj = k + (((size_t)b * L + (uint32_t)colidx[e]) * H + h) * d;
+                    float sum = 0.f;
+                    for (uint32_t x = 0; x < d; x++) sum += qi[x] * kj[x];
+                    s[e - lo] = sum;
+                    if (sum > mx) mx = sum;
+                }
+                float tot = 0.f;
+                for (int32_t e = lo; e < hi; e++) {
+                    s[e - lo] = (float)exp((s[e - lo] - mx) * scale);
+                    tot += s[e - lo];
+                }
+                for (int32_t e = lo; e < hi; e++) s[e - lo] /= (tot + 1e-6f);
+                for (uint32_t x = 0; x < d; x++) {
+                    float acc = 0.f;
+                    for (int32_t e = lo; e < hi; e++)
+                        acc += s[e - lo] * v[(((size_t)b * L + (uint32_t)colidx[e]) * H + h) * d + x];
+                    oi[x] = acc;
+                }
+            }
+            free(s);
+        }
+}
+
+/* ------------------------------------------------------------------------------ */
 void orc_magicu64(uint32_t d, uint32_t *magic, uint32_t *shift)
 {
     /* blocksparse.h:1016-1043: smallest p with 2^p > nc*(d-1-(2^p-1)%d) */

@@ -160,6 +160,13 @@ void orc_linear_nt(float *out, const float *x, const float *wt, const float *bia
 void orc_embedding(float *out, const float *table, const int32_t *ids, const float *pos, uint32_t batch, uint32_t seq_len,
                    uint32_t hidden, uint32_t vocab);
 
+/* ---- element-sparse (CSR) attention, the alternative format the reference prototypes (cuda_kernels.h:976-1075,
+ *      mask generators ewops.h:430-459) ---- */
+void orc_csr_full_mask(int32_t *rowptr, int32_t *colidx, uint32_t L);
+uint32_t orc_csr_from_layout(const uint8_t *layout, uint32_t nb, uint32_t bs, int32_t *rowptr, int32_t *colidx);
+void orc_csr_attention(const float *q, const float *k, const float *v, const int32_t *rowptr, const int32_t *colidx,
+                       uint32_t B, uint32_t H, uint32_t L, uint32_t d, float scale, float *o);
+
 /* magic-number division constants (blocksparse.h:1016-1043) */
 void orc_magicu64(uint32_t d, uint32_t *magic, uint32_t *shift);
 

@@ -24,7 +24,8 @@ SYMBOLS = [
     "sfb_last_error", "sfb_version", "sfb_layout_generate", "sfb_lut_count", "sfb_lut_build", "sfb_mask_pack",
     "sfb_magicu64", "sfb_bst_sgemm_nt", "sfb_masked_softmax", "sfb_bst_sgemm_xn", "sfb_fused_sddmm_softmax",
     "sfb_fused_attention", "sfb_bias_residual_layernorm", "sfb_device_status", "sfb_bias_gelu", "sfb_lut_build_tn",
-    "sfb_masked_softmax_grad", "sfb_linear", "sfb_linear_nt", "sfb_embedding",
+    "sfb_masked_softmax_grad", "sfb_linear", "sfb_linear_nt", "sfb_embedding", "sfb_csr_from_layout",
+    "sfb_csr_attention",
 ]
 
 if not os.path.exists(LIB_PATH):
@@ -49,6 +50,8 @@ lib.sfb_masked_softmax_grad.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32] + [_u32] 
 lib.sfb_linear.argtypes = [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _i32, _i32]
 lib.sfb_linear_nt.argtypes = [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _i32, _i32]
 lib.sfb_embedding.argtypes = [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _i32, _vp]
+lib.sfb_csr_from_layout.argtypes = [_vp, _vp, _u32, _u32, _vp, _vp]
+lib.sfb_csr_attention.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _u32, _u32, _u32, _u32, _f32, _vp]
 lib.sfb_fused_sddmm_softmax.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 10 + [_f32]
 lib.sfb_fused_attention.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32] + [_u32] * 9 + [_f32, _u32]
 lib.sfb_bias_residual_layernorm.argtypes = [_vp] * 10 + [_u32, _u32, _i32]
@@ -243,6 +246,27 @@ def embedding(table, ids, pos=None):
     bad = torch.zeros(1, dtype=torch.int32, device=table.device)
     _check(lib.sfb_embedding(_stream(), _p(out), _p(table), _p(ids), _p(pos), B, L, hidden, vocab, dtype_tag(table), _p(bad)))
     return out, bad
+
+
+def csr_from_layout(lay, head=0):
+    """(rowptr, colidx): the element pattern of one head of a BlockLayout as CSR (every element of every kept block)."""
+    bs, nb = lay.block_size, lay.nb
+    dev = lay.layout.device
+    rowptr = torch.empty(nb * bs + 1, dtype=torch.int32, device=dev)
+    colidx = torch.empty(lay.blocks * bs * bs, dtype=torch.int32, device=dev)
+    _check(lib.sfb_csr_from_layout(_stream(), _p(lay.layout[head]), nb, bs, _p(rowptr), _p(colidx)))
+    return rowptr, colidx
+
+
+def csr_attention(q, k, v, rowptr, colidx, scale):
+    """Element-sparse attention over one CSR pattern shared by every (batch, head) (the reference's csr_* prototype,
+    cuda_kernels.h:976-1075).  Returns (o, number of column indices that were outside the sequence)."""
+    B, L, H, d = q.shape
+    assert rowptr.dtype == torch.int32 and colidx.dtype == torch.int32 and rowptr.numel() == L + 1
+    o = torch.empty_like(q)
+    bad = torch.zeros(1, dtype=torch.int32, device=q.device)
+    _check(lib.sfb_csr_attention(_stream(), _p(rowptr), _p(colidx), _p(q), _p(k), _p(v), _p(o), dtype_tag(q), B, L, H, d, scale, _p(bad)))
+    return o, bad
 
 
 def bst_sgemm_tn(a, b, lay):

@@ -265,6 +265,49 @@ def ref_matmul_nt(a, b):
     return c
 
 
+_i32p = C.POINTER(C.c_int32)
+
+
+def csr_full_mask(L):
+    rowptr = np.zeros(L + 1, np.int32)
+    colidx = np.zeros(L * (L + 1) // 2, np.int32)
+    lib().orc_csr_full_mask(rowptr.ctypes.data_as(_i32p), colidx.ctypes.data_as(_i32p), C.c_uint32(L))
+    return rowptr, colidx
+
+
+def csr_from_layout(lay2d, bs):
+    lay2d = np.ascontiguousarray(lay2d, np.uint8)
+    nb = lay2d.shape[0]
+    rowptr = np.zeros(nb * bs + 1, np.int32)
+    colidx = np.zeros(int(lay2d.sum()) * bs * bs, np.int32)
+    fn = lib().orc_csr_from_layout
+    fn.restype = C.c_uint32
+    nnz = fn(_ptr(lay2d, _u8p), C.c_uint32(nb), C.c_uint32(bs), rowptr.ctypes.data_as(_i32p), colidx.ctypes.data_as(_i32p))
+    assert nnz == colidx.size
+    return rowptr, colidx
+
+
+def csr_attention(q, k, v, rowptr, colidx, scale):
+    q, k, v = (np.ascontiguousarray(t, np.float32) for t in (q, k, v))
+    B, L, H, d = q.shape
+    o = np.zeros_like(q)
+    lib().orc_csr_attention(_ptr(q, _f32p), _ptr(k, _f32p), _ptr(v, _f32p), rowptr.ctypes.data_as(_i32p), colidx.ctypes.data_as(_i32p),
+                            C.c_uint32(B), C.c_uint32(H), C.c_uint32(L), C.c_uint32(d), C.c_float(scale), _ptr(o, _f32p))
+    return o
+
+
+def ref_csr_full_mask(batch, heads, L):
+    """generate_csr_full_mask of the reference (ewops.h:430-443) for batch*heads stacked patterns."""
+    R = ref()
+    assert R is not None
+    rows = batch * heads * L
+    rowptr = np.zeros(rows + 1, np.int32)
+    colidx = np.zeros(batch * heads * L * (L + 1) // 2, np.int32)
+    R.ref_generate_csr_full_mask(rowptr.ctypes.data_as(C.POINTER(C.c_int)), colidx.ctypes.data_as(C.POINTER(C.c_int)), C.c_int(batch),
+                                 C.c_int(heads), C.c_int(L))
+    return rowptr, colidx
+
+
 def ref_matmul_nn(a, b):
     """matrixMulNNCPU of the reference (matmul.h:101-118)."""
     R = ref()

@@ -279,3 +279,32 @@ def test_embedding_and_logits_match_live_reference_when_built(oracle):
     out = oracle.embedding(table, bad, None)
     assert float(np.abs(out[0, 0]).max()) == 0.0 and float(np.abs(out[1, 2]).max()) == 0.0
 
+
+def test_csr_path_matches_live_reference_when_built(oracle):
+    """The CSR causal pattern against generate_csr_full_mask, and CSR attention on it against the reference's dense
+    causal CPU attention (the one pattern both can express) -- bit-exact."""
+    if oracle.ref() is None:
+        pytest.skip("oracle/_ref not built on this machine")
+    L = 48
+    rowptr, colidx = oracle.csr_full_mask(L)
+    rr, rc = oracle.ref_csr_full_mask(2, 3, L)
+    nnz = L * (L + 1) // 2
+    for g in range(6):      # the reference stacks one copy per (batch, head), row pointers running on
+        assert np.array_equal(rr[g * L:(g + 1) * L + 1] - g * nnz, rowptr)
+        assert np.array_equal(rc[g * nnz:(g + 1) * nnz], colidx)
+    q, k, v = (oracle.fill_normal((2, L, 3, 16), s) for s in (71, 72, 73))
+    o = oracle.csr_attention(q, k, v, rowptr, colidx, 0.25)
+    _, _, want = oracle.ref_dense_causal_attention(q, k, v, 0.25)
+    assert np.array_equal(o, want)
+
+
+def test_csr_attention_equals_block_attention_on_a_block_pattern(oracle):
+    bs, nb = 32, 6
+    lay = oracle.layout("stride", 1, nb, band=2, every=3)
+    luts = oracle.lut_build(lay)
+    rowptr, colidx = oracle.csr_from_layout(lay[0], bs)
+    q, k, v = (oracle.fill_normal((1, nb * bs, 2, 32), s) for s in (81, 82, 83))
+    a = oracle.attention(q, k, v, luts, bs, 0.2, want=("o",))["o"]
+    b = oracle.csr_attention(q, k, v, rowptr, colidx, 0.2)
+    assert np.array_equal(a, b)
+
