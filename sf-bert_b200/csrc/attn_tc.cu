@@ -50,7 +50,7 @@ struct Params {
 template <bool HAS_MASK, bool BF16>
 __global__ void __launch_bounds__(192, 2)
 fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
-                          const __grid_constant__ CUtensorMap vmap, const Params p)
+                          const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap omap, const Params p)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -288,37 +288,54 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
         }
         tmem_wait_ld();
 
-        // ---- epilogue: O / row sum -> global ----
+        // ---- epilogue: O / row sum -> global.  The four softmax warps agree first on whether all of them got here
+        // in good order (they meet at a named barrier below, so they take that road together or not at all) ----
         if (T > 0 && alive) alive = mbar_wait_warp(&st->o_final, 0, abort_flag, 10);
-        if (alive && row_valid) {
+        uint32_t all_ok;
+        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.red.and.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(all_ok) : "r"((uint32_t)alive) : "memory");
+        if (all_ok) {
             tcgen05_fence_after();
+            uint32_t oc[64];
             float inv = 0.f;
             if (T > 0) {
                 uint32_t lc[16];
                 TMEM_LD_16((lc), tmem_o + lane_field + 64);
+                TMEM_LD_32((oc), tmem_o + lane_field);
+                TMEM_LD_32((oc + 32), tmem_o + lane_field + 32);
                 tmem_wait_ld();
                 const float lsum = __uint_as_float(lc[0]);
                 inv = lsum > 0.f ? 1.f / lsum : 0.f;
             }
-            uint16_t *dst = (uint16_t *)p.O + ((size_t)b * L + (size_t)pair * 128 + r) * ((size_t)p.H * 64) + (size_t)h * 64;
+            uint32_t w[32];
 #pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 16) {
-                uint32_t oc[16], w[8];
-                if (T > 0) {
-                    TMEM_LD_16((oc), tmem_o + lane_field + c0);
-                    tmem_wait_ld();
-                }
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const float a0 = T > 0 ? __uint_as_float(oc[2 * j]) * inv : 0.f;
-                    const float a1 = T > 0 ? __uint_as_float(oc[2 * j + 1]) * inv : 0.f;
-                    w[j] = pack2(a0, a1, BF16);
-                }
-                *(uint4 *)(dst + c0) = make_uint4(w[0], w[1], w[2], w[3]);
-                *(uint4 *)(dst + c0 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+            for (int j = 0; j < 32; j++) {
+                const float a0 = T > 0 ? __uint_as_float(oc[2 * j]) * inv : 0.f;
+                const float a1 = T > 0 ? __uint_as_float(oc[2 * j + 1]) * inv : 0.f;
+                w[j] = pack2(a0, a1, BF16);
             }
-        } else if (!row_valid) {
-            // lanes of the absent lower block-row still take part in the aligned TMEM loads above: nothing to do
+            if (has_row1) {
+                // the 128 x 64 tile leaves through the Q tile's shared memory (every MMA that read Q has completed) and one
+                // TMA store: whole 128-byte lines instead of 128 scattered rows.  16-byte chunk c of row r sits at chunk
+                // c ^ (r % 8), the tensor map's 128-byte swizzle.
+                uint8_t *orow = q_tile + r * 128;
+#pragma unroll
+                for (int ch = 0; ch < 8; ch++)
+                    *(uint4 *)(orow + ((ch ^ (r & 7)) << 4)) = make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
+                fence_proxy_async();
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                                 ::"l"((uint64_t)&omap), "r"(smem_u32(q_tile)), "r"(xq), "r"((int32_t)(b * L + pair * 128)) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory must outlive the store's reads
+                }
+            } else if (row_valid) {
+                // an odd number of block-rows: the last CTA owns 64 rows only and writes them directly
+                uint16_t *dst = (uint16_t *)p.O + ((size_t)b * L + (size_t)pair * 128 + r) * ((size_t)p.H * 64) + (size_t)h * 64;
+#pragma unroll
+                for (int ch = 0; ch < 8; ch++) *(uint4 *)(dst + 8 * ch) = make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
+            }
         }
     }
 
@@ -360,9 +377,9 @@ int tc_fused_attention(cudaStream_t s, const void *nn_lut, const void *q, const 
     SFB_REQUIRE((al & 15) == 0, "sfb_fused_attention: q, k, v, o must be 16-byte aligned");
     const int is_bf16 = dtype == SFB_BF16;
     const uint64_t rows = (uint64_t)p.B * p.nb_a * 64;
-    CUtensorMap qm, km, vm;
+    CUtensorMap qm, km, vm, om;
     if (make_map(&qm, q, rows, p.H, is_bf16, 128) || make_map(&km, k, rows, p.H, is_bf16, 64) ||
-        make_map(&vm, v, rows, p.H, is_bf16, 64))
+        make_map(&vm, v, rows, p.H, is_bf16, 64) || make_map(&om, o, rows, p.H, is_bf16, 128))
         return 1;
     Params prm = {(const uint2 *)nn_lut, (const uint64_t *)mask, o, p.B, p.H, p.nb_a, p.blocks, p.lut_stride, p.mask_stride,
                   scale * 1.4426950408889634f, is_bf16};
@@ -376,10 +393,10 @@ int tc_fused_attention(cudaStream_t s, const void *nn_lut, const void *q, const 
         if (e != cudaSuccess) return fail("sfb_fused_attention: cannot reserve %zu bytes of shared memory", kSmemBytes);
         configured = true;
     }
-    if (mask && is_bf16) fused_attention_tc_kernel<true, true><<<grid, 192, kSmemBytes, s>>>(qm, km, vm, prm);
-    else if (mask) fused_attention_tc_kernel<true, false><<<grid, 192, kSmemBytes, s>>>(qm, km, vm, prm);
-    else if (is_bf16) fused_attention_tc_kernel<false, true><<<grid, 192, kSmemBytes, s>>>(qm, km, vm, prm);
-    else fused_attention_tc_kernel<false, false><<<grid, 192, kSmemBytes, s>>>(qm, km, vm, prm);
+    if (mask && is_bf16) fused_attention_tc_kernel<true, true><<<grid, 192, kSmemBytes, s>>>(qm, km, vm, om, prm);
+    else if (mask) fused_attention_tc_kernel<true, false><<<grid, 192, kSmemBytes, s>>>(qm, km, vm, om, prm);
+    else if (is_bf16) fused_attention_tc_kernel<false, true><<<grid, 192, kSmemBytes, s>>>(qm, km, vm, om, prm);
+    else fused_attention_tc_kernel<false, false><<<grid, 192, kSmemBytes, s>>>(qm, km, vm, om, prm);
     return check_launch("sfb_fused_attention");
 }
 
