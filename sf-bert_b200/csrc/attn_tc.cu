@@ -291,6 +291,8 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
         // ---- epilogue: O / row sum -> global.  The four softmax warps agree first on whether all of them got here
         // in good order (they meet at a named barrier below, so they take that road together or not at all) ----
         if (T > 0 && alive) alive = mbar_wait_warp(&st->o_final, 0, abort_flag, 10);
+        // a row pair without key blocks never multiplied: its Q load may still be on its way into the buffer O is staged in
+        if (T == 0 && alive) alive = mbar_wait_warp(&st->q_full, 0, abort_flag, 2);
         uint32_t all_ok;
         asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.red.and.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                      : "=r"(all_ok) : "r"((uint32_t)alive) : "memory");
