@@ -419,6 +419,24 @@ def run_bandwidth_kernel(args):
         fn = lambda: sfb.masked_softmax_grad(dy, y, lay, 0.125)
         nbytes = dy.numel() * 2 * 3
         name, unit_name = "softmax_grad_kernel", "bf16 dy and y read + bf16 dx written"
+    elif args.kernel == "attention_backward":
+        # the reference's five backward calls (transformer_attention_optimize.cu:924-964) on 16-bit operands, from saved probabilities
+        lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
+        q, k, v, do = (torch.randn(B, L, H, d, device="cuda").to(torch.bfloat16) for _ in range(4))
+        pblk = sfb.fused_sddmm_softmax(q, k, lay, 0.125, torch.bfloat16)
+        _ = lay.tn_lut
+        blk_bytes = pblk.numel() * 2
+        if args.fused_grad:
+            o = sfb.bst_sgemm_xn(pblk, v, lay)
+            fn = lambda: sfb.attention_backward_fused(q, k, v, pblk, o, do, lay, 0.125)
+            # dV: P in; dS: P in, dS out; dK, dQ: dS in
+            nbytes = 5 * blk_bytes + 10 * q.numel() * 2
+            name, unit_name = "spmm_tc_kernel x3 + sddmm_tc_kernel<GRAD> + rowdot_kernel", "5 passes over the block tensors + the dense operands"
+        else:
+            fn = lambda: sfb.attention_backward(q, k, v, pblk, do, lay, 0.125)
+            # dV: P in; dP: out; dS: dP, P in, dS out; dK, dQ: dS in -- plus each [B,L,H,d] operand once per call
+            nbytes = 7 * blk_bytes + 10 * q.numel() * 2
+            name, unit_name = "spmm_tc_kernel x3 + sddmm_tc_kernel + softmax_grad_kernel", "7 passes over the block tensors + the dense operands of the five calls"
     elif args.kernel == "spmm_tn":
         lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
         pblk = torch.rand(B, H, lay.blocks, bs, bs, device="cuda").to(torch.bfloat16)
@@ -468,15 +486,16 @@ def run_bandwidth_kernel(args):
     print(json.dumps({
         "metric": args.kernel + " GB/s (algorithmic bytes)", "value": round(gbs, 1), "unit": "GB/s", "n_gpus": 1,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5), "higher_is_better": True,
-        "dtype": "bf16" if args.kernel in ("softmax", "softmax_grad", "spmm_tn") else cfg["dtype"], "data": "synthetic",
+        "dtype": "bf16" if args.kernel in ("softmax", "softmax_grad", "spmm_tn", "attention_backward") else cfg["dtype"], "data": "synthetic",
         "tflops_on_kept_blocks": (round(2.0 * bs * bs * d * lay.blocks * B * H / (ms * 1e-3) / 1e12, 1)
                                   if args.kernel in ("sddmm", "spmm", "fused_p", "spmm_tn") else
-                                  round(4.0 * bs * bs * d * lay.blocks * B * H / (ms * 1e-3) / 1e12, 2) if args.kernel == "csr_attention" else None),
+                                  round(4.0 * bs * bs * d * lay.blocks * B * H / (ms * 1e-3) / 1e12, 2) if args.kernel == "csr_attention" else
+                                  round(8.0 * bs * bs * d * lay.blocks * B * H / (ms * 1e-3) / 1e12, 1) if args.kernel == "attention_backward" else None),
         "config": {"workload": args.config, "kernel": name, "bytes": unit_name, "l2": "flushed between timed steps"},
         "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm"], "unit": "GB/s",
                      "frac": round(gbs / pk["hbm"], 4), "traffic": None, "peak_source": pk["source"] + " copy bandwidth",
                      "algorithmic_bytes": nbytes},
-        "gpu_launches": args.steps, "clocks": clocks}), flush=True)
+        "gpu_launches": args.steps * (5 if args.kernel == "attention_backward" else 1), "clocks": clocks}), flush=True)
 
 
 def run_linear(args, sfb, cfg, pk, flush):
@@ -660,10 +679,11 @@ if __name__ == "__main__":
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="stride_bertbase", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer", "softmax_grad", "spmm_tn", "linear", "embedding", "encoder_stack", "csr_attention"],
+    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer", "softmax_grad", "spmm_tn", "linear", "embedding", "encoder_stack", "csr_attention", "attention_backward"],
                     help="fused = the headline fused attention; softmax / layernorm = the bandwidth kernels (N=1)")
     ap.add_argument("--projections", default="tensor", choices=["tensor", "library"],
                     help="--kernel encoder_layer: the layer's GEMMs on this library's tcgen05 kernel or on the GEMM library")
+    ap.add_argument("--fused-grad", action="store_true", help="--kernel attention_backward: dP and dS in one launch (sfb_fused_sddmm_softmax_grad)")
     ap.add_argument("--layers", type=int, default=24, help="--kernel encoder_stack: number of encoder layers")
     a = ap.parse_args()
     if a.impl == "reference":

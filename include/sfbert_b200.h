@@ -145,6 +145,21 @@ int sfb_masked_softmax_grad(sfb_stream_t stream, const void *lut, const void *dy
                             uint32_t head_dim, uint32_t ctx_blks, uint32_t lut_heads, uint32_t lut_dim,
                             uint32_t max_lut, float scale);
 
+/* out[row] = sum over the row of a * b, rows of d elements (d a multiple of 8) of type dtype, out fp32.
+ * delta = sfb_rowdot(dO, O) over the B*L*H head rows is the row constant of the softmax gradient below.
+ * No counterpart in the reference. */
+int sfb_rowdot(sfb_stream_t stream, float *out, const void *a, const void *b, uint64_t rows, uint32_t d, int dtype);
+
+/* dS = P * (dO . V^T - delta) * scale on the kept blocks in ONE launch, in place of sfb_bst_sgemm_nt(dO, V) followed by
+ * sfb_masked_softmax_grad (transformer_attention_optimize.cu:934-944): delta [B, L, H] (fp32, sfb_rowdot(dO, O))
+ * equals the sum over a query row of dP * P that the unfused gradient reduces first, so no pass over the row is
+ * needed and dP is never written.  lut is the nt_lut; dO, V are [B, L, H, d]; P and dS are [B, H, blocks, 64, 64];
+ * all four of type dtype (SFB_BF16 or SFB_F16); block_size 64, state_dim 64.  No counterpart in the reference. */
+int sfb_fused_sddmm_softmax_grad(sfb_stream_t stream, const void *nt_lut, const void *dout, const void *v,
+                                 const void *p_blocks, const float *delta, void *ds, int dtype, uint32_t block_size,
+                                 uint32_t blocks, uint32_t batch_dim, uint32_t ctx_blks, uint32_t head_dim,
+                                 uint32_t state_dim, uint32_t lut_heads, uint32_t lut_dim, float scale);
+
 /* ---- fused, synchronisation-free operators -------------------------------------------- */
 
 /* SDDMM + masked softmax in one launch: each CTA owns a block-row, so there are no flags, no

@@ -25,7 +25,7 @@ SYMBOLS = [
     "sfb_magicu64", "sfb_bst_sgemm_nt", "sfb_masked_softmax", "sfb_bst_sgemm_xn", "sfb_fused_sddmm_softmax",
     "sfb_fused_attention", "sfb_bias_residual_layernorm", "sfb_device_status", "sfb_bias_gelu", "sfb_lut_build_tn",
     "sfb_masked_softmax_grad", "sfb_linear", "sfb_linear_nt", "sfb_embedding", "sfb_csr_from_layout",
-    "sfb_csr_attention",
+    "sfb_csr_attention", "sfb_rowdot", "sfb_fused_sddmm_softmax_grad",
 ]
 
 if not os.path.exists(LIB_PATH):
@@ -51,6 +51,8 @@ lib.sfb_linear.argtypes = [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _i32, _i32
 lib.sfb_linear_nt.argtypes = [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _i32, _i32]
 lib.sfb_embedding.argtypes = [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _i32, _vp]
 lib.sfb_csr_from_layout.argtypes = [_vp, _vp, _u32, _u32, _vp, _vp]
+lib.sfb_rowdot.argtypes = [_vp, _vp, _vp, _vp, _u64, _u32, _i32]
+lib.sfb_fused_sddmm_softmax_grad.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32] + [_u32] * 8 + [_f32]
 lib.sfb_csr_attention.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _u32, _u32, _u32, _u32, _f32, _vp]
 lib.sfb_fused_sddmm_softmax.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 10 + [_f32]
 lib.sfb_fused_attention.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32] + [_u32] * 9 + [_f32, _u32]
@@ -289,6 +291,35 @@ def masked_softmax_grad(dy, y, lay, scale):
     _check(lib.sfb_masked_softmax_grad(_stream(), _p(lay.nn_lut), _p(dy), _p(y), _p(dx), dtype_tag(y), lay.block_size,
                                        lay.blocks, B, H, lay.nb, lay.heads, lay.nn_lut_dim, lay.nn_max, scale))
     return dx
+
+
+def rowdot(a, b):
+    """sum over the last dimension of a * b, fp32: delta = rowdot(dO, O) for the fused softmax gradient."""
+    assert a.shape == b.shape and a.dtype == b.dtype and a.is_contiguous() and b.is_contiguous()
+    d = a.shape[-1]
+    out = torch.empty(a.shape[:-1], dtype=torch.float32, device=a.device)
+    _check(lib.sfb_rowdot(_stream(), _p(out), _p(a), _p(b), a.numel() // d, d, dtype_tag(a)))
+    return out
+
+
+def fused_sddmm_softmax_grad(do, v, p, delta, lay, scale):
+    """dS = P * (dO.V^T - delta) * scale in one launch (16-bit operands, 64x64 blocks, 64-wide heads)."""
+    B, L, H, d = _dims(do, lay)
+    assert p.dtype == do.dtype == v.dtype and delta.dtype == torch.float32 and tuple(delta.shape) == (B, L, H)
+    ds = torch.empty_like(p)
+    _check(lib.sfb_fused_sddmm_softmax_grad(_stream(), _p(lay.nt_lut), _p(do), _p(v), _p(p), _p(delta), _p(ds), dtype_tag(p),
+                                            lay.block_size, lay.blocks, B, lay.nb, H, d, lay.heads, lay.nt_lut_dim, scale))
+    return ds
+
+
+def attention_backward_fused(q, k, v, p, o, do, lay, scale):
+    """The backward with the dP / dS pair fused: dV = P^T.dO, dS = P*(dO.V^T - rowdot(dO, O))*scale, dK = dS^T.Q, dQ = dS.K.
+    16-bit operands; o is the forward output.  Returns (dq, dk, dv)."""
+    dv = bst_sgemm_tn(p, do, lay)
+    ds = fused_sddmm_softmax_grad(do, v, p, rowdot(do, o), lay, scale)
+    dk = bst_sgemm_tn(ds, q, lay)
+    dq = bst_sgemm_xn(ds, k, lay)
+    return dq, dk, dv
 
 
 def attention_backward(q, k, v, p, do, lay, scale, s_dtype=torch.bfloat16):

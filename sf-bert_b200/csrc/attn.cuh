@@ -36,6 +36,9 @@ int tc_spmm(cudaStream_t s, const void *lut, const void *a, const void *b, void 
 bool tc_fused_p_supported(int ab_dtype, uint32_t bs, const AttnDims &p, float scale);
 int tc_fused_p(cudaStream_t s, const void *nn_lut, const void *a, const void *b, const void *mask, void *y, int ab_dtype,
                int y_dtype, const AttnDims &p, float scale);
+int tc_sddmm_softmax_grad(cudaStream_t s, const void *nt_lut, const void *dout, const void *v, const void *pblk, const float *delta,
+                          void *ds, int dtype, const AttnDims &p, float scale);
+int rowdot(cudaStream_t s, float *out, const void *a, const void *b, size_t rows, uint32_t d, int dtype);
 int tc_status_unfused(uint32_t *out);
 
 // tcgen05 dense projection (gemm_tc.cu)

@@ -29,6 +29,8 @@ struct UParams {
     int is_bf16;               // operand format
     uint32_t p_rows;           // spmm: rows of the 2-D view of P (= B*H*blocks*64); a coordinate beyond it reads zeros
     int trans;                 // spmm: 1 = the blocks are used transposed and the LUT walks block columns (TN_OP)
+    const float *delta;        // sddmm, gradient mode: [B, L, H] row sums of dO * O
+    float scale;               // sddmm, gradient mode
 };
 
 constexpr int kSdStages = 3;
@@ -37,6 +39,7 @@ struct SdShared {
     uint32_t tmem_base, abort_flag;
 };
 constexpr size_t kSddmmSmem = 1024 + kSdStages * 2 * kTileBytes + 2 * kTileBytes /* output staging */ + sizeof(SdShared);
+constexpr size_t kSddmmGradSmem = 1024 + kSdStages * 3 * kTileBytes + 2 * kTileBytes + sizeof(SdShared);
 constexpr size_t kSpmmSmem = 1024 + kUStages * (kQBytes + kTileBytes) + sizeof(UShared);
 
 __device__ __forceinline__ void store_row16(void *dst_base, size_t elem_off, const uint32_t (&v)[16], int out_dtype, int c0)
@@ -66,16 +69,23 @@ __device__ __forceinline__ void store_row16(void *dst_base, size_t elem_off, con
 // by-product (K.K^T) that is never read -- the operator is bound by the 8 KB of S it writes per block, not by
 // tensor work.  warp 0: TMA; warp 1: MMA; warps 4-5 and 8-9: TMEM lanes 0-63 -> global, half a score row (32
 // columns) per thread.
+//
+// GRAD: the same kernel as the first half of a fused backward.  With a = dO and b = V the accumulator is dP = dO.V^T;
+// a third tile per stage brings the block of P, and the drain writes dS = P * (dP - delta) * scale, where
+// delta[row] = sum over the head of dO * O.  That row constant equals the sum over the row's blocks of dP * P which the
+// unfused softmax gradient has to reduce first, so dS needs no pass over the row and dP never reaches memory.
 constexpr uint32_t kChunk = 32;
 
-__global__ void __launch_bounds__(320, 4)
+template <bool GRAD>
+__global__ void __launch_bounds__(320, GRAD ? 2 : 4)
 sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
-                const __grid_constant__ CUtensorMap omap, const UParams p)
+                const __grid_constant__ CUtensorMap omap, const __grid_constant__ CUtensorMap pmap, const UParams p)
 {
+    constexpr uint32_t kStage = (GRAD ? 3 : 2) * kTileBytes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t *tiles = smem;                                   // stage s: Q rows (8 KB) then K rows (8 KB)
-    uint8_t *stage_out = tiles + kSdStages * 2 * kTileBytes; // two 8 KB tiles of 16-bit scores on their way out
+    uint8_t *tiles = smem;                                   // stage s: Q rows (8 KB), K rows (8 KB), GRAD: the block of P (8 KB)
+    uint8_t *stage_out = tiles + kSdStages * kStage;         // two 8 KB tiles of 16-bit scores on their way out
     SdShared *st = (SdShared *)(stage_out + 2 * kTileBytes);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,7 +98,8 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
     const uint32_t fmt = p.is_bf16 ? 1u : 0u;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kSdStages; s++) { mbar_init(&st->in_full[s], 1); mbar_init(&st->in_empty[s], 1); }
+        // GRAD: a stage is free when the MMA has read Q and K AND the 128 drain threads have read P
+        for (int s = 0; s < kSdStages; s++) { mbar_init(&st->in_full[s], 1); mbar_init(&st->in_empty[s], GRAD ? 129 : 1); }
         for (int s = 0; s < 2; s++) { mbar_init(&st->s_full[s], 1); mbar_init(&st->s_empty[s], 128); }
         mbar_init(&st->drained, 1);
         st->abort_flag = 0;
@@ -116,9 +127,12 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
                     atomicCAS(&g_status, 0u, (20u << 24) | (blockIdx.x & 0xffffffu));
                     break;
                 }
-                mbar_expect_tx(&st->in_full[s], 2 * kTileBytes);
-                tma_load_2d(smem_u32(tiles + s * 2 * kTileBytes), &qmap, &st->in_full[s], xq, (int32_t)(b * L + ent.x * 64));
-                tma_load_2d(smem_u32(tiles + s * 2 * kTileBytes + kTileBytes), &kmap, &st->in_full[s], xq, (int32_t)(b * L + ent.y * 64));
+                mbar_expect_tx(&st->in_full[s], kStage);
+                tma_load_2d(smem_u32(tiles + s * kStage), &qmap, &st->in_full[s], xq, (int32_t)(b * L + ent.x * 64));
+                tma_load_2d(smem_u32(tiles + s * kStage + kTileBytes), &kmap, &st->in_full[s], xq, (int32_t)(b * L + ent.y * 64));
+                if (GRAD)
+                    tma_load_2d(smem_u32(tiles + s * kStage + 2 * kTileBytes), &pmap, &st->in_full[s], 0,
+                                (int32_t)((((size_t)b * p.H + h) * p.blocks + k0 + t) * 64));
             }
         }
     } else if (warp == 1) {
@@ -129,8 +143,8 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
                 if (!mbar_wait(&st->in_full[s], (t / kSdStages) & 1, abort_flag, 23)) break;
                 if (t >= 2 && !mbar_wait(&st->s_empty[t & 1], ((t >> 1) - 1) & 1, abort_flag, 24)) break;
                 tcgen05_fence_after();
-                const uint64_t a_desc = smem_desc_sw128(smem_u32(tiles + s * 2 * kTileBytes));
-                const uint64_t b_desc = smem_desc_sw128(smem_u32(tiles + s * 2 * kTileBytes + kTileBytes));
+                const uint64_t a_desc = smem_desc_sw128(smem_u32(tiles + s * kStage));
+                const uint64_t b_desc = smem_desc_sw128(smem_u32(tiles + s * kStage + kTileBytes));
 #pragma unroll
                 for (uint32_t kk = 0; kk < 4; kk++) umma_f16(tmem + 64 * (t & 1), a_desc + 2 * kk, b_desc + 2 * kk, idesc, kk);
                 umma_commit(&st->s_full[t & 1]);
@@ -166,11 +180,39 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
                 if (leader) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the store that used this buffer has read it
                 asm volatile("bar.sync 4, 128;" ::: "memory");
                 uint8_t *orow = stage_out + (t & 1) * kTileBytes + r * 128;
+                const uint32_t sg = t % kSdStages;
+                const uint8_t *prow = tiles + sg * kStage + 2 * kTileBytes + r * 128;
+                float dl = 0.f;
+                bool p_ok = true;
+                if (GRAD) {
+                    // P arrived with the same transaction barrier the MMA waited for; observing it here makes the tile visible
+                    p_ok = mbar_wait_warp(&st->in_full[sg], (t / kSdStages) & 1, abort_flag, 26);
+                    dl = __ldg(p.delta + ((size_t)b * L + (size_t)lut[t].x * 64 + r) * p.H + h);
+                }
 #pragma unroll
                 for (int c0 = cbase; c0 < cbase + 32; c0 += 16) {
                     uint32_t v[16], w[8];
                     TMEM_LD_16((v), tmem + 64 * (t & 1) + lane_field + c0);
                     tmem_wait_ld();
+                    if (GRAD) {
+                        const uint32_t chp = c0 >> 3;
+                        const uint4 pa = *(const uint4 *)(prow + ((chp ^ (r & 7)) << 4)), pb = *(const uint4 *)(prow + (((chp + 1) ^ (r & 7)) << 4));
+                        const uint32_t pw[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            float p0, p1;
+                            if (p.out_dtype == SFB_BF16) {
+                                p0 = __uint_as_float(pw[j] << 16);
+                                p1 = __uint_as_float(pw[j] & 0xffff0000u);
+                            } else {
+                                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&pw[j]));
+                                p0 = f.x;
+                                p1 = f.y;
+                            }
+                            v[2 * j] = __float_as_uint(p_ok ? p0 * (__uint_as_float(v[2 * j]) - dl) * p.scale : 0.f);
+                            v[2 * j + 1] = __float_as_uint(p_ok ? p1 * (__uint_as_float(v[2 * j + 1]) - dl) * p.scale : 0.f);
+                        }
+                    }
 #pragma unroll
                     for (int j = 0; j < 8; j++) w[j] = pack2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), p.out_dtype == SFB_BF16);
                     const uint32_t ch = c0 >> 3;
@@ -185,6 +227,7 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
                                  ::"l"((uint64_t)&omap), "r"(smem_u32(stage_out + (t & 1) * kTileBytes)), "r"(0), "r"(y) : "memory");
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
+                if (GRAD) mbar_arrive(&st->in_empty[sg]);   // this thread is done with the stage's P tile
             }
             tcgen05_fence_before();
             mbar_arrive(&st->s_empty[t & 1]);
@@ -544,12 +587,38 @@ int tc_sddmm(cudaStream_t s, const void *nt_lut, const void *a, const void *b, v
     UParams prm = {(const uint2 *)nt_lut, c, p.B, p.H, p.nb_a, p.blocks, p.lut_stride, c_dtype, is_bf16, 0};
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(sddmm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSddmmSmem) != cudaSuccess)
-            return fail("sfb_bst_sgemm_nt: cannot reserve %zu bytes of shared memory", kSddmmSmem);
+        if (cudaFuncSetAttribute(sddmm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSddmmSmem) != cudaSuccess ||
+            cudaFuncSetAttribute(sddmm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSddmmGradSmem) != cudaSuccess)
+            return fail("sfb_bst_sgemm_nt: cannot reserve %zu bytes of shared memory", kSddmmGradSmem);
         configured = true;
     }
-    sddmm_tc_kernel<<<dim3((p.blocks + kChunk - 1) / kChunk, p.B, p.H), 320, kSddmmSmem, s>>>(qm, km, om, prm);
+    sddmm_tc_kernel<false><<<dim3((p.blocks + kChunk - 1) / kChunk, p.B, p.H), 320, kSddmmSmem, s>>>(qm, km, om, om, prm);
     return check_launch("sfb_bst_sgemm_nt");
+}
+
+// dS = P * (dO.V^T - delta) * scale on the kept blocks: 16-bit dO, V, P and dS of one type
+int tc_sddmm_softmax_grad(cudaStream_t s, const void *nt_lut, const void *dout, const void *v, const void *pblk, const float *delta,
+                          void *ds, int dtype, const AttnDims &p, float scale)
+{
+    using namespace tc;
+    SFB_REQUIRE((((uintptr_t)dout | (uintptr_t)v | (uintptr_t)pblk) & 15) == 0 && ((uintptr_t)ds & 31) == 0,
+                "sfb_fused_sddmm_softmax_grad: dO, V, P must be 16-byte and dS 32-byte aligned");
+    const int is_bf16 = dtype == SFB_BF16;
+    const uint64_t rows = (uint64_t)p.B * p.nb_a * 64, prow = (uint64_t)p.B * p.H * p.blocks * 64;
+    SFB_REQUIRE(prow < (1ull << 31), "sfb_fused_sddmm_softmax_grad: too many blocks for one launch");
+    CUtensorMap qm, km, om, pm;
+    if (make_map(&qm, dout, rows, p.H, is_bf16, 64) || make_map(&km, v, rows, p.H, is_bf16, 64) || make_p_map(&om, ds, prow, is_bf16) ||
+        make_p_map(&pm, pblk, prow, is_bf16))
+        return 1;
+    UParams prm = {(const uint2 *)nt_lut, ds, p.B, p.H, p.nb_a, p.blocks, p.lut_stride, dtype, is_bf16, 0, 0, delta, scale};
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(sddmm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSddmmGradSmem) != cudaSuccess)
+            return fail("sfb_fused_sddmm_softmax_grad: cannot reserve %zu bytes of shared memory", kSddmmGradSmem);
+        configured = true;
+    }
+    sddmm_tc_kernel<true><<<dim3((p.blocks + kChunk - 1) / kChunk, p.B, p.H), 320, kSddmmGradSmem, s>>>(qm, km, om, pm, prm);
+    return check_launch("sfb_fused_sddmm_softmax_grad");
 }
 
 bool tc_fused_p_supported(int ab_dtype, uint32_t bs, const AttnDims &p, float scale)

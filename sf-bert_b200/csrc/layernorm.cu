@@ -243,6 +243,38 @@ __global__ void __launch_bounds__(256) embedding_kernel(void *__restrict__ out, 
     }
 }
 
+// out[row] = sum over the row of a * b: rows of d elements, 8 lanes per row (16-byte accesses, shuffle reduction).
+// delta = rowdot(dO, O) is the row constant of the softmax gradient.
+template <int DT>
+__global__ void __launch_bounds__(256) rowdot_kernel(float *__restrict__ out, const void *__restrict__ a, const void *__restrict__ b,
+                                                    size_t rows, uint32_t d)
+{
+    constexpr int N = Vec8<DT>::N;
+    const size_t row = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) / 8;
+    const uint32_t part = threadIdx.x & 7;
+    float sum = 0.f;
+    if (row < rows)
+        for (uint32_t c = part * N; c < d; c += 8 * N) {
+            float x[N], y[N];
+            Vec8<DT>::load(x, a, row * d + c);
+            Vec8<DT>::load(y, b, row * d + c);
+#pragma unroll
+            for (int t = 0; t < N; t++) sum = fmaf(x[t], y[t], sum);
+        }
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (row < rows && part == 0) out[row] = sum;
+}
+
+int rowdot(cudaStream_t s, float *out, const void *a, const void *b, size_t rows, uint32_t d, int dtype)
+{
+    const unsigned ctas = (unsigned)((rows * 8 + 255) / 256);
+    if (dtype == SFB_F32) rowdot_kernel<SFB_F32><<<ctas, 256, 0, s>>>(out, a, b, rows, d);
+    else if (dtype == SFB_BF16) rowdot_kernel<SFB_BF16><<<ctas, 256, 0, s>>>(out, a, b, rows, d);
+    else rowdot_kernel<SFB_F16><<<ctas, 256, 0, s>>>(out, a, b, rows, d);
+    return check_launch("sfb_rowdot");
+}
+
 int embedding_lookup(cudaStream_t s, void *out, const void *table, const int32_t *ids, const void *pos, uint32_t batch,
                      uint32_t seq_len, uint32_t hidden, uint32_t vocab, int dtype, uint32_t *bad_ids)
 {

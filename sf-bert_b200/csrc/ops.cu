@@ -168,6 +168,35 @@ static int linear_common(const char *who, sfb_stream_t stream, void *out, const 
     return tc_linear(as_stream(stream), out, x, w, bias, m, n, k, dtype, act, w_transposed);
 }
 
+extern "C" int sfb_rowdot(sfb_stream_t stream, float *out, const void *a, const void *b, uint64_t rows, uint32_t d, int dtype)
+{
+    const char *who = "sfb_rowdot";
+    SFB_REQUIRE(out && a && b, "%s: NULL pointer", who);
+    SFB_REQUIRE(valid_dtype(dtype), "%s: unknown dtype", who);
+    SFB_REQUIRE(d % 8 == 0 && d > 0, "%s: row length %u must be a positive multiple of 8", who, d);
+    SFB_REQUIRE(aligned16(a) && aligned16(b), "%s: a and b must be 16-byte aligned", who);
+    SFB_REQUIRE(rows < (1ull << 40), "%s: too many rows", who);
+    if (rows == 0) { clear_error(); return 0; }
+    return rowdot(as_stream(stream), out, a, b, (size_t)rows, d, dtype);
+}
+
+extern "C" int sfb_fused_sddmm_softmax_grad(sfb_stream_t stream, const void *nt_lut, const void *dout, const void *v, const void *p_blocks,
+                                            const float *delta, void *ds, int dtype, uint32_t block_size, uint32_t blocks,
+                                            uint32_t batch_dim, uint32_t ctx_blks, uint32_t head_dim, uint32_t state_dim,
+                                            uint32_t lut_heads, uint32_t lut_dim, float scale)
+{
+    const char *who = "sfb_fused_sddmm_softmax_grad";
+    SFB_REQUIRE(nt_lut && dout && v && p_blocks && delta && ds, "%s: NULL pointer", who);
+    SFB_REQUIRE(dtype == SFB_BF16 || dtype == SFB_F16, "%s: dO, V, P and dS must be bf16 or fp16", who);
+    SFB_REQUIRE(block_size == 64 && state_dim == 64, "%s: block_size %u / state_dim %u not supported (64 / 64)", who, block_size, state_dim);
+    if (check_common(who, block_size, batch_dim, head_dim, state_dim, lut_heads)) return 1;
+    SFB_REQUIRE(lut_heads == 1 || lut_dim >= blocks, "%s: lut_dim %u smaller than blocks %u", who, lut_dim, blocks);
+    if (blocks == 0 || ctx_blks == 0) { clear_error(); return 0; }
+    AttnDims p = {batch_dim, head_dim, state_dim, ctx_blks, ctx_blks, blocks, lut_heads > 1 ? lut_dim : 0, 0};
+    SFB_REQUIRE((uint64_t)batch_dim * ctx_blks * 64 < (1ull << 31), "%s: sequence too long for one launch", who);
+    return tc_sddmm_softmax_grad(as_stream(stream), nt_lut, dout, v, p_blocks, delta, ds, dtype, p, scale);
+}
+
 extern "C" int sfb_device_status(uint32_t *status)
 {
     SFB_REQUIRE(status, "sfb_device_status: NULL pointer");

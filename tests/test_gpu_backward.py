@@ -196,3 +196,36 @@ def test_backward_at_benchmark_size_properties(sfb, oracle):
     want_dk = oracle.spmm_tn(dsn, q[b0:b0 + 1, :, h0:h0 + 1].cpu().numpy(), tn, bs)
     got_dk = dk[b0:b0 + 1, :, h0:h0 + 1].cpu().numpy()
     assert np.abs(got_dk - want_dk).max() <= 1e-4 * max(1.0, np.abs(want_dk).max())
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("H_lut,nb,kind,kw,dev", [
+    (1, 16, "stride", dict(band=4, every=8), ("LAYOUT_STRIDE", dict(p0=4, p1=8))),
+    (1, 5, "full", dict(causal=1), ("LAYOUT_FULL", dict(causal=1))),
+    (4, 16, "fixed", dict(stride=4), ("LAYOUT_FIXED", dict(p0=4))),             # per-head LUTs
+    (1, 40, "local", dict(left=1, right=2), ("LAYOUT_LOCAL", dict(p0=1, p1=2))),  # more blocks than one CTA's chunk
+])
+def test_fused_sddmm_softmax_grad(sfb, oracle, dtype, H_lut, nb, kind, kw, dev):
+    """dS = P*(dO.V^T - rowdot(dO, O))*scale in one launch against the oracle's unfused chain on the same P."""
+    B, H, bs, d = 2, 4, 64, 64
+    lay, ref_layout, luts = _make(sfb, oracle, kind, kw, dev, H_lut, nb, bs)
+    scale = np.float32(0.125)
+    q, k, v, do = (torch.from_numpy(oracle.fill_normal((B, nb * bs, H, d), 370 + i)).cuda().to(TD[dtype]) for i in range(4))
+    fwd = oracle.attention(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(), luts, bs, scale, eps=0.0, want=("p",))
+    p = torch.from_numpy(fwd["p"]).cuda().to(TD[dtype])
+    pn, von, don = p.float().cpu().numpy(), v.float().cpu().numpy(), do.float().cpu().numpy()
+    o = oracle.spmm_nn(pn, von, luts["nn"], bs)                              # the forward output that belongs to this (rounded) P
+    delta = sfb.rowdot(do, torch.from_numpy(o).cuda().to(TD[dtype]))
+    want_delta = (don * torch.from_numpy(o).to(TD[dtype]).float().numpy()).sum(-1)
+    np.testing.assert_allclose(delta.cpu().numpy(), want_delta, rtol=0, atol=1e-4 * max(1.0, np.abs(want_delta).max()))
+    ds = sfb.fused_sddmm_softmax_grad(do, v, p, delta, lay, float(scale)).float().cpu().numpy()
+    assert sfb.device_status() == 0
+    dp = oracle.attention(don, von, von, luts, bs, scale, want=("s",))["s"]
+    want = oracle.softmax_grad(dp, pn, luts, bs, scale)
+    assert np.abs(ds - want).max() <= 3e-2 * np.abs(want).max()
+    # and the whole fused backward against the unfused one
+    dq1, dk1, dv1 = sfb.attention_backward_fused(q, k, v, p, torch.from_numpy(o).cuda().to(TD[dtype]), do, lay, float(scale))
+    dq0, dk0, dv0 = sfb.attention_backward(q, k, v, p, do, lay, float(scale), s_dtype=TD[dtype])
+    for a, b in ((dq1, dq0), (dk1, dk0), (dv1, dv0)):
+        assert float((a.float() - b.float()).abs().max()) <= 5e-2 * float(b.float().abs().max())
+
