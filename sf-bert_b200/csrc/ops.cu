@@ -161,7 +161,8 @@ static int linear_common(const char *who, sfb_stream_t stream, void *out, const 
     SFB_REQUIRE(dtype == SFB_BF16 || dtype == SFB_F16, "%s: x, w and out must be bf16 or fp16 (fp32 products stay with the GEMM library)", who);
     SFB_REQUIRE(act == SFB_ACT_NONE || act == SFB_ACT_GELU, "%s: unknown activation %d", who, act);
     SFB_REQUIRE(n % 16 == 0 && k % 8 == 0, "%s: n=%u must be a multiple of 16 and k=%u of 8", who, n, k);
-    SFB_REQUIRE(aligned16(x) && aligned16(w) && ((uintptr_t)out & 31) == 0, "%s: x, w must be 16-byte and out 32-byte aligned", who);
+    SFB_REQUIRE(aligned16(x) && aligned16(w) && (!bias || aligned16(bias)) && ((uintptr_t)out & 31) == 0,
+                "%s: x, w, bias must be 16-byte and out 32-byte aligned", who);
     SFB_REQUIRE((uint64_t)m < (1ull << 31) && (uint64_t)n < (1ull << 31) && (uint64_t)k < (1ull << 31), "%s: dimension too large", who);
     if (m == 0 || n == 0) { clear_error(); return 0; }
     SFB_REQUIRE(k > 0, "%s: k is 0", who);
