@@ -672,6 +672,52 @@ def cpu_reference_sample(cfg, budget_s, steps):
             "seconds_per_pass": best, "L_sample": Ls}
 
 
+def reference_gpu_sample(cfg, steps, warmup):
+    """Times the reference's own unfused GPU operators on this GPU: bst_sgemm_nt -> BlocksparseMaskedSoftmax ->
+    bst_sgemm_xn (the three launches of transformer_attention_optimize.cu:728,738,748), compiled for sm_100a from the
+    reference header.  Its matmuls exist for 32x32 blocks only, so the workload's layout is split into 32x32 blocks:
+    the same element mask, the same attention, four times the block count.  fp32 activations, bf16 scores and
+    probabilities, as the reference stores them.  Returns None without a GPU or without the prebuilt library.
+    The reference's fused kernels spin on global flags without a bound and are not run."""
+    try:
+        import torch
+    except ImportError:
+        return None
+    if not torch.cuda.is_available():
+        return None
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as O
+    if O.ref_gpu() is None:
+        return None
+    B, H, L, d, bs = cfg["B"], cfg["H"], cfg["L"], cfg["d"], cfg["bs"]
+    lay = O.layout(cfg["oracle"][0], cfg.get("lut_heads", 1), L // bs, **cfg["oracle"][1])
+    kept = int(lay[0].sum())
+    if bs != 32:
+        lay = O.split_layout(lay, bs // 32)
+    ref = O.RefGpuAttention(lay)
+    g = torch.Generator(device="cuda").manual_seed(1234)
+    q, k, v = (torch.randn(B, L, H, d, device="cuda", generator=g) for _ in range(3))
+    ref.alloc(q)
+    scale = 1.0 / d ** 0.5
+    for _ in range(max(warmup, 3)):
+        ref.launch(q, k, v, scale)
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(max(steps, 1))]
+    for a, b in ev:
+        a.record()
+        ref.launch(q, k, v, scale)
+        b.record()
+    torch.cuda.synchronize()
+    ms = statistics.mean(a.elapsed_time(b) for a, b in ev)
+    flops = 4.0 * bs * bs * d * kept * B * H
+    finite = bool(torch.isfinite(ref.o).all())
+    return {"value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "launches_per_step": 3,
+            "blocks_32x32_per_head": ref.blocks, "finite": finite,
+            "what": "reference bst_sgemm_nt + BlocksparseMaskedSoftmax<bhalf> + bst_sgemm_xn(NN) on this GPU, fp32 "
+                    "activations, bf16 scores, the %s layout split into 32x32 blocks, inputs larger than L2, CUDA events"
+                    % cfg["oracle"][0]}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -689,6 +735,9 @@ def run_reference(args):
         "cpu_baseline": {"value": res["value"], "unit": "TFLOP/s", "cores": res["cores"], "kind": res["kind"], "sample": res["sample"]},
         "e2e": {"value": res["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    gpu = reference_gpu_sample(cfg, args.steps, args.warmup)
+    if gpu is not None:
+        line["reference_gpu"] = gpu
     print(json.dumps(line), flush=True)
 
 

@@ -453,3 +453,73 @@ def blocks_to_dense(blk, nt, nb, bs):
             i, j = int(lut[kk, 0]), int(lut[kk, 1])
             out[:, h, i * bs:(i + 1) * bs, j * bs:(j + 1) * bs] = blk[:, h, kk]
     return out
+
+
+# ---------------------------------------------------------------- the reference's unfused GPU operators
+_ref_gpu = None
+
+
+def ref_gpu():
+    """The reference's SDDMM / masked softmax / SpMM kernels compiled for this GPU
+    (oracle/_ref/libsfb_ref_gpu.so); None when it was never built."""
+    global _ref_gpu
+    if _ref_gpu is None:
+        path = os.path.join(ORACLE_DIR, "_ref", "libsfb_ref_gpu.so")
+        if not os.path.exists(path):
+            return None
+        _ref_gpu = C.CDLL(path)
+    return _ref_gpu
+
+
+def split_layout(lay, factor=2):
+    """The same element mask on blocks `factor` times smaller: every kept block becomes factor x factor kept blocks."""
+    lay = np.ascontiguousarray(lay, dtype=np.uint8)
+    return np.ascontiguousarray(lay.repeat(factor, axis=1).repeat(factor, axis=2))
+
+
+class RefGpuAttention:
+    """Device copies of the LUTs of one layout (built by the oracle, block size 32) and the three launches the
+    reference's training driver makes per layer (transformer_attention_optimize.cu:728,738,748):
+    bst_sgemm_nt -> BlocksparseMaskedSoftmax -> bst_sgemm_xn(NN_OP).  q, k, v: CUDA fp32 [B, L, H, d]."""
+
+    def __init__(self, layout, device="cuda"):
+        import torch
+        self.torch = torch
+        self.G = ref_gpu()
+        assert self.G is not None
+        luts = lut_build(layout)
+        self.heads, self.nb = layout.shape[0], layout.shape[1]
+        self.blocks, self.nn_max = luts["blocks"], luts["nn_max"]
+        self.nt = torch.from_numpy(luts["nt"].view(np.int32)).to(device)
+        self.nn = torch.from_numpy(luts["nn"].view(np.int32)).to(device)
+        self.s = self.p = self.o = None
+
+    def alloc(self, q, p_float=False):
+        torch = self.torch
+        B, L, H, d = q.shape
+        assert L == self.nb * 32 and self.heads in (1, H) and q.dtype == torch.float32 and q.is_contiguous()
+        self.s = torch.empty(B, H, self.blocks, 32, 32, dtype=torch.bfloat16, device=q.device)
+        self.p = torch.empty(B, H, self.blocks, 32, 32, dtype=torch.float32 if p_float else torch.bfloat16, device=q.device)
+        self.o = torch.empty_like(q)
+
+    def launch(self, q, k, v, scale):
+        """The three launches on torch's current stream; returns nothing (results in self.s, self.p, self.o)."""
+        torch = self.torch
+        B, L, H, d = q.shape
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        vp = lambda t: C.c_void_p(t.data_ptr())
+        u = C.c_uint32
+        G = self.G
+        rc = G.ref_gpu_bst_sgemm_nt(st, vp(self.nt), vp(q), vp(k), vp(self.s), u(32), u(self.blocks), u(B), u(self.nb),
+                                    u(self.nb), u(H), u(d), u(self.heads), u(self.blocks))
+        assert rc == 0, rc
+        rc = G.ref_gpu_masked_softmax(st, vp(self.nn), None, vp(self.s), vp(self.p),
+                                      C.c_int(1 if self.p.dtype == torch.float32 else 0), u(32), u(self.blocks), u(B),
+                                      u(H), u(self.nb), u(self.heads), u(self.blocks + self.nb), u(self.nn_max),
+                                      u(self.heads), C.c_float(scale))
+        assert rc == 0, rc
+        if self.p.dtype == torch.bfloat16:
+            rc = G.ref_gpu_bst_sgemm_nn(st, vp(self.nn), vp(self.p), vp(v), vp(self.o), u(32), u(self.blocks), u(B),
+                                        u(self.nb), u(self.nb), u(H), u(d), u(self.heads), u(self.blocks + self.nb),
+                                        u(self.nn_max))
+            assert rc == 0, rc
