@@ -56,6 +56,24 @@ def peaks():
     return dict(tensor=1590.0, tensor_sustained=1400.0, hbm=6650.0, source="fallback")
 
 
+class L2Flush:
+    """What runs between timed steps: 256 MB written (twice the 126 MB L2) and then, unless mode is "write", 256 MB of a
+    second buffer read.  After the write alone the L2 is full of the flush's own dirty lines, and their write-back
+    (up to ~120 MB of DRAM writes) would land inside the next timed kernel; after the read it is cold and clean."""
+
+    def __init__(self, torch, mode="write_read"):
+        self.mode = mode
+        self.w = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        self.r = torch.zeros(64 << 20, dtype=torch.int32, device="cuda") if mode != "write" else None
+        self.note = ("256 MB written then 256 MB read between timed steps (cold and clean)" if mode != "write"
+                     else "256 MB written between timed steps")
+
+    def fill_(self, value=1):
+        self.w.fill_(value)
+        if self.r is not None:
+            self.sink = self.r.sum()
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples while the timed region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -151,7 +169,7 @@ def run_ours(args):
     o = torch.empty_like(q)
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
     ho = torch.empty_like(hq).pin_memory()
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")   # larger than the 126 MB L2
+    flush = L2Flush(torch, args.l2_flush)
 
     def step():
         sfb.fused_attention(q, k, v, lay, scale, out=o)
@@ -233,7 +251,7 @@ def run_ours(args):
             "dtype": cfg["dtype"], "data": "synthetic",
             "config": {"workload": args.config, "B_per_gpu": B, "H": H, "L": L, "d": d, "block": bs,
                        "layout": cfg["layout"][0], "nnz_blocks_per_head": lay.blocks, "max_row": lay.nn_max,
-                       "sharding": "batch x head, no collective on the data path", "l2": "flushed between timed steps"},
+                       "sharding": "batch x head, no collective on the data path", "l2": flush.note},
             "roofline": {"bound": "tensor", "achieved": round(per_gpu, 3), "peak": pk["tensor"], "unit": "TFLOP/s",
                          "frac": round(per_gpu / pk["tensor"], 4), "traffic": NCU_TRAFFIC_BYTES.get(args.config),
                          "peak_source": pk["source"] + " burst bf16",
@@ -401,7 +419,7 @@ def run_bandwidth_kernel(args):
     cfg = CONFIGS[args.config]
     B, H, L, d, bs = cfg["B"], cfg["H"], cfg["L"], cfg["d"], cfg["bs"]
     pk = peaks()
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    flush = L2Flush(torch, args.l2_flush)
     if args.kernel == "encoder_layer":
         return run_encoder_layer(args, sfb, cfg, pk, flush)
     if args.kernel == "linear":
@@ -512,7 +530,7 @@ def run_bandwidth_kernel(args):
                                   if args.kernel in ("sddmm", "spmm", "fused_p", "spmm_tn") else
                                   round(4.0 * bs * bs * d * lay.blocks * B * H / (ms * 1e-3) / 1e12, 2) if args.kernel == "csr_attention" else
                                   round(8.0 * bs * bs * d * lay.blocks * B * H / (ms * 1e-3) / 1e12, 1) if args.kernel == "attention_backward" else None),
-        "config": {"workload": args.config, "kernel": name, "bytes": unit_name, "l2": "flushed between timed steps"},
+        "config": {"workload": args.config, "kernel": name, "bytes": unit_name, "l2": flush.note},
         "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm"], "unit": "GB/s",
                      "frac": round(gbs / pk["hbm"], 4), "traffic": None, "peak_source": pk["source"] + " copy bandwidth",
                      "algorithmic_bytes": nbytes},
@@ -573,7 +591,7 @@ def run_linear(args, sfb, cfg, pk, flush):
         "warmup": max(args.warmup, 3), "ms_per_step": round(total_ms, 4), "higher_is_better": True, "dtype": cfg["dtype"],
         "data": "synthetic",
         "config": {"workload": args.config, "kernel": "linear_tc_kernel", "products": res, "library": "torch.addmm (+ gelu) on cuBLAS",
-                   "library_ms": round(total_lib, 4), "l2": "flushed between timed steps"},
+                   "library_ms": round(total_lib, 4), "l2": flush.note},
         "roofline": {"bound": "tensor", "achieved": round(tf, 1), "peak": pk["tensor"], "unit": "TFLOP/s", "frac": round(tf / pk["tensor"], 4),
                      "traffic": None, "peak_source": pk["source"] + " cuBLAS bf16 burst"},
         "gpu_launches": args.steps * 4, "clocks": clocks}), flush=True)
@@ -616,7 +634,7 @@ def run_encoder_layer(args, sfb, cfg, pk, flush):
         "dtype": cfg["dtype"], "data": "synthetic",
         "config": {"workload": args.config, "B": B, "L": L, "hidden": hidden, "ffn": ffn, "heads": H, "ln": "post",
                    "projections": "sfb_linear (tcgen05, bias/GELU in the epilogue)" if proj == "tensor" else "torch.matmul (cuBLAS)",
-                   "l2": "flushed between timed steps"},
+                   "l2": flush.note},
         "tflops_total": round((gemm_flops + attn_flops) / (ms * 1e-3) / 1e12, 1),
         "gpu_launches": args.steps * 4, "clocks": clocks}), flush=True)
 
@@ -702,17 +720,16 @@ def reference_gpu_sample(cfg, steps, warmup):
     for _ in range(max(warmup, 3)):
         ref.launch(q, k, v, scale)
     torch.cuda.synchronize()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(max(steps, 1))]
-    for a, b in ev:
-        a.record()
-        ref.launch(q, k, v, scale)
-        b.record()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(max(steps, 1))]
+    for marks in ev:
+        ref.launch(q, k, v, scale, marks)
     torch.cuda.synchronize()
-    ms = statistics.mean(a.elapsed_time(b) for a, b in ev)
+    ms = statistics.mean(m[0].elapsed_time(m[3]) for m in ev)
+    per_launch = [statistics.mean(m[i].elapsed_time(m[i + 1]) for m in ev) for i in range(3)]
     flops = 4.0 * bs * bs * d * kept * B * H
     finite = bool(torch.isfinite(ref.o).all())
     return {"value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "launches_per_step": 3,
-            "blocks_32x32_per_head": ref.blocks, "finite": finite,
+            "ms_sddmm_softmax_spmm": [round(x, 4) for x in per_launch], "blocks_32x32_per_head": ref.blocks, "finite": finite,
             "what": "reference bst_sgemm_nt + BlocksparseMaskedSoftmax<bhalf> + bst_sgemm_xn(NN) on this GPU, fp32 "
                     "activations, bf16 scores, the %s layout split into 32x32 blocks, inputs larger than L2, CUDA events"
                     % cfg["oracle"][0]}
@@ -754,6 +771,8 @@ if __name__ == "__main__":
     ap.add_argument("--projections", default="tensor", choices=["tensor", "library"],
                     help="--kernel encoder_layer: the layer's GEMMs on this library's tcgen05 kernel or on the GEMM library")
     ap.add_argument("--fused-grad", action="store_true", help="--kernel attention_backward: dP and dS in one launch (sfb_fused_sddmm_softmax_grad)")
+    ap.add_argument("--l2-flush", default="write_read", choices=["write_read", "write"],
+                    help="what runs between timed steps: 256 MB written and 256 MB read (cold, clean L2), or the write alone")
     ap.add_argument("--layers", type=int, default=24, help="--kernel encoder_stack: number of encoder layers")
     a = ap.parse_args()
     if a.impl == "reference":

@@ -502,24 +502,30 @@ class RefGpuAttention:
         self.p = torch.empty(B, H, self.blocks, 32, 32, dtype=torch.float32 if p_float else torch.bfloat16, device=q.device)
         self.o = torch.empty_like(q)
 
-    def launch(self, q, k, v, scale):
-        """The three launches on torch's current stream; returns nothing (results in self.s, self.p, self.o)."""
+    def launch(self, q, k, v, scale, marks=None):
+        """The three launches on torch's current stream; returns nothing (results in self.s, self.p, self.o).
+        marks: optional list of four CUDA events recorded before, between and after the launches."""
         torch = self.torch
+        mark = (lambda i: marks[i].record()) if marks is not None else (lambda i: None)
         B, L, H, d = q.shape
         st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
         vp = lambda t: C.c_void_p(t.data_ptr())
         u = C.c_uint32
         G = self.G
+        mark(0)
         rc = G.ref_gpu_bst_sgemm_nt(st, vp(self.nt), vp(q), vp(k), vp(self.s), u(32), u(self.blocks), u(B), u(self.nb),
                                     u(self.nb), u(H), u(d), u(self.heads), u(self.blocks))
         assert rc == 0, rc
+        mark(1)
         rc = G.ref_gpu_masked_softmax(st, vp(self.nn), None, vp(self.s), vp(self.p),
                                       C.c_int(1 if self.p.dtype == torch.float32 else 0), u(32), u(self.blocks), u(B),
                                       u(H), u(self.nb), u(self.heads), u(self.blocks + self.nb), u(self.nn_max),
                                       u(self.heads), C.c_float(scale))
         assert rc == 0, rc
+        mark(2)
         if self.p.dtype == torch.bfloat16:
             rc = G.ref_gpu_bst_sgemm_nn(st, vp(self.nn), vp(self.p), vp(v), vp(self.o), u(32), u(self.blocks), u(B),
                                         u(self.nb), u(self.nb), u(H), u(d), u(self.heads), u(self.blocks + self.nb),
                                         u(self.nn_max))
             assert rc == 0, rc
+        mark(3)

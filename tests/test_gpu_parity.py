@@ -271,6 +271,25 @@ def test_bias_residual_layernorm(sfb, oracle, dtype, m, hidden):
     assert np.abs(y2.float().cpu().numpy() - wy2).max() <= tol * max(1.0, np.abs(wy2).max())
 
 
+@pytest.mark.parametrize("dtype,m,hidden", [("f16", 5000, 768), ("bf16", 4736, 1024), ("f32", 6001, 768),
+                                             ("bf16", 9473, 320), ("f16", 4741, 2048), ("bf16", 20003, 8)])
+def test_layernorm_many_rows(sfb, oracle, dtype, m, hidden):
+    """More rows than the fixed grid has warps (the warps loop), ragged last round, rows narrower than a warp."""
+    x = torch.from_numpy(oracle.fill_normal((m, hidden), 41)).cuda().to(TD[dtype])
+    r = torch.from_numpy(oracle.fill_normal((m, hidden), 42)).cuda().to(TD[dtype])
+    b = torch.from_numpy(oracle.fill_normal((hidden,), 43, 0.02)).cuda()
+    g = torch.from_numpy(1.0 + oracle.fill_normal((hidden,), 44, 0.1)).cuda()
+    be = torch.from_numpy(oracle.fill_normal((hidden,), 45, 0.1)).cuda()
+    y, summed, mean, rstd = sfb.bias_residual_layernorm(x, b, r, g, be, want_sum=True)
+    wy, ws, wm, wr = oracle.bias_residual_layernorm(x.float().cpu().numpy(), b.cpu().numpy(), r.float().cpu().numpy(),
+                                                    g.cpu().numpy(), be.cpu().numpy())
+    tol = 1e-5 if dtype == "f32" else 2e-2
+    np.testing.assert_allclose(mean.cpu().numpy(), wm, atol=1e-5)
+    np.testing.assert_allclose(rstd.cpu().numpy(), wr, rtol=1e-5)
+    assert np.abs(summed.float().cpu().numpy() - ws).max() <= tol * max(1.0, np.abs(ws).max())
+    assert np.abs(y.float().cpu().numpy() - wy).max() <= tol * max(1.0, np.abs(wy).max())
+
+
 def test_layernorm_matches_reference_cpu_golden(sfb, oracle):
     g = np.load(os.path.join(GOLD, "ref_cpu_attention.npz"))
     m, hidden = (int(x) for x in g["ln/shape"])
