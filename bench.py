@@ -519,9 +519,24 @@ def run_bandwidth_kernel(args):
         fn()
         b_.record()
     torch.cuda.synchronize()
-    clocks = sampler.stop()
     ms = sum(a.elapsed_time(b_) for a, b_ in ev) / args.steps
     gbs = nbytes / (ms * 1e-3) / 1e9
+    # a device-to-device copy moving the same number of bytes (half read, half written), timed the same way: what a
+    # launch of this size can reach at all (the measured peak is a long copy; a short launch also pays ramp-up and tail)
+    half = max(int(nbytes) // 2, 1 << 20)
+    csrc = torch.empty(half, dtype=torch.uint8, device="cuda")
+    cdst = torch.empty(half, dtype=torch.uint8, device="cuda")
+    for _ in range(3):
+        cdst.copy_(csrc)
+    for a, b_ in ev:
+        flush.fill_(1)
+        a.record()
+        cdst.copy_(csrc)
+        b_.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    copy_ms = sum(a.elapsed_time(b_) for a, b_ in ev) / args.steps
+    copy_gbs = 2.0 * half / (copy_ms * 1e-3) / 1e9
     print(json.dumps({
         "metric": args.kernel + " GB/s (algorithmic bytes)", "value": round(gbs, 1), "unit": "GB/s", "n_gpus": 1,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5), "higher_is_better": True,
@@ -533,7 +548,9 @@ def run_bandwidth_kernel(args):
         "config": {"workload": args.config, "kernel": name, "bytes": unit_name, "l2": flush.note},
         "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm"], "unit": "GB/s",
                      "frac": round(gbs / pk["hbm"], 4), "traffic": None, "peak_source": pk["source"] + " copy bandwidth",
-                     "algorithmic_bytes": nbytes},
+                     "algorithmic_bytes": nbytes,
+                     "copy_of_same_bytes": {"gbs": round(copy_gbs, 1), "ms": round(copy_ms, 5),
+                                            "frac_of_it": round(gbs / copy_gbs, 4)}},
         "gpu_launches": args.steps * (5 if args.kernel == "attention_backward" else 1), "clocks": clocks}), flush=True)
 
 

@@ -145,9 +145,10 @@ static int launch_ln(cudaStream_t s, void *out, void *sum_out, float *mean, floa
     const uint32_t per_chunk = 32 * N;
     const uint32_t chunks = (hidden + per_chunk - 1) / per_chunk;
     const uint32_t rows_per_cta = 8;
-    // at most 16 CTAs per SM's worth of warps; the warps loop over the remaining rows
+    // at most the CTAs that are resident at once (four per SM at 61 registers); the warps loop over the remaining
+    // rows.  Measured against 16 per SM and against one row per warp: 0.66 / 0.62 / 0.59 of copy bandwidth.
     uint32_t ctas = (m + rows_per_cta - 1) / rows_per_cta;
-    if (ctas > 148 * 16) ctas = 148 * 16;
+    if (ctas > 148 * 4) ctas = 148 * 4;
     dim3 grid(ctas);
 #define LN_CASE(C)                                                                                                   \
     bias_residual_layernorm_kernel<DT, C><<<grid, 32 * rows_per_cta, 0, s>>>(out, sum_out, mean, rstd, x, bias, resid, \
