@@ -64,7 +64,7 @@ class L2Flush:
     def __init__(self, torch, mode="write_read"):
         self.mode = mode
         self.w = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-        self.r = torch.zeros(64 << 20, dtype=torch.int32, device="cuda") if mode != "write" else None
+        self.r = torch.zeros(64 << 20, dtype=torch.float32, device="cuda") if mode != "write" else None   # summed as it is, no cast pass
         self.note = ("256 MB written then 256 MB read between timed steps (cold and clean)" if mode != "write"
                      else "256 MB written between timed steps")
 
