@@ -432,7 +432,7 @@ def run_bandwidth_kernel(args):
         fn = lambda: sfb.csr_attention(q, k, v, rowptr, colidx, 0.125)
         # what the format makes every query row gather: its keys' K and V rows (through L2), plus Q in and O out
         nbytes = int(colidx.numel()) * B * H * 2 * d * q.element_size() + 2 * q.numel() * q.element_size()
-        name, unit_name = "csr_attention_kernel", "K and V rows gathered per query row (L2 traffic, not HBM) + Q read + O written"
+        name, unit_name = "csr_attention_split_kernel", "K and V rows gathered per query row (L2 traffic, not HBM) + Q read + O written"
     elif args.kernel == "embedding":
         tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[cfg["dtype"]]
         vocab, hidden = 30522, H * d
@@ -523,7 +523,7 @@ def run_bandwidth_kernel(args):
     gbs = nbytes / (ms * 1e-3) / 1e9
     # a device-to-device copy moving the same number of bytes (half read, half written), timed the same way: what a
     # launch of this size can reach at all (the measured peak is a long copy; a short launch also pays ramp-up and tail)
-    half = max(int(nbytes) // 2, 1 << 20)
+    half = min(max(int(nbytes) // 2, 1 << 20), 1 << 30)   # bounded: csr_attention's bytes are gathered L2 traffic, not a buffer size
     csrc = torch.empty(half, dtype=torch.uint8, device="cuda")
     cdst = torch.empty(half, dtype=torch.uint8, device="cuda")
     for _ in range(3):
