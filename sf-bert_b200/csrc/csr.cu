@@ -8,7 +8,8 @@
 //                            registers (eight keys per warp and step, partial scores joined by two shuffles, K and V
 //                            pieces requested together); every group of four runs its own online softmax, merged by
 //                            shuffles at the end.  Measured on the BERT-base stride pattern: 5.7 ms, against 9.0 ms with
-//                            two lanes per key and 17.7 ms with one (whole q_i per lane, 8 resident warps per SM).
+//                            two lanes per key, 17.7 ms with one (whole q_i per lane, 8 resident warps per SM), 6.8 ms with eight,
+//                            7.0 ms with four and two keys per group and step.
 // The format has no reuse of K/V between query rows (every row gathers its own keys through L2), which is why the
 // block-sparse path exists; these kernels are the correct, coalesced-per-key version of the prototype, not a fast path.
 #include "attn.cuh"
