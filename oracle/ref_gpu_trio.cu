@@ -10,7 +10,8 @@
  * deliberately not wrapped: nothing here can launch them.
  *
  * The reference implements the two matmuls for block_size 32 only (blocksparse.h:448, :996; any other
- * size launches nothing), so every wrapper refuses another block size instead of returning garbage.
+ * size launches nothing), so their wrappers refuse another block size instead of returning garbage; the
+ * softmax wrapper also takes 64.
  */
 #include "blocksparse.h"
 
@@ -55,9 +56,11 @@ int ref_gpu_masked_softmax(void *stream, const void *nn_lut, const void *mask, c
                            uint ctx_blks, uint lut_heads, uint lut_dim, uint max_lut, uint mask_heads,
                            float scale)
 {
-    int rc = check_common(block_size, blocks, batch_dim, ctx_blks, head_dim, 4);
+    /* the softmax, unlike the two matmuls, is also implemented for block size 64 (blocksparse.h:684-693, uint64 masks) */
+    int rc = check_common(block_size == 64 ? 32 : block_size, blocks, batch_dim, ctx_blks, head_dim, 4);
     if (rc) return rc;
-    if (!max_lut || max_lut > 1024) return -6;        /* keeps the launch at <= 1024 threads, unroll 4..8 */
+    if (1ull * batch_dim * head_dim * blocks * block_size * block_size >= (1ull << 32)) return -4;
+    if (!max_lut || max_lut * block_size > 16 * 1024) return -6;   /* keeps the launch at <= 1024 threads, unroll 4..8 */
     if (y_is_float)
         BlocksparseMaskedSoftmax<float, float2>((CUstream)stream, (const uint2 *)nn_lut, (const uint *)mask,
             (const bhalf *)x, (float *)y, block_size, blocks, batch_dim, head_dim, ctx_blks, lut_heads,

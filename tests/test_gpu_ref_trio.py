@@ -138,3 +138,30 @@ def test_same_mask_on_blocks_of_64_and_32(sfb, trio):
         o = sfb.fused_attention(q.to(dt), k.to(dt), v.to(dt), lay64, scale).float()
         assert float((o - ref.o).abs().max()) <= 2e-2 * float(ref.o.abs().max())
     assert sfb.device_status() == 0
+
+
+@pytest.mark.parametrize("kind,dev,nb", [("stride", ("LAYOUT_STRIDE", dict(p0=4, p1=8)), 32),
+                                          ("local", ("LAYOUT_LOCAL", dict(p0=8, p1=8)), 48),
+                                          ("full", ("LAYOUT_FULL", dict()), 8)])
+def test_reference_gpu_softmax_at_block_64(sfb, trio, kind, dev, nb):
+    """The reference's softmax is also implemented for 64x64 blocks (its matmuls are not): on the block size of the
+    tensor-core kernels the product's stand-alone softmax must agree with it on the same bf16 scores."""
+    import ctypes as C
+    O = trio
+    B, H, d, bs = 2, 4, 64, 64
+    L = nb * bs
+    scale = float(np.float32(1.0 / np.sqrt(d)))
+    lay = sfb.BlockLayout.generate(getattr(sfb, dev[0]), 1, nb, bs, **dev[1])
+    q, k, _ = _qkv(O, (B, L, H, d), 930)
+    s = sfb.bst_sgemm_nt(q.to(torch.bfloat16), k.to(torch.bfloat16), lay, out_dtype=torch.bfloat16)
+    p_ref = torch.empty_like(s)
+    u, vp = C.c_uint32, lambda t: C.c_void_p(t.data_ptr())
+    rc = O.ref_gpu().ref_gpu_masked_softmax(C.c_void_p(torch.cuda.current_stream().cuda_stream), vp(lay.nn_lut), None, vp(s),
+                                            vp(p_ref), C.c_int(0), u(bs), u(lay.blocks), u(B), u(H), u(nb), u(1),
+                                            u(lay.nn_lut_dim), u(lay.nn_max), u(1), C.c_float(scale))
+    assert rc == 0, rc
+    torch.cuda.synchronize()
+    p_ours = sfb.masked_softmax(s, lay, scale, out_dtype=torch.bfloat16).float()
+    p_ref = p_ref.float()
+    _within(p_ref, p_ours, 2e-2 * torch.maximum(p_ref, p_ours) + 1e-6, "probabilities at block 64")
+    assert sfb.device_status() == 0
