@@ -745,8 +745,35 @@ def reference_gpu_sample(cfg, steps, warmup):
     per_launch = [statistics.mean(m[i].elapsed_time(m[i + 1]) for m in ev) for i in range(3)]
     flops = 4.0 * bs * bs * d * kept * B * H
     finite = bool(torch.isfinite(ref.o).all())
+    softmax64 = None
+    if bs == 64:
+        # the reference's softmax (not its matmuls) also exists for 64x64 blocks: the workload's own layout, bf16 in and out
+        import ctypes as C
+        lay64 = O.layout(cfg["oracle"][0], cfg.get("lut_heads", 1), L // bs, **cfg["oracle"][1])
+        luts = O.lut_build(lay64)
+        nn = torch.from_numpy(luts["nn"].view("int32")).cuda()
+        xs = torch.randn(B, H, luts["blocks"], 64, 64, device="cuda", generator=g).to(torch.bfloat16)
+        ys = torch.empty_like(xs)
+        u, vp = C.c_uint32, lambda t: C.c_void_p(t.data_ptr())
+
+        def soft():
+            rc = O.ref_gpu().ref_gpu_masked_softmax(C.c_void_p(torch.cuda.current_stream().cuda_stream), vp(nn), None, vp(xs), vp(ys),
+                                                    C.c_int(0), u(64), u(luts["blocks"]), u(B), u(H), u(L // bs), u(lay64.shape[0]),
+                                                    u(luts["blocks"] + L // bs), u(luts["nn_max"]), u(1), C.c_float(scale))
+            assert rc == 0, rc
+        for _ in range(3):
+            soft()
+        torch.cuda.synchronize()
+        for m_ in ev:
+            m_[0].record()
+            soft()
+            m_[1].record()
+        torch.cuda.synchronize()
+        sm_ms = statistics.mean(m_[0].elapsed_time(m_[1]) for m_ in ev)
+        softmax64 = {"ms": round(sm_ms, 4), "gbs": round(xs.numel() * 4 / (sm_ms * 1e-3) / 1e9, 1),
+                     "what": "reference BlocksparseMaskedSoftmax<bhalf> on the workload's own 64x64 layout, bf16 in and out"}
     return {"value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "launches_per_step": 3,
-            "ms_sddmm_softmax_spmm": [round(x, 4) for x in per_launch], "blocks_32x32_per_head": ref.blocks, "finite": finite,
+            "ms_sddmm_softmax_spmm": [round(x, 4) for x in per_launch], "blocks_32x32_per_head": ref.blocks, "finite": finite, "softmax_block64": softmax64,
             "what": "reference bst_sgemm_nt + BlocksparseMaskedSoftmax<bhalf> + bst_sgemm_xn(NN) on this GPU, fp32 "
                     "activations, bf16 scores, the %s layout split into 32x32 blocks, inputs larger than L2, CUDA events"
                     % cfg["oracle"][0]}
