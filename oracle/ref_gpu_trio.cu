@@ -5,7 +5,8 @@
  * the same B200) and a timed "reference on the same GPU" figure for bench.py's reference arm.
  * Built by oracle/Makefile into oracle/_ref/libsfb_ref_gpu.so.
  *
- * Only these three operators are wrapped.  They launch plain kernels without cross-CTA waits.
+ * Only these operators (forward: SDDMM, softmax, SpMM; backward: softmax gradient, transposed SpMM) are
+ * wrapped.  They launch plain kernels without cross-CTA waits.
  * The reference's fused kernels (fusion_blocksparse.h) spin on global flags without a bound and are
  * deliberately not wrapped: nothing here can launch them.
  *
@@ -87,6 +88,41 @@ int ref_gpu_bst_sgemm_nn(void *stream, const void *nn_lut, const void *a, const 
     magicu64(CEIL_DIV(state_dim, 64), magic, shift);
     bst_sgemm_xn((CUstream)stream, (const uint2 *)nn_lut, (const bhalf *)a, b, c, block_size, blocks,
                  batch_dim, ctx_blks_b, ctx_blks_c, head_dim, state_dim, lut_heads, lut_dim, NN_OP,
+                 magic, shift, max_lut);
+    return launched();
+}
+
+/* blocksparse.h:1164-1227  dx = (dy - sum over the query row of dy*y) * y * scale, <bhalf,bhalf2> as at
+ * no_fusion_test.cu:460 / transformer_attention_optimize.cu:944; block size 32 or 64. */
+int ref_gpu_masked_softmax_grad(void *stream, const void *nn_lut, const void *dy, const void *y, void *dx,
+                                uint block_size, uint blocks, uint batch_dim, uint head_dim, uint ctx_blks,
+                                uint lut_heads, uint lut_dim, uint max_lut, float scale)
+{
+    int rc = check_common(block_size == 64 ? 32 : block_size, blocks, batch_dim, ctx_blks, head_dim, 4);
+    if (rc) return rc;
+    if (1ull * batch_dim * head_dim * blocks * block_size * block_size >= (1ull << 32)) return -4;
+    if (!max_lut || max_lut * block_size > 16 * 1024) return -6;
+    BlocksparseMaskedSoftmaxGrad<bhalf, bhalf2>((CUstream)stream, (const uint2 *)nn_lut, (const bhalf *)dy,
+        (const bhalf *)y, (bhalf *)dx, block_size, blocks, batch_dim, head_dim, ctx_blks, lut_heads, lut_dim,
+        max_lut, scale);
+    return launched();
+}
+
+/* blocksparse.h:965-1014 with TN_OP  C-rows(block column j) = sum over the column's blocks of A[b,h,k]^T .
+ * B-rows(row of k); lut = tn_lut (header per block column), max_lut its longest column.  dV = P^T dO and
+ * dK = dS^T Q at transformer_attention_optimize.cu:924,954. */
+int ref_gpu_bst_sgemm_tn(void *stream, const void *tn_lut, const void *a, const float *b, float *c,
+                         uint block_size, uint blocks, uint batch_dim, uint ctx_blks_b, uint ctx_blks_c,
+                         uint head_dim, uint state_dim, uint lut_heads, uint lut_dim, uint max_lut)
+{
+    int rc = check_common(block_size, blocks, batch_dim, ctx_blks_c, head_dim, state_dim);
+    if (rc) return rc;
+    if (ctx_blks_b != ctx_blks_c) return -5;
+    if (!max_lut || ((max_lut + 1) / 2) * 2 * 8 > 32 * 1024) return -6;
+    uint magic = 0, shift = 0;
+    magicu64(CEIL_DIV(state_dim, 64), magic, shift);
+    bst_sgemm_xn((CUstream)stream, (const uint2 *)tn_lut, (const bhalf *)a, b, c, block_size, blocks,
+                 batch_dim, ctx_blks_b, ctx_blks_c, head_dim, state_dim, lut_heads, lut_dim, TN_OP,
                  magic, shift, max_lut);
     return launched();
 }

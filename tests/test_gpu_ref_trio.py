@@ -165,3 +165,89 @@ def test_reference_gpu_softmax_at_block_64(sfb, trio, kind, dev, nb):
     p_ref = p_ref.float()
     _within(p_ref, p_ours, 2e-2 * torch.maximum(p_ref, p_ours) + 1e-6, "probabilities at block 64")
     assert sfb.device_status() == 0
+
+
+@pytest.mark.parametrize("kind,kw,dev,lut_heads,B,H,L", [
+    ("stride", dict(band=4, every=8), ("LAYOUT_STRIDE", dict(p0=4, p1=8)), 1, 2, 4, 1024),
+    ("fixed", dict(stride=4), ("LAYOUT_FIXED", dict(p0=4)), 4, 1, 4, 512),
+    ("local", dict(left=2, right=1), ("LAYOUT_LOCAL", dict(p0=2, p1=1)), 1, 1, 3, 1024),
+])
+def test_reference_gpu_backward_operators(sfb, trio, kind, kw, dev, lut_heads, B, H, L):
+    """The reference's backward call sequence on this GPU (transformer_attention_optimize.cu:924-964: dV = P^T dO with
+    TN_OP, dP = dO V^T, dS = softmax gradient, dK = dS^T Q, dQ = dS K) beside the product's, each operator fed with the
+    reference's own inputs; block size 32, fp32 activations, bf16 block tensors."""
+    import ctypes as C
+    O = trio
+    d, bs = 64, 32
+    nb = L // bs
+    scale = float(np.float32(1.0 / np.sqrt(d)))
+    layout = O.layout(kind, lut_heads, nb, **kw)
+    q, k, v = _qkv(O, (B, L, H, d), 940)
+    do = torch.from_numpy(O.fill_normal((B, L, H, d), 944)).cuda()
+    ref = O.RefGpuAttention(layout)
+    ref.alloc(q)
+    ref.launch(q, k, v, scale)
+    lay = sfb.BlockLayout.generate(getattr(sfb, dev[0]), lut_heads, nb, bs, **dev[1])
+    tn = O.lut_build_tn(layout)
+    assert np.array_equal(lay.tn_lut.cpu().numpy().view(np.uint32), tn["tn"]) and lay.tn_max == tn["tn_max"]
+    G = O.ref_gpu()
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    u, vp = C.c_uint32, lambda t: C.c_void_p(t.data_ptr())
+    p = ref.p                                                           # bf16 probabilities of the reference's forward
+
+    def ref_tn(a, b):
+        c = torch.empty_like(b)
+        rc = G.ref_gpu_bst_sgemm_tn(st, vp(lay.tn_lut), vp(a), vp(b), vp(c), u(bs), u(lay.blocks), u(B), u(nb), u(nb), u(H), u(d),
+                                    u(lut_heads), u(lay.blocks + nb), u(lay.tn_max))
+        assert rc == 0, rc
+        return c
+
+    def close32(a, b, what):
+        assert float((a - b).abs().max()) <= 1e-4 * float(a.abs().max()) + 1e-5, what
+
+    # dV = P^T dO
+    close32(ref_tn(p, do), sfb.bst_sgemm_tn(p, do, lay), "dV")
+    # dP = dO V^T, rounded to bf16 once on both sides
+    dp_ref = torch.empty_like(ref.s)
+    rc = G.ref_gpu_bst_sgemm_nt(st, vp(ref.nt), vp(do), vp(v), vp(dp_ref), u(bs), u(lay.blocks), u(B), u(nb), u(nb), u(H), u(d),
+                                u(lut_heads), u(lay.blocks))
+    assert rc == 0, rc
+    dp_ours = sfb.bst_sgemm_nt(do, v, lay, out_dtype=torch.bfloat16)
+    a, b_ = dp_ref.float(), dp_ours.float()
+    _within(a, b_, torch.maximum(a.abs(), b_.abs()) * 2.0 ** -7 + 1e-4, "dP")
+    # dS from the reference's dP and P
+    ds_ref = torch.empty_like(p)
+    rc = G.ref_gpu_masked_softmax_grad(st, vp(ref.nn), vp(dp_ref), vp(p), vp(ds_ref), u(bs), u(lay.blocks), u(B), u(H), u(nb),
+                                       u(lut_heads), u(lay.blocks + nb), u(lay.nn_max), C.c_float(scale))
+    assert rc == 0, rc
+    ds_ours = sfb.masked_softmax_grad(dp_ref, p, lay, scale)
+    a, b_ = ds_ref.float(), ds_ours.float()
+    _within(a, b_, torch.maximum(a.abs(), b_.abs()) * 2.0 ** -7 + 1e-5 * float(a.abs().max()) + 1e-7, "dS")
+    # dK = dS^T Q and dQ = dS K from the reference's dS
+    close32(ref_tn(ds_ref, q), sfb.bst_sgemm_tn(ds_ref, q, lay), "dK")
+    dq_ref = torch.empty_like(q)
+    rc = G.ref_gpu_bst_sgemm_nn(st, vp(ref.nn), vp(ds_ref), vp(k), vp(dq_ref), u(bs), u(lay.blocks), u(B), u(nb), u(nb), u(H), u(d),
+                                u(lut_heads), u(lay.blocks + nb), u(lay.nn_max))
+    assert rc == 0, rc
+    close32(dq_ref, sfb.bst_sgemm_xn(ds_ref, k, lay), "dQ")
+    torch.cuda.synchronize()
+    assert sfb.device_status() == 0
+
+
+def test_reference_gpu_softmax_grad_at_block_64(sfb, trio):
+    import ctypes as C
+    O = trio
+    B, H, nb, bs = 2, 4, 32, 64
+    lay = sfb.BlockLayout.generate(sfb.LAYOUT_STRIDE, 1, nb, bs, p0=4, p1=8)
+    g = torch.Generator(device="cuda").manual_seed(950)
+    y = torch.rand(B, H, lay.blocks, bs, bs, device="cuda", generator=g).mul_(0.01).to(torch.bfloat16)
+    dy = torch.randn(B, H, lay.blocks, bs, bs, device="cuda", generator=g).to(torch.bfloat16)
+    dx_ref = torch.empty_like(y)
+    u, vp = C.c_uint32, lambda t: C.c_void_p(t.data_ptr())
+    rc = O.ref_gpu().ref_gpu_masked_softmax_grad(C.c_void_p(torch.cuda.current_stream().cuda_stream), vp(lay.nn_lut), vp(dy), vp(y),
+                                                 vp(dx_ref), u(bs), u(lay.blocks), u(B), u(H), u(nb), u(1), u(lay.nn_lut_dim),
+                                                 u(lay.nn_max), C.c_float(0.125))
+    assert rc == 0, rc
+    torch.cuda.synchronize()
+    a, b_ = dx_ref.float(), sfb.masked_softmax_grad(dy, y, lay, 0.125).float()
+    _within(a, b_, torch.maximum(a.abs(), b_.abs()) * 2.0 ** -7 + 1e-5 * float(a.abs().max()) + 1e-7, "dS at block 64")
