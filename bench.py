@@ -745,6 +745,39 @@ def reference_gpu_sample(cfg, steps, warmup):
     per_launch = [statistics.mean(m[i].elapsed_time(m[i + 1]) for m in ev) for i in range(3)]
     flops = 4.0 * bs * bs * d * kept * B * H
     finite = bool(torch.isfinite(ref.o).all())
+    # the reference's five backward calls (transformer_attention_optimize.cu:924-964) on the same 32x32 layout, from the
+    # probabilities its forward just wrote: dV = P^T dO, dP = dO V^T, dS = softmax gradient, dK = dS^T Q, dQ = dS K
+    import ctypes as C
+    G_ = O.ref_gpu()
+    tn = O.lut_build_tn(lay)
+    tn_lut = torch.from_numpy(tn["tn"].view("int32")).cuda()
+    do = torch.randn(B, L, H, d, device="cuda", generator=g)
+    dv, dk, dq = (torch.empty_like(q) for _ in range(3))
+    dp, ds = torch.empty_like(ref.s), torch.empty_like(ref.s)
+    nb32, heads32 = ref.nb, ref.heads
+    u, vp = C.c_uint32, lambda t: C.c_void_p(t.data_ptr())
+
+    def backward(marks=None):
+        st_ = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        common = (u(32), u(ref.blocks), u(B), u(nb32), u(nb32), u(H), u(d), u(heads32))
+        rcs = []
+        if marks: marks[0].record()
+        rcs.append(G_.ref_gpu_bst_sgemm_tn(st_, vp(tn_lut), vp(ref.p), vp(do), vp(dv), *common, u(ref.blocks + nb32), u(tn["tn_max"])))
+        rcs.append(G_.ref_gpu_bst_sgemm_nt(st_, vp(ref.nt), vp(do), vp(v), vp(dp), *common, u(ref.blocks)))
+        rcs.append(G_.ref_gpu_masked_softmax_grad(st_, vp(ref.nn), vp(dp), vp(ref.p), vp(ds), u(32), u(ref.blocks), u(B), u(H), u(nb32),
+                                                  u(heads32), u(ref.blocks + nb32), u(ref.nn_max), C.c_float(scale)))
+        rcs.append(G_.ref_gpu_bst_sgemm_tn(st_, vp(tn_lut), vp(ds), vp(q), vp(dk), *common, u(ref.blocks + nb32), u(tn["tn_max"])))
+        rcs.append(G_.ref_gpu_bst_sgemm_nn(st_, vp(ref.nn), vp(ds), vp(k), vp(dq), *common, u(ref.blocks + nb32), u(ref.nn_max)))
+        if marks: marks[1].record()
+        assert not any(rcs), rcs
+    for _ in range(3):
+        backward()
+    torch.cuda.synchronize()
+    for m_ in ev:
+        backward(m_)
+    torch.cuda.synchronize()
+    bwd_ms = statistics.mean(m_[0].elapsed_time(m_[1]) for m_ in ev)
+    bwd_finite = bool(torch.isfinite(dq).all() and torch.isfinite(dk).all() and torch.isfinite(dv).all())
     softmax64 = None
     if bs == 64:
         # the reference's softmax (not its matmuls) also exists for 64x64 blocks: the workload's own layout, bf16 in and out
@@ -774,6 +807,9 @@ def reference_gpu_sample(cfg, steps, warmup):
                      "what": "reference BlocksparseMaskedSoftmax<bhalf> on the workload's own 64x64 layout, bf16 in and out"}
     return {"value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "launches_per_step": 3,
             "ms_sddmm_softmax_spmm": [round(x, 4) for x in per_launch], "blocks_32x32_per_head": ref.blocks, "finite": finite, "softmax_block64": softmax64,
+            "backward": {"ms_per_step": round(bwd_ms, 4), "launches_per_step": 5, "finite": bwd_finite,
+                         "what": "reference bst_sgemm_xn(TN) + bst_sgemm_nt + BlocksparseMaskedSoftmaxGrad<bhalf> + bst_sgemm_xn(TN) + "
+                                 "bst_sgemm_xn(NN) on the same 32x32 layout, fp32 activations, bf16 block tensors"},
             "what": "reference bst_sgemm_nt + BlocksparseMaskedSoftmax<bhalf> + bst_sgemm_xn(NN) on this GPU, fp32 "
                     "activations, bf16 scores, the %s layout split into 32x32 blocks, inputs larger than L2, CUDA events"
                     % cfg["oracle"][0]}
