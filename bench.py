@@ -534,9 +534,18 @@ def run_bandwidth_kernel(args):
         cdst.copy_(csrc)
         b_.record()
     torch.cuda.synchronize()
-    clocks = sampler.stop()
     copy_ms = sum(a.elapsed_time(b_) for a, b_ in ev) / args.steps
     copy_gbs = 2.0 * half / (copy_ms * 1e-3) / 1e9
+    # and a pure write of as many bytes as the copy wrote: the ceiling of a kernel that mostly writes (SDDMM, fused_p)
+    for a, b_ in ev:
+        flush.fill_(1)
+        a.record()
+        cdst.fill_(3)
+        b_.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    fill_ms = sum(a.elapsed_time(b_) for a, b_ in ev) / args.steps
+    fill_gbs = half / (fill_ms * 1e-3) / 1e9
     print(json.dumps({
         "metric": args.kernel + " GB/s (algorithmic bytes)", "value": round(gbs, 1), "unit": "GB/s", "n_gpus": 1,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5), "higher_is_better": True,
@@ -550,7 +559,8 @@ def run_bandwidth_kernel(args):
                      "frac": round(gbs / pk["hbm"], 4), "traffic": None, "peak_source": pk["source"] + " copy bandwidth",
                      "algorithmic_bytes": nbytes,
                      "copy_of_same_bytes": {"gbs": round(copy_gbs, 1), "ms": round(copy_ms, 5),
-                                            "frac_of_it": round(gbs / copy_gbs, 4)}},
+                                            "frac_of_it": round(gbs / copy_gbs, 4)},
+                     "fill_gbs": round(fill_gbs, 1)},
         "gpu_launches": args.steps * (5 if args.kernel == "attention_backward" else 1), "clocks": clocks}), flush=True)
 
 

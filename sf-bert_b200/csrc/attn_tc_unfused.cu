@@ -33,13 +33,16 @@ struct UParams {
     float scale;               // sddmm, gradient mode
 };
 
-constexpr int kSdStages = 3;
+constexpr int kSdStages = 4;
+constexpr uint32_t kChunk = 32;                 // consecutive LUT entries one CTA takes
 struct SdShared {
-    uint64_t in_full[kSdStages], in_empty[kSdStages], s_full[2], s_empty[2], drained;
+    uint64_t in_full[kSdStages], in_empty[kSdStages], s_full[2], s_empty[2], drained, q_full[2], q_empty[2];
     uint32_t tmem_base, abort_flag;
+    uint2 ent[kChunk];                          // this CTA's LUT entries
 };
-constexpr size_t kSddmmSmem = 1024 + kSdStages * 2 * kTileBytes + 2 * kTileBytes /* output staging */ + sizeof(SdShared);
-constexpr size_t kSddmmGradSmem = 1024 + kSdStages * 3 * kTileBytes + 2 * kTileBytes + sizeof(SdShared);
+// two query-row tiles (kept while consecutive blocks share their block-row), the key stages, two output staging tiles
+constexpr size_t kSddmmSmem = 1024 + 2 * kTileBytes + kSdStages * 1 * kTileBytes + 2 * kTileBytes + sizeof(SdShared);
+constexpr size_t kSddmmGradSmem = 1024 + 2 * kTileBytes + kSdStages * 2 * kTileBytes + 2 * kTileBytes + sizeof(SdShared);
 constexpr size_t kSpmmSmem = 1024 + kUStages * (kQBytes + kTileBytes) + sizeof(UShared);
 
 __device__ __forceinline__ void store_row16(void *dst_base, size_t elem_off, const uint32_t (&v)[16], int out_dtype, int c0)
@@ -64,27 +67,27 @@ __device__ __forceinline__ void store_row16(void *dst_base, size_t elem_off, con
 
 // ---- SDDMM ----------------------------------------------------------------------------------------
 // The operator only receives the nt_lut (one (row, column) pair per kept block, in any order), so a CTA takes
-// a run of kChunk consecutive blocks.  Per block one stage holds the 64 query rows followed by the 64 key rows;
-// the M=128 MMA reads the stage as its A operand, so accumulator lanes 0-63 hold Q.K^T and lanes 64-127 a
-// by-product (K.K^T) that is never read -- the operator is bound by the 8 KB of S it writes per block, not by
-// tensor work.  warp 0: TMA; warp 1: MMA; warps 4-5 and 8-9: TMEM lanes 0-63 -> global, half a score row (32
+// a run of kChunk consecutive blocks.  The 64 query rows sit in one of two tiles that are loaded only when the
+// block-row changes (the LUT is in row-major scan order, so a run shares its rows: without this every block pulled
+// 16 KB through L2 for the 8 KB it writes); per block a stage holds the 64 key rows.  The M=128 MMA reads the query
+// tile and whatever follows it as its A operand, so accumulator lanes 0-63 hold Q.K^T and lanes 64-127 a by-product
+// that is never read -- the operator is bound by the bytes it moves, not by tensor work.  warp 0: TMA; warp 1: MMA; warps 4-5 and 8-9: TMEM lanes 0-63 -> global, half a score row (32
 // columns) per thread.
 //
 // GRAD: the same kernel as the first half of a fused backward.  With a = dO and b = V the accumulator is dP = dO.V^T;
 // a third tile per stage brings the block of P, and the drain writes dS = P * (dP - delta) * scale, where
 // delta[row] = sum over the head of dO * O.  That row constant equals the sum over the row's blocks of dP * P which the
 // unfused softmax gradient has to reduce first, so dS needs no pass over the row and dP never reaches memory.
-constexpr uint32_t kChunk = 32;
-
 template <bool GRAD>
 __global__ void __launch_bounds__(320, GRAD ? 2 : 4)
 sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                 const __grid_constant__ CUtensorMap omap, const __grid_constant__ CUtensorMap pmap, const UParams p)
 {
-    constexpr uint32_t kStage = (GRAD ? 3 : 2) * kTileBytes;
+    constexpr uint32_t kStage = (GRAD ? 2 : 1) * kTileBytes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t *tiles = smem;                                   // stage s: Q rows (8 KB), K rows (8 KB), GRAD: the block of P (8 KB)
+    uint8_t *q_tiles = smem;                                 // two tiles of query rows
+    uint8_t *tiles = q_tiles + 2 * kTileBytes;               // stage s: K rows (8 KB), GRAD: the block of P (8 KB)
     uint8_t *stage_out = tiles + kSdStages * kStage;         // two 8 KB tiles of 16-bit scores on their way out
     SdShared *st = (SdShared *)(stage_out + 2 * kTileBytes);
 
@@ -101,10 +104,12 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
         // GRAD: a stage is free when the MMA has read Q and K AND the 128 drain threads have read P
         for (int s = 0; s < kSdStages; s++) { mbar_init(&st->in_full[s], 1); mbar_init(&st->in_empty[s], GRAD ? 129 : 1); }
         for (int s = 0; s < 2; s++) { mbar_init(&st->s_full[s], 1); mbar_init(&st->s_empty[s], 128); }
+        for (int s = 0; s < 2; s++) { mbar_init(&st->q_full[s], 1); mbar_init(&st->q_empty[s], 1); }
         mbar_init(&st->drained, 1);
         st->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (threadIdx.x >= 64 && threadIdx.x < 64 + T) st->ent[threadIdx.x - 64] = lut[threadIdx.x - 64];
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&st->tmem_base)), "r"(128u) : "memory");
@@ -118,37 +123,53 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
+            uint32_t n_q = 0;                                  // query tiles requested so far
             for (uint32_t t = 0; t < T; t++) {
                 const uint32_t s = t % kSdStages;
                 if (t >= kSdStages && !mbar_wait(&st->in_empty[s], ((t / kSdStages) - 1) & 1, abort_flag, 21)) break;
-                const uint2 ent = lut[t];
+                const uint2 ent = st->ent[t];
                 if (ent.x >= p.nb || ent.y >= p.nb) {   // a LUT entry outside the block grid: report, do not fetch
                     st->abort_flag = 1;
                     atomicCAS(&g_status, 0u, (20u << 24) | (blockIdx.x & 0xffffffu));
                     break;
                 }
+                if (t == 0 || ent.x != st->ent[t - 1].x) {
+                    // a new block-row: its query rows go into the tile the row before last used, once the MMAs that read it are done
+                    const uint32_t qi = n_q & 1;
+                    if (n_q >= 2 && !mbar_wait(&st->q_empty[qi], ((n_q >> 1) - 1) & 1, abort_flag, 27)) break;
+                    mbar_expect_tx(&st->q_full[qi], kTileBytes);
+                    tma_load_2d(smem_u32(q_tiles + qi * kTileBytes), &qmap, &st->q_full[qi], xq, (int32_t)(b * L + ent.x * 64));
+                    n_q++;
+                }
                 mbar_expect_tx(&st->in_full[s], kStage);
-                tma_load_2d(smem_u32(tiles + s * kStage), &qmap, &st->in_full[s], xq, (int32_t)(b * L + ent.x * 64));
-                tma_load_2d(smem_u32(tiles + s * kStage + kTileBytes), &kmap, &st->in_full[s], xq, (int32_t)(b * L + ent.y * 64));
+                tma_load_2d(smem_u32(tiles + s * kStage), &kmap, &st->in_full[s], xq, (int32_t)(b * L + ent.y * 64));
                 if (GRAD)
-                    tma_load_2d(smem_u32(tiles + s * kStage + 2 * kTileBytes), &pmap, &st->in_full[s], 0,
+                    tma_load_2d(smem_u32(tiles + s * kStage + kTileBytes), &pmap, &st->in_full[s], 0,
                                 (int32_t)((((size_t)b * p.H + h) * p.blocks + k0 + t) * 64));
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc(fmt, fmt, 128, 64, 0);
+            uint32_t n_q = 0, qi = 0;
             for (uint32_t t = 0; t < T; t++) {
                 const uint32_t s = t % kSdStages;
+                const uint32_t row = st->ent[t].x;
+                if (t == 0 || row != st->ent[t - 1].x) {
+                    qi = n_q & 1;
+                    if (!mbar_wait(&st->q_full[qi], (n_q >> 1) & 1, abort_flag, 28)) break;
+                    n_q++;
+                }
                 if (!mbar_wait(&st->in_full[s], (t / kSdStages) & 1, abort_flag, 23)) break;
                 if (t >= 2 && !mbar_wait(&st->s_empty[t & 1], ((t >> 1) - 1) & 1, abort_flag, 24)) break;
                 tcgen05_fence_after();
-                const uint64_t a_desc = smem_desc_sw128(smem_u32(tiles + s * kStage));
-                const uint64_t b_desc = smem_desc_sw128(smem_u32(tiles + s * kStage + kTileBytes));
+                const uint64_t a_desc = smem_desc_sw128(smem_u32(q_tiles + qi * kTileBytes));
+                const uint64_t b_desc = smem_desc_sw128(smem_u32(tiles + s * kStage));
 #pragma unroll
                 for (uint32_t kk = 0; kk < 4; kk++) umma_f16(tmem + 64 * (t & 1), a_desc + 2 * kk, b_desc + 2 * kk, idesc, kk);
                 umma_commit(&st->s_full[t & 1]);
                 umma_commit(&st->in_empty[s]);
+                if (t + 1 == T || st->ent[t + 1].x != row) umma_commit(&st->q_empty[qi]);   // last block of this block-row
             }
         }
     } else if (warp == 4 || warp == 5 || warp == 8 || warp == 9) {
@@ -181,13 +202,13 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
                 asm volatile("bar.sync 4, 128;" ::: "memory");
                 uint8_t *orow = stage_out + (t & 1) * kTileBytes + r * 128;
                 const uint32_t sg = t % kSdStages;
-                const uint8_t *prow = tiles + sg * kStage + 2 * kTileBytes + r * 128;
+                const uint8_t *prow = tiles + sg * kStage + kTileBytes + r * 128;
                 float dl = 0.f;
                 bool p_ok = true;
                 if (GRAD) {
                     // P arrived with the same transaction barrier the MMA waited for; observing it here makes the tile visible
                     p_ok = mbar_wait_warp(&st->in_full[sg], (t / kSdStages) & 1, abort_flag, 26);
-                    dl = __ldg(p.delta + ((size_t)b * L + (size_t)lut[t].x * 64 + r) * p.H + h);
+                    dl = __ldg(p.delta + ((size_t)b * L + (size_t)st->ent[t].x * 64 + r) * p.H + h);
                 }
 #pragma unroll
                 for (int c0 = cbase; c0 < cbase + 32; c0 += 16) {
