@@ -33,16 +33,16 @@ struct UParams {
     float scale;               // sddmm, gradient mode
 };
 
-constexpr int kSdStages = 4;
+constexpr int kSdStagesMax = 5;                 // key stages: five without the P tile, four with it (shared memory per CTA)
 constexpr uint32_t kChunk = 32;                 // consecutive LUT entries one CTA takes
 struct SdShared {
-    uint64_t in_full[kSdStages], in_empty[kSdStages], s_full[2], s_empty[2], drained, q_full[2], q_empty[2];
+    uint64_t in_full[kSdStagesMax], in_empty[kSdStagesMax], s_full[2], s_empty[2], drained, q_full[2], q_empty[2];
     uint32_t tmem_base, abort_flag;
     uint2 ent[kChunk];                          // this CTA's LUT entries
 };
 // two query-row tiles (kept while consecutive blocks share their block-row), the key stages, two output staging tiles
-constexpr size_t kSddmmSmem = 1024 + 2 * kTileBytes + kSdStages * 1 * kTileBytes + 2 * kTileBytes + sizeof(SdShared);
-constexpr size_t kSddmmGradSmem = 1024 + 2 * kTileBytes + kSdStages * 2 * kTileBytes + 2 * kTileBytes + sizeof(SdShared);
+constexpr size_t kSddmmSmem = 1024 + 2 * kTileBytes + 5 * 1 * kTileBytes + 2 * kTileBytes + sizeof(SdShared);
+constexpr size_t kSddmmGradSmem = 1024 + 2 * kTileBytes + 4 * 2 * kTileBytes + 2 * kTileBytes + sizeof(SdShared);
 constexpr size_t kSpmmSmem = 1024 + kUStages * (kQBytes + kTileBytes) + sizeof(UShared);
 
 __device__ __forceinline__ void store_row16(void *dst_base, size_t elem_off, const uint32_t (&v)[16], int out_dtype, int c0)
@@ -84,6 +84,7 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
                 const __grid_constant__ CUtensorMap omap, const __grid_constant__ CUtensorMap pmap, const UParams p)
 {
     constexpr uint32_t kStage = (GRAD ? 2 : 1) * kTileBytes;
+    constexpr uint32_t kSdStages = GRAD ? 4 : 5;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *q_tiles = smem;                                 // two tiles of query rows
@@ -102,7 +103,7 @@ sddmm_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
 
     if (threadIdx.x == 0) {
         // GRAD: a stage is free when the MMA has read Q and K AND the 128 drain threads have read P
-        for (int s = 0; s < kSdStages; s++) { mbar_init(&st->in_full[s], 1); mbar_init(&st->in_empty[s], GRAD ? 129 : 1); }
+        for (uint32_t s = 0; s < kSdStages; s++) { mbar_init(&st->in_full[s], 1); mbar_init(&st->in_empty[s], GRAD ? 129 : 1); }
         for (int s = 0; s < 2; s++) { mbar_init(&st->s_full[s], 1); mbar_init(&st->s_empty[s], 128); }
         for (int s = 0; s < 2; s++) { mbar_init(&st->q_full[s], 1); mbar_init(&st->q_empty[s], 1); }
         mbar_init(&st->drained, 1);
