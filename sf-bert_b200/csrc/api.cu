@@ -29,6 +29,23 @@ int check_launch(const char *what)
     return 0;
 }
 
+int current_device()
+{
+    int dev = -1;
+    return cudaGetDevice(&dev) == cudaSuccess ? dev : -1;
+}
+
+int device_sm_count(int dev)
+{
+    static std::atomic<int> cache[64];
+    if (dev < 0 || dev >= 64) return 0;
+    int v = cache[dev].load(std::memory_order_relaxed);
+    if (v > 0) return v;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 0;
+    cache[dev].store(v, std::memory_order_relaxed);
+    return v;
+}
+
 }  // namespace sfb
 
 extern "C" const char *sfb_last_error(void) { return sfb::error_buffer(); }

@@ -503,6 +503,8 @@ fused_p_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 
             const UnionEntry ent = st->entries[t % T];
             const bool mine = (ent.flags >> half) & 1;
+            // the row sum is final once sweep 1 is over, whichever block-row owns the union's first and last entries
+            if (t == T) inv = l > 0.f ? 1.f / l : 0.f;
             if (!mine) continue;
             if (p.mask) {
                 const uint64_t w = p.mask[(size_t)h * p.mask_stride + (size_t)ent.blk[half] * 64 + (r & 63)];
@@ -526,10 +528,8 @@ fused_p_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                     for (int c = 0; c < 64; c++) ps4[c & 3] += ex2_approx(fmaf(__uint_as_float(sr[c]), sl, -m));
                     l += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
                 }
-                if (t + 1 == T) inv = l > 0.f ? 1.f / l : 0.f;
             } else {
                 // sweep 2: probabilities out
-                if (t == T) inv = l > 0.f ? 1.f / l : 0.f;
                 const float neg_m = m > -INFINITY ? -m : 0.f;
                 const size_t off = ((((size_t)b * p.H + h) * p.blocks + ent.blk[half]) * 64 + (r & 63)) * 64;
 #pragma unroll
@@ -607,12 +607,13 @@ int tc_sddmm(cudaStream_t s, const void *nt_lut, const void *a, const void *b, v
     if (make_p_map(&om, c, (uint64_t)p.B * p.H * p.blocks * 64, c_dtype != SFB_F16)) return 1;
     SFB_REQUIRE((uint64_t)p.B * p.H * p.blocks * 64 < (1ull << 31), "sfb_bst_sgemm_nt: too many blocks for one launch");
     UParams prm = {(const uint2 *)nt_lut, c, p.B, p.H, p.nb_a, p.blocks, p.lut_stride, c_dtype, is_bf16, 0};
-    static bool configured = false;
-    if (!configured) {
+    static DeviceOnce once;
+    const int dev = current_device();
+    if (!once.done(dev)) {
         if (cudaFuncSetAttribute(sddmm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSddmmSmem) != cudaSuccess ||
             cudaFuncSetAttribute(sddmm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSddmmGradSmem) != cudaSuccess)
             return fail("sfb_bst_sgemm_nt: cannot reserve %zu bytes of shared memory", kSddmmGradSmem);
-        configured = true;
+        once.mark(dev);
     }
     sddmm_tc_kernel<false><<<dim3((p.blocks + kChunk - 1) / kChunk, p.B, p.H), 320, kSddmmSmem, s>>>(qm, km, om, om, prm);
     return check_launch("sfb_bst_sgemm_nt");
@@ -633,11 +634,12 @@ int tc_sddmm_softmax_grad(cudaStream_t s, const void *nt_lut, const void *dout, 
         make_p_map(&pm, pblk, prow, is_bf16))
         return 1;
     UParams prm = {(const uint2 *)nt_lut, ds, p.B, p.H, p.nb_a, p.blocks, p.lut_stride, dtype, is_bf16, 0, 0, delta, scale};
-    static bool configured = false;
-    if (!configured) {
+    static DeviceOnce once;
+    const int dev = current_device();
+    if (!once.done(dev)) {
         if (cudaFuncSetAttribute(sddmm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSddmmGradSmem) != cudaSuccess)
             return fail("sfb_fused_sddmm_softmax_grad: cannot reserve %zu bytes of shared memory", kSddmmGradSmem);
-        configured = true;
+        once.mark(dev);
     }
     sddmm_tc_kernel<true><<<dim3((p.blocks + kChunk - 1) / kChunk, p.B, p.H), 320, kSddmmGradSmem, s>>>(qm, km, om, pm, prm);
     return check_launch("sfb_fused_sddmm_softmax_grad");
@@ -661,11 +663,12 @@ int tc_fused_p(cudaStream_t s, const void *nn_lut, const void *a, const void *b,
     if (make_map(&qm, a, rows, p.H, is_bf16, 128) || make_map(&km, b, rows, p.H, is_bf16, 64)) return 1;
     FpParams prm = {(const uint2 *)nn_lut, (const uint64_t *)mask, y, p.B, p.H, p.nb_a, p.blocks, p.lut_stride, p.mask_stride,
                     scale * 1.4426950408889634f, y_dtype, is_bf16};
-    static bool configured = false;
-    if (!configured) {
+    static DeviceOnce once;
+    const int dev = current_device();
+    if (!once.done(dev)) {
         if (cudaFuncSetAttribute(fused_p_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFpSmem) != cudaSuccess)
             return fail("sfb_fused_sddmm_softmax: cannot reserve %zu bytes of shared memory", kFpSmem);
-        configured = true;
+        once.mark(dev);
     }
     fused_p_tc_kernel<<<dim3((p.nb_a + 1) / 2, p.B, p.H), 192, kFpSmem, s>>>(qm, km, prm);
     return check_launch("sfb_fused_sddmm_softmax");
@@ -685,11 +688,12 @@ int tc_spmm(cudaStream_t s, const void *nn_lut, const void *a, const void *b, vo
     CUtensorMap pm, vm;
     if (make_p_map(&pm, a, prow, is_bf16) || make_map(&vm, b, (uint64_t)p.B * p.nb_b * 64, p.H, is_bf16, 64)) return 1;
     UParams prm = {(const uint2 *)nn_lut, c, p.B, p.H, p.nb_a, p.blocks, p.lut_stride, dtype, is_bf16, (uint32_t)prow, trans ? 1 : 0};
-    static bool configured = false;
-    if (!configured) {
+    static DeviceOnce once;
+    const int dev = current_device();
+    if (!once.done(dev)) {
         if (cudaFuncSetAttribute(spmm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSpmmSmem) != cudaSuccess)
             return fail("sfb_bst_sgemm_xn: cannot reserve %zu bytes of shared memory", kSpmmSmem);
-        configured = true;
+        once.mark(dev);
     }
     spmm_tc_kernel<<<dim3((p.nb_a + 1) / 2, p.B, p.H), 192, kSpmmSmem, s>>>(pm, vm, prm);
     return check_launch("sfb_bst_sgemm_xn");

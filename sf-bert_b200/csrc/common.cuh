@@ -6,6 +6,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdarg.h>
+#include <atomic>
 
 #include "../../include/sfbert_b200.h"
 
@@ -23,6 +24,17 @@ int check_launch(const char *what);
     } while (0)
 
 static inline cudaStream_t as_stream(sfb_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// ---- host: set-up that is per DEVICE (function attributes, SM count), not per process ----------
+// A launcher keeps one DeviceOnce per kernel family:  if (!once.done(dev)) { ...set attributes...; once.mark(dev); }
+// Two threads may both run the set-up of a device; setting an attribute twice is harmless.
+int current_device();                 // ordinal of the calling thread's current device, -1 on failure
+int device_sm_count(int dev);         // cached per device, 0 on failure
+struct DeviceOnce {
+    std::atomic<uint64_t> mask{0};
+    bool done(int dev) const { return dev >= 0 && dev < 64 && ((mask.load(std::memory_order_acquire) >> dev) & 1u); }
+    void mark(int dev) { if (dev >= 0 && dev < 64) mask.fetch_or(1ull << dev, std::memory_order_release); }
+};
 
 // ---- device: element conversion -------------------------------------------------------------
 // fp32 -> bf16 bits the way the reference stores S and P (ew_op_gpu.h:241-253): add half a bf16

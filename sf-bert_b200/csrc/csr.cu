@@ -286,9 +286,7 @@ int csr_attention(cudaStream_t s, const int32_t *rowptr, const int32_t *colidx, 
     if (bad) cudaMemsetAsync(bad, 0, sizeof(uint32_t), s);
     const dim3 grid((L + 3) / 4, B, H);
     const float sl = scale * 1.4426950408889634f;
-    // four lanes per key; SFB_CSR_LANES=1 or 2 selects the other kernels (for comparison)
-    const char *force = getenv("SFB_CSR_LANES");
-    const int lanes = force && (force[0] == '1' || force[0] == '2') ? force[0] - '0' : 4;
+    const int lanes = 4;   // lanes per key; the one- and two-lane kernels are kept for comparison
 #define CSR_LAUNCH(DTV, DV)                                                                                            \
     do {                                                                                                               \
         if (lanes == 4) csr_attention_split_kernel<DTV, DV, 4><<<grid, 128, 0, s>>>(rowptr, colidx, q, k, v, o, L, H, sl, bad); \

@@ -249,20 +249,19 @@ int tc_linear(cudaStream_t s, void *out, const void *x, const void *w, const flo
     CUtensorMap am, bm;
     if (make_map_2d(&am, x, m, k, is_bf16, kGBM)) return 1;
     if (w_transposed ? make_map_2d(&bm, w, n, k, is_bf16, kGBN) : make_map_2d(&bm, w, k, n, is_bf16, kGBK)) return 1;
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0, v = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
-            return fail("sfb_linear: cannot read the SM count");
+    static DeviceOnce once;
+    const int dev = current_device();
+    const int sms = device_sm_count(dev);
+    if (sms <= 0) return fail("sfb_linear: cannot read the SM count");
+    if (!once.done(dev)) {
         if (cudaFuncSetAttribute(linear_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GCfg<1>::smem) != cudaSuccess ||
             cudaFuncSetAttribute(linear_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GCfg<2>::smem) != cudaSuccess)
             return fail("sfb_linear: cannot reserve %zu bytes of shared memory", GCfg<1>::smem);
-        sms = v;
+        once.mark(dev);
     }
     // long-k products are bound by what travels from L2: 256-row tiles, as long as they still fill the SMs twice over
     const uint32_t tiles_n = (n + kGBN - 1) / kGBN;
-    int mt = (k >= 2048 && (uint64_t)((m + 255) / 256) * tiles_n >= 2ull * sms) ? 2 : 1;
-    if (const char *force = getenv("SFB_LINEAR_MT")) mt = force[0] == '2' ? 2 : 1;
+    const int mt = (k >= 2048 && (uint64_t)((m + 255) / 256) * tiles_n >= 2ull * sms) ? 2 : 1;
     GParams prm = {out, bias, m, n, k, (m + mt * kGBM - 1) / (mt * kGBM), tiles_n, is_bf16, act, w_transposed ? 1 : 0};
     const uint32_t tiles = prm.tiles_m * prm.tiles_n;
     const uint32_t grid = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;

@@ -11,7 +11,10 @@ namespace tc {
 constexpr int kMaxUnion = 512;                  // key blocks a row pair may touch
 constexpr uint32_t kTileBytes = 64 * 64 * 2;    // one 64x64 16-bit tile
 constexpr uint32_t kQBytes = 128 * 64 * 2;
-constexpr uint32_t kWaitLimit = 1u << 24;
+#ifndef SFB_WAIT_LIMIT_LOG2
+#define SFB_WAIT_LIMIT_LOG2 24
+#endif
+constexpr uint32_t kWaitLimit = 1u << SFB_WAIT_LIMIT_LOG2;   // polls before a bounded wait gives up
 
 struct UnionEntry {
     uint32_t col;      // key block column
@@ -47,6 +50,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// one look at the barrier that never suspends the thread (for a thread that watches several barriers)
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// the same with a suspend-time hint: the thread sleeps in the barrier unit until the phase completes or about
+// `ns` nanoseconds have passed, instead of coming back at once and polling again (polling warps take issue slots
+// and shared-memory bandwidth from the warps that do the work)
+__device__ __forceinline__ bool mbar_try_wait_sleep(uint64_t *bar, uint32_t parity, uint32_t ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
         : "memory");
     return ok != 0;
 }

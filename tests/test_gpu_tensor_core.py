@@ -229,6 +229,39 @@ def test_fused_sddmm_softmax_on_tensor_cores(sfb, oracle, dtype, out, pred, ctx)
     np.testing.assert_allclose(sums, 1.0, atol=1e-3 if out == "f32" else 2e-2)
 
 
+@pytest.mark.parametrize("case", ["lower_interior_subset", "upper_empty", "lower_in_the_middle_only"])
+@pytest.mark.parametrize("op", ["probabilities", "attention"])
+def test_row_pair_ownership_of_union_entries(sfb, oracle, case, op):
+    """A block-row of a pair that owns neither the first nor the last entry of the pair's union of key blocks
+    (or no entry at all) still gets its softmax denominator: the tensor-core kernels walk the union, not the row."""
+    nb, B, H, d = 4, 2, 2, 64
+    layout = np.zeros((1, nb, nb), np.uint8)
+    if case == "lower_interior_subset":
+        rows = {0: (0, 1, 2), 1: (1,), 2: (0, 3), 3: (2,)}
+    elif case == "upper_empty":
+        rows = {0: (), 1: (0, 2), 2: (1,), 3: (0, 1, 2, 3)}
+    else:
+        rows = {0: (0, 1, 2, 3), 1: (2,), 2: (0, 1, 3), 3: (1,)}
+    for i, cols in rows.items():
+        layout[0, i, list(cols)] = 1
+    lay = sfb.BlockLayout(torch.from_numpy(layout).cuda(), 64)
+    luts = oracle.lut_build(layout)
+    q, k, v = (_rand(oracle, (B, nb * 64, H, d), 1100 + i, "bf16") for i in range(3))
+    ref = oracle.attention(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(), luts, 64,
+                           np.float32(0.125), want=("p", "o"))
+    if op == "probabilities":
+        p = sfb.fused_sddmm_softmax(q, k, lay, 0.125, torch.float32).float().cpu().numpy()
+        assert sfb.device_status() == 0
+        assert np.abs(p - ref["p"]).max() <= 2e-3 * ref["p"].max()
+        sums = oracle.blocks_to_dense(p, luts["nt"], nb, 64).sum(-1)
+        for i, cols in rows.items():
+            np.testing.assert_allclose(sums[:, :, i * 64:(i + 1) * 64], 1.0 if cols else 0.0, atol=1e-3)
+    else:
+        o = sfb.fused_attention(q, k, v, lay, 0.125).float().cpu().numpy()
+        assert sfb.device_status() == 0
+        assert np.abs(o - ref["o"]).max() <= REL * np.abs(ref["o"]).max()
+
+
 def test_host_pipeline_matches_resident_call(sfb):
     """Pinned host operands through the chunked, overlapped pipeline give the result of the resident call."""
     B, L, H, d = 4, 1024, 3, 64
