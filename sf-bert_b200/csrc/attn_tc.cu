@@ -29,6 +29,12 @@
 #ifndef SFB_TC_POLY
 #define SFB_TC_POLY 0
 #endif
+#ifndef SFB_TC_PREFETCH
+#define SFB_TC_PREFETCH 0
+#endif
+#ifndef SFB_TC_DEFER
+#define SFB_TC_DEFER 0
+#endif
 
 namespace sfb {
 
@@ -211,10 +217,10 @@ __device__ __forceinline__ bool mbar_wait2(uint64_t *bar_a, uint32_t par_a, uint
     return (a || bar_wait(bar_a, par_a, abort_flag, code)) && (b || bar_wait(bar_b, par_b, abort_flag, code));
 }
 
-// one poll for a whole warp with one outcome for all lanes
-__device__ __forceinline__ bool warp_try_wait(uint64_t *bar, uint32_t parity)
+// one look at a barrier for a whole warp with one outcome for all lanes; never suspends the warp
+__device__ __forceinline__ bool warp_test_wait(uint64_t *bar, uint32_t parity)
 {
-    return __all_sync(0xffffffffu, mbar_try_wait(bar, parity));
+    return __all_sync(0xffffffffu, mbar_test_wait(bar, parity));
 }
 
 // The union of the key blocks of block-rows 2*pair and 2*pair+1, built by ONE warp: the upper row's blocks in LUT
@@ -277,6 +283,8 @@ __device__ __forceinline__ void tma_producer(uint32_t s, uint8_t *smem, SharedSt
     uint32_t k = 0, t = 0, T = 0, g = 0, kq = 0, stage = 0, stored = 0, age = 0, idle = 0;
     int32_t xq = 0, row0 = 0, pair128 = 0;
     bool pending = false, done = false;
+    uint64_t *blocked_on = &st->list_ready[0];     // what this lane waits for when a round makes no progress
+    uint32_t blocked_par = 0;
     while (!done) {
         bool progress = false;
         if (!IS_K) {
@@ -314,7 +322,11 @@ __device__ __forceinline__ void tma_producer(uint32_t s, uint8_t *smem, SharedSt
                     progress = true;
                     break;
                 }
-                if (!mbar_test_wait(&st->list_ready[k & 1], (k >> 1) & 1)) break;
+                if (!mbar_test_wait(&st->list_ready[k & 1], (k >> 1) & 1)) {
+                    blocked_on = &st->list_ready[k & 1];
+                    blocked_par = (k >> 1) & 1;
+                    break;
+                }
                 T = st->list_n[k & 1];
                 progress = again = true;
                 if (T == 0) {
@@ -330,7 +342,11 @@ __device__ __forceinline__ void tma_producer(uint32_t s, uint8_t *smem, SharedSt
                 stage = IS_K ? 1 : 2;
             } else if (stage == 1) {
                 // the query tile is free once the previous item's last S product has completed
-                if (kq >= 1 && !mbar_test_wait(&st->q_free, (kq - 1) & 1)) break;
+                if (kq >= 1 && !mbar_test_wait(&st->q_free, (kq - 1) & 1)) {
+                    blocked_on = &st->q_free;
+                    blocked_par = (kq - 1) & 1;
+                    break;
+                }
                 mbar_expect_tx(&st->q_full, kQBytes);
                 tma_load_2d(smem_u32(smem + kOffQ + s * kQBytes), &qmap, &st->q_full, xq, row0 + pair128);
                 stage = 2;
@@ -340,7 +356,11 @@ __device__ __forceinline__ void tma_producer(uint32_t s, uint8_t *smem, SharedSt
                 const UEntry *list = lists + (s * 2 + (k & 1)) * kMaxU;
                 uint64_t *empty = IS_K ? &st->qk_done[b2] : &st->pv_done[b2];
                 uint64_t *full = IS_K ? &st->k_full[b2] : &st->v_full[b2];
-                if (gg >= 2 && !mbar_test_wait(empty, ((gg >> 1) - 1) & 1)) break;
+                if (gg >= 2 && !mbar_test_wait(empty, ((gg >> 1) - 1) & 1)) {
+                    blocked_on = empty;
+                    blocked_par = ((gg >> 1) - 1) & 1;
+                    break;
+                }
                 mbar_expect_tx(full, kTileBytes);
                 tma_load_2d(smem_u32(smem + (IS_K ? kOffK : kOffV) + (s * 2 + b2) * kTileBytes), &tmap, full, xq,
                             row0 + (int32_t)((list[t].col_flags & 0x3fffffffu) * 64));
@@ -357,8 +377,11 @@ __device__ __forceinline__ void tma_producer(uint32_t s, uint8_t *smem, SharedSt
         if (progress) {
             idle = 0;
         } else {
-            // no __nanosleep here: even a request of 20 ns came back after about a microsecond (measured), and a tile that is
-            // asked for a microsecond late stalls its stream
+            // Nothing to do: sleep in the barrier unit on what this lane is waiting for, a quarter of a microsecond at most (the
+            // tiles are asked for a step ahead, the value lanes' stores can wait that long too).  A lane that polls flat
+            // out takes a third of its sub-partition's issue slots from the softmax warps (measured); __nanosleep is no
+            // alternative: a request of 20 ns came back after about a microsecond.
+            if (stage != 4) mbar_try_wait_sleep(blocked_on, blocked_par, 256);
             if ((++idle & 63u) == 0 && *abort_flag) break;
             if (idle > (kWaitLimit >> 2)) {
                 give_up(abort_flag, IS_K ? 1 : 15);
@@ -537,38 +560,113 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
         uint8_t *ostage = smem + kOffO + s * kQBytes;
         const float sl = p.scale_log2e;
         const uint64_t sl2 = pk64(sl, sl);
-        uint32_t g = 0, kq = 0;
+        uint32_t g = 0, kq = 0, n_epi = 0;
         bool alive = true;
+
+        // The epilogue of an item: O / row sum -> the stream's staging tile -> (value producer) one TMA store per row pair.
+        // It runs AFTER the first softmax step of the stream's next item: by then the item's last O product has long
+        // completed, so nothing waits for the tensor core, and the next item's first products were not held up.
+        // 16 accumulator columns at a time: the registers of the next step's scores stay live around it.
+        auto epilogue = [&](bool has_data, uint32_t e_id, uint64_t l0, uint64_t l1) -> bool {
+            const Item e_it = decode_item(e_id, p);
+            const uint32_t e_pair = e_it.pair, e_b = e_it.b, e_h = e_it.h;
+            const bool has_row1 = e_pair * 2 + 1 < p.nb;
+            float inv = 0.f;
+            if (has_data) {
+                if (!bar_wait_warp(&st->o_final, kq & 1, abort_flag, 10)) return false;
+                tcgen05_fence_after();
+                float a0, a1, a2, a3;
+                up64(l0, a0, a1);
+                up64(l1, a2, a3);
+                const float lsum = (a0 + a1) + (a2 + a3);
+                inv = lsum > 0.f ? 1.f / lsum : 0.f;
+            }
+            // the previous store out of the staging tile has been read out of shared memory
+            if (n_epi >= 1 && !bar_wait_warp(&st->stage_free, (n_epi - 1) & 1, abort_flag, 13)) return false;
+            uint8_t *orow = ostage + r * 128;
+            uint16_t *dst = (uint16_t *)p.O + ((size_t)e_b * L + (size_t)e_pair * 128 + r) * (size_t)p.o_pitch + (size_t)e_h * 64;
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) {
+                uint32_t oc[16];
+                if (has_data) {
+                    TMEM_LD_16((oc), t_o + c0);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 16; c++) oc[c] = 0u;      // a row pair without key blocks gives zeros (blocksparse.h:949-962)
+                }
+                uint32_t w[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) w[j] = pack_pair<BF16>(__uint_as_float(oc[2 * j]) * inv, __uint_as_float(oc[2 * j + 1]) * inv);
+                if (has_row1) {
+                    // 16-byte chunk c of row r sits at chunk c ^ (r % 8): the tensor map's 128-byte swizzle
+                    const int ch = c0 >> 3;
+                    *(uint4 *)(orow + (((ch) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *(uint4 *)(orow + (((ch + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+                } else if (half == 0) {
+                    // an odd number of block-rows: the last pair has 64 rows only, written directly
+                    *(uint4 *)(dst + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *(uint4 *)(dst + c0 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                }
+            }
+            if (has_data) {
+                tcgen05_fence_before();
+                mbar_arrive(&st->o_free);              // the next item's first O product may overwrite the accumulator
+                kq++;
+            }
+            if (has_row1) fence_proxy_async();
+            if (r == 0) {
+                st->store_x = (int32_t)(e_h * 64);
+                st->store_y = has_row1 ? (int32_t)(e_b * L + e_pair * 128) : -1;
+            }
+            mbar_arrive(&st->stage_full);      // the value producer issues the store and hands the tile back
+            n_epi++;
+            return true;
+        };
+
+        bool pend = false, pre = false;                    // an epilogue is owed / the next step's scores are in registers
+        uint32_t pend_id = 0;
+        uint64_t pend_l0 = 0, pend_l1 = 0;
+        uint32_t sr[64];                                   // this row of S(t), fp32 bits
         for (uint32_t k = 0; alive; k++) {
             const uint32_t id = item_id(k, s);
             if (id >= p.n_items) break;
             if (!bar_wait_warp(&st->list_ready[k & 1], (k >> 1) & 1, abort_flag, 8)) break;
             const uint32_t T = st->list_n[k & 1];
             const UEntry *list = lists + (s * 2 + (k & 1)) * kMaxU;
-            const Item it = decode_item(id, p);
-            const bool has_row1 = it.pair * 2 + 1 < p.nb;
+            const uint32_t item_h = HAS_MASK ? decode_item(id, p).h : 0u;
+            if (T == 0) {
+                if (pend && !epilogue(true, pend_id, pend_l0, pend_l1)) break;
+                pend = false;
+                if (!epilogue(false, id, 0ull, 0ull)) break;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&st->list_free[k & 1]);
+                continue;
+            }
             float m_used = -INFINITY;
             uint64_t lacc0 = 0, lacc1 = 0;                 // four partial row sums (two packed pairs)
-            uint32_t sr[64];                               // this row of S(t), fp32 bits; later this row of O
             for (uint32_t t = 0; t < T; t++) {
                 const uint32_t gg = g + t, b2 = gg & 1;
-                TRACE_SM(gg, 0);
-                if (!bar_wait_warp(&st->qk_done[b2], (gg >> 1) & 1, abort_flag, 6)) { alive = false; break; }
-                TRACE_SM(gg, 1);
-                TRACE_Q(gg, quarter);
-                tcgen05_fence_after();
                 const uint32_t t_s = tbase + 32 * b2, t_p = tbase + 64 * b2;
-                TMEM_LD_32((sr), t_s);
-                TMEM_LD_32((sr + 32), t_s + 32);
-                const bool mine = (list[t].col_flags >> (30 + half)) & 1;     // the same for the whole warp
-                uint64_t mw = ~0ull;
-                if (HAS_MASK && mine) mw = p.mask[(size_t)it.h * p.mask_stride + (size_t)list[t].blk[half] * 64 + (r & 63)];
-                tmem_wait_ld();
+                TRACE_SM(gg, 0);
+                if (!pre) {
+                    if (!bar_wait_warp(&st->qk_done[b2], (gg >> 1) & 1, abort_flag, 6)) { alive = false; break; }
+                    TRACE_SM(gg, 1);
+                    tcgen05_fence_after();
+                    TMEM_LD_32((sr), t_s);
+                    TMEM_LD_32((sr + 32), t_s + 32);
+                    tmem_wait_ld();
+                }
+                pre = false;
                 tcgen05_fence_before();
                 mbar_arrive(&st->s_free);                  // the buffer may be overwritten from here on
                 TRACE_SM(gg, 2);
+                const bool mine = (list[t].col_flags >> (30 + half)) & 1;     // the same for the whole warp
+                // is the next step's S there already?  Then its two halves are fetched while this step's exponentials run
+                bool fetch = false;
                 if (mine) {
                     if (HAS_MASK) {
+                        const uint64_t mw = p.mask[(size_t)item_h * p.mask_stride + (size_t)list[t].blk[half] * 64 + (r & 63)];
 #pragma unroll
                         for (int c = 0; c < 64; c++)
                             if (!((mw >> c) & 1)) sr[c] = 0xff800000u;
@@ -622,6 +720,9 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                             const int c = hh * 32 + 2 * j;
                             const uint64_t x = fma2p(pk64(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), sl2, nm2);
                             float e0, e1;
+#if defined(SFB_TC_ABL) && SFB_TC_ABL == 1
+                            up64(x, e0, e1);      // timing experiment only: no exponentials
+#else
                             if (POLY > 0 && (j % (POLY > 0 ? POLY : 1)) == (POLY > 0 ? POLY : 1) - 1) {
                                 exp2_fma_pair(x, e0, e1);
                             } else {
@@ -630,11 +731,20 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                                 e0 = ex2_approx(x0);
                                 e1 = ex2_approx(x1);
                             }
+#endif
                             if (j & 1) lacc1 = add2p(lacc1, pk64(e0, e1));
                             else lacc0 = add2p(lacc0, pk64(e0, e1));
                             pk[j] = pack_pair<BF16>(e0, e1);
                         }
                         TMEM_ST_16(t_p + hh * 16, (pk));
+                        if (hh == 0) {
+                            // the first half of the registers is free: the next step's scores start their way into them
+                            fetch = SFB_TC_PREFETCH && t + 1 < T && warp_test_wait(&st->qk_done[b2 ^ 1], ((gg + 1) >> 1) & 1);
+                            if (fetch) {
+                                tcgen05_fence_after();
+                                TMEM_LD_32((sr), tbase + 32 * (b2 ^ 1));
+                            }
+                        }
                     }
                 } else {
                     uint32_t pk[16];
@@ -642,69 +752,43 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                     for (int j = 0; j < 16; j++) pk[j] = 0u;
                     TMEM_ST_16(t_p, (pk));
                     TMEM_ST_16(t_p + 16, (pk));
+                    fetch = SFB_TC_PREFETCH && t + 1 < T && warp_test_wait(&st->qk_done[b2 ^ 1], ((gg + 1) >> 1) & 1);
+                    if (fetch) {
+                        tcgen05_fence_after();
+                        TMEM_LD_32((sr), tbase + 32 * (b2 ^ 1));
+                    }
                 }
+                if (fetch) TMEM_LD_32((sr + 32), tbase + 32 * (b2 ^ 1) + 32);
                 TRACE_SM(gg, 4);
                 tmem_wait_st();
                 tcgen05_fence_before();
                 mbar_arrive(&st->p_full[b2]);
                 TRACE_SM(gg, 5);
                 TRACE_Q(gg, 4 + quarter);
+                if (fetch) {
+                    // no load is left in flight across the loop's back edge: the registers it fills are read right after
+                    tmem_wait_ld();
+                    pre = true;
+                }
+                if (t == 0 && pend) {
+                    if (!epilogue(true, pend_id, pend_l0, pend_l1)) { alive = false; break; }
+                    pend = false;
+                }
             }
             if (!alive) break;
             g += T;
-
-            // ---- epilogue: O / row sum -> the stream's staging tile -> one TMA store per row pair ----
-            float inv = 0.f;
-            if (T > 0) {
-                if (!bar_wait_warp(&st->o_final, kq & 1, abort_flag, 10)) break;
-                TRACE_SM(g - 1, 6);
-                tcgen05_fence_after();
-                TMEM_LD_32((sr), t_o);
-                TMEM_LD_32((sr + 32), t_o + 32);
-                tmem_wait_ld();
-                tcgen05_fence_before();
-                mbar_arrive(&st->o_free);
-                if (quarter == 0) TRACE_Q(g - 1, 8);
-                kq++;
-                float l0, l1, l2, l3;
-                up64(lacc0, l0, l1);
-                up64(lacc1, l2, l3);
-                const float lsum = (l0 + l1) + (l2 + l3);
-                inv = lsum > 0.f ? 1.f / lsum : 0.f;
+            if (SFB_TC_DEFER) {
+                pend = true;
+                pend_id = id;
+                pend_l0 = lacc0;
+                pend_l1 = lacc1;
+            } else if (!epilogue(true, id, lacc0, lacc1)) {
+                break;
             }
-            uint32_t w[32];
-#pragma unroll
-            for (int j = 0; j < 32; j++) {
-                const float a0 = T > 0 ? __uint_as_float(sr[2 * j]) * inv : 0.f;
-                const float a1 = T > 0 ? __uint_as_float(sr[2 * j + 1]) * inv : 0.f;
-                w[j] = pack_pair<BF16>(a0, a1);
-            }
-            if (quarter == 0 && T > 0) TRACE_Q(g - 1, 9);
-            // the previous store out of the staging tile has been read out of shared memory
-            if (k >= 1 && !bar_wait_warp(&st->stage_free, (k - 1) & 1, abort_flag, 13)) break;
-            if (quarter == 0 && T > 0) TRACE_Q(g - 1, 10);
-            if (has_row1) {
-                // 16-byte chunk c of row r sits at chunk c ^ (r % 8): the tensor map's 128-byte swizzle
-                uint8_t *orow = ostage + r * 128;
-#pragma unroll
-                for (int ch = 0; ch < 8; ch++)
-                    *(uint4 *)(orow + ((ch ^ (r & 7)) << 4)) = make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
-                fence_proxy_async();
-            } else if (half == 0) {
-                // an odd number of block-rows: the last pair has 64 rows only, written directly
-                uint16_t *dst = (uint16_t *)p.O + ((size_t)it.b * L + (size_t)it.pair * 128 + r) * (size_t)p.o_pitch + (size_t)it.h * 64;
-#pragma unroll
-                for (int ch = 0; ch < 8; ch++) *(uint4 *)(dst + 8 * ch) = make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
-            }
-            if (r == 0) {
-                st->store_x = (int32_t)(it.h * 64);
-                st->store_y = has_row1 ? (int32_t)(it.b * L + it.pair * 128) : -1;
-            }
-            mbar_arrive(&st->stage_full);      // the value producer issues the store and hands the tile back
-            if (T > 0) TRACE_SM(g - 1, 7);
             __syncwarp();
             if (lane == 0) mbar_arrive(&st->list_free[k & 1]);
         }
+        if (alive && pend) epilogue(true, pend_id, pend_l0, pend_l1);
     }
 
     // ---- teardown (also the way out after a timeout) ----
