@@ -185,11 +185,30 @@ int sfb_fused_attention(sfb_stream_t stream, const void *nn_lut, const void *q, 
                         uint32_t lut_heads, uint32_t lut_dim, uint32_t mask_heads,
                         float scale, uint32_t max_lut);
 
+/* The same operator on a SLICE of the heads of wider tensors, in place: q, k, v point at the slice's first head inside
+ * [B, L, H_total, d] tensors whose rows (one sequence position) lie in_pitch elements apart (H_total * d), o likewise
+ * with out_pitch; head_dim counts the heads of the slice, lut_heads / mask_heads are 1 or that count.  0 for a pitch
+ * means head_dim * state_dim, i.e. sfb_fused_attention.  This is how one GPU of several takes its share of the
+ * (batch, head) pairs without packing them first: the reference addresses a pair by offsets off the tensor base with
+ * the full row stride (blocksparse.h:250-266), but derives that stride from head_dim (blocksparse.h:434-437), so its
+ * own entry points cannot be handed a slice.  The tensor cores are used when the pitches are multiples of 8 elements. */
+int sfb_fused_attention_slice(sfb_stream_t stream, const void *nn_lut, const void *q, const void *k,
+                              const void *v, void *o, const void *mask, int dtype,
+                              uint32_t block_size, uint32_t blocks, uint32_t batch_dim,
+                              uint32_t ctx_blks, uint32_t head_dim, uint32_t state_dim,
+                              uint32_t lut_heads, uint32_t lut_dim, uint32_t mask_heads,
+                              float scale, uint32_t max_lut, uint64_t in_pitch, uint64_t out_pitch);
+
 /* Synchronises with the device and reads the library's status word into *status (HOST pointer):
  * 0 while no kernel has given up on a bounded wait, otherwise (code << 24 | CTA index) of the
- * first one that did.  No counterpart in the reference, whose fused kernels spin without a bound
- * (fusion_blocksparse.h:246-289). */
+ * first one that did.  Code 9 is not a wait: a row pair of sfb_fused_attention touched more key blocks than the
+ * tensor-core kernel's list holds (256) although max_lut promised otherwise; that pair's output rows are written
+ * as zeros, all other rows are correct.  No counterpart in the reference, whose fused kernels spin without a
+ * bound (fusion_blocksparse.h:246-289). */
 int sfb_device_status(uint32_t *status);
+
+/* Synchronises with the device and sets the status word back to 0 (it keeps the first code it was given until then). */
+int sfb_device_status_clear(void);
 
 /* ---- epilogue -------------------------------------------------------------------------- */
 

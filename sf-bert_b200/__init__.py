@@ -25,7 +25,7 @@ SYMBOLS = [
     "sfb_magicu64", "sfb_bst_sgemm_nt", "sfb_masked_softmax", "sfb_bst_sgemm_xn", "sfb_fused_sddmm_softmax",
     "sfb_fused_attention", "sfb_bias_residual_layernorm", "sfb_device_status", "sfb_bias_gelu", "sfb_lut_build_tn",
     "sfb_masked_softmax_grad", "sfb_linear", "sfb_linear_nt", "sfb_embedding", "sfb_csr_from_layout",
-    "sfb_csr_attention", "sfb_rowdot", "sfb_fused_sddmm_softmax_grad",
+    "sfb_csr_attention", "sfb_rowdot", "sfb_fused_sddmm_softmax_grad", "sfb_fused_attention_slice", "sfb_device_status_clear",
 ]
 
 if not os.path.exists(LIB_PATH):
@@ -56,6 +56,7 @@ lib.sfb_fused_sddmm_softmax_grad.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, 
 lib.sfb_csr_attention.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _u32, _u32, _u32, _u32, _f32, _vp]
 lib.sfb_fused_sddmm_softmax.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32] + [_u32] * 10 + [_f32]
 lib.sfb_fused_attention.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32] + [_u32] * 9 + [_f32, _u32]
+lib.sfb_fused_attention_slice.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32] + [_u32] * 9 + [_f32, _u32, _u64, _u64]
 lib.sfb_bias_residual_layernorm.argtypes = [_vp] * 10 + [_u32, _u32, _i32]
 
 
@@ -68,6 +69,11 @@ def device_status():
     v = _u32(0)
     _check(lib.sfb_device_status(C.byref(v)))
     return v.value
+
+
+def device_status_clear():
+    """Sets the status word back to 0 (synchronises with the device)."""
+    _check(lib.sfb_device_status_clear())
 
 
 class SfbError(RuntimeError):
@@ -356,6 +362,31 @@ def fused_attention(q, k, v, lay, scale=None, use_mask=False, out=None):
     _check(lib.sfb_fused_attention(_stream(), _p(lay.nn_lut), _p(q), _p(k), _p(v), _p(o), _p(mask), dtype_tag(q),
                                    lay.block_size, lay.blocks, B, lay.nb, H, d, lay.heads, lay.nt_lut_dim, lay.heads,
                                    scale, lay.nn_max))
+    return o
+
+
+def _row_pitch(t):
+    """Row pitch (elements) of a [B, L, H, d] view whose heads are a slice of a wider tensor: rows of one batch element
+    and batch elements themselves must follow each other at that pitch."""
+    B, L, H, d = t.shape
+    sb, sl, sh, sd = t.stride()
+    assert sd == 1 and sh == d and sl >= H * d and (B == 1 or sb == L * sl), "not a head slice of a [B, L, H_total, d] tensor"
+    return sl
+
+
+def fused_attention_slice(q, k, v, lay, scale=None, use_mask=False, out=None):
+    """fused_attention on views that select some heads (and batch elements) of wider [B, L, H_total, d] tensors, in
+    place (sfb_fused_attention_slice): what one rank of a multi-GPU run calls on its share of the (batch, head) pairs."""
+    B, L, H, d = _dims(q, lay)
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    o = torch.empty(B, L, H, d, dtype=q.dtype, device=q.device) if out is None else out
+    pin = _row_pitch(q)
+    assert _row_pitch(k) == pin and _row_pitch(v) == pin
+    mask = lay.mask_np if use_mask else None
+    _check(lib.sfb_fused_attention_slice(_stream(), _p(lay.nn_lut), _p(q), _p(k), _p(v), _p(o), _p(mask), dtype_tag(q),
+                                         lay.block_size, lay.blocks, B, lay.nb, H, d, lay.heads, lay.nt_lut_dim, lay.heads,
+                                         scale, lay.nn_max, pin, _row_pitch(o)))
     return o
 
 

@@ -633,7 +633,8 @@ __global__ void __launch_bounds__(256) fused_attention_kernel(const uint2 *__res
     const uint32_t i = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
     const uint2 *nn = lut + (size_t)h * p.lut_stride;
     const uint2 head = nn[i];
-    const size_t HD = (size_t)p.H * p.d;
+    const size_t HD = p.in_pitch ? (size_t)p.in_pitch : (size_t)p.H * p.d;      // row pitch of q, k, v
+    const size_t HDo = p.out_pitch ? (size_t)p.out_pitch : (size_t)p.H * p.d;   // row pitch of o
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const W *mh = mask ? mask + (size_t)h * p.mask_stride : nullptr;
 
@@ -704,14 +705,14 @@ __global__ void __launch_bounds__(256) fused_attention_kernel(const uint2 *__res
                 for (int n = 0; n < TD; n++) acc[m][n] = fmaf(a[m], bb[n], acc[m][n]);
         }
     }
-    const size_t baseO = ((size_t)b * p.nb_a * BS + (size_t)i * BS) * HD + (size_t)h * p.d;
+    const size_t baseO = ((size_t)b * p.nb_a * BS + (size_t)i * BS) * HDo + (size_t)h * p.d;
 #pragma unroll
     for (int m = 0; m < T; m++) {
         const float inv = sum[m] > 0.f ? 1.f / sum[m] : 0.f;
 #pragma unroll
         for (int n = 0; n < TD; n++)
             if ((uint32_t)(tx + 16 * n) < p.d)
-                Elem<DT>::store(O, baseO + (size_t)(ty + 16 * m) * HD + tx + 16 * n, acc[m][n] * inv);
+                Elem<DT>::store(O, baseO + (size_t)(ty + 16 * m) * HDo + tx + 16 * n, acc[m][n] * inv);
     }
 }
 

@@ -827,19 +827,17 @@ int tc_fused_attention(cudaStream_t s, const void *nn_lut, const void *q, const 
                        const void *mask, int dtype, const AttnDims &p, float scale)
 {
     using namespace tc;
-    const uintptr_t al = (uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o;
-    SFB_REQUIRE((al & 15) == 0, "sfb_fused_attention: q, k, v, o must be 16-byte aligned");
     const int is_bf16 = dtype == SFB_BF16;
     const uint64_t rows = (uint64_t)p.B * p.nb_a * 64;
     CUtensorMap qm, km, vm, om;
-    if (make_map(&qm, q, rows, p.H, is_bf16, 128) || make_map(&km, k, rows, p.H, is_bf16, 64) ||
-        make_map(&vm, v, rows, p.H, is_bf16, 64) || make_map(&om, o, rows, p.H, is_bf16, 128))
+    if (make_map(&qm, q, rows, p.H, is_bf16, 128, p.in_pitch) || make_map(&km, k, rows, p.H, is_bf16, 64, p.in_pitch) ||
+        make_map(&vm, v, rows, p.H, is_bf16, 64, p.in_pitch) || make_map(&om, o, rows, p.H, is_bf16, 128, p.out_pitch))
         return 1;
     const uint32_t npairs = (p.nb_a + 1) / 2;
     const uint64_t n_items = (uint64_t)npairs * p.B * p.H;
     SFB_REQUIRE(n_items < (1ull << 31), "sfb_fused_attention: too many row pairs for one launch");
     Params prm = {(const uint2 *)nn_lut, (const uint64_t *)mask, o, p.B, p.H, p.nb_a, npairs, (uint32_t)n_items, p.lut_stride,
-                  p.mask_stride, p.H * 64, scale * 1.4426950408889634f};
+                  p.mask_stride, (uint32_t)(p.out_pitch ? p.out_pitch : (uint64_t)p.H * 64), scale * 1.4426950408889634f};
     const int dev = current_device();
     const int sms = device_sm_count(dev);
     if (sms <= 0) return fail("sfb_fused_attention: cannot read the SM count");
@@ -868,6 +866,14 @@ extern "C" int sfb_debug_trace(long long *out, int n)
     return cudaMemcpyFromSymbol(out, tc::g_trace, sizeof(long long) * n) == cudaSuccess ? 0 : 1;
 }
 #endif
+
+int tc_status_clear_fused()
+{
+    const uint32_t zero = 0;
+    cudaError_t e = cudaMemcpyToSymbol(tc::g_status, &zero, sizeof(uint32_t));
+    if (e != cudaSuccess) return fail("sfb_device_status_clear: %s", cudaGetErrorString(e));
+    return 0;
+}
 
 int tc_status_fused(uint32_t *out)
 {

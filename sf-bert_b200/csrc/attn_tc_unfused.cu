@@ -699,6 +699,14 @@ int tc_spmm(cudaStream_t s, const void *nn_lut, const void *a, const void *b, vo
     return check_launch("sfb_bst_sgemm_xn");
 }
 
+int tc_status_clear_unfused()
+{
+    const uint32_t zero = 0;
+    cudaError_t e = cudaMemcpyToSymbol(tc::g_status, &zero, sizeof(uint32_t));
+    if (e != cudaSuccess) return fail("sfb_device_status_clear: %s", cudaGetErrorString(e));
+    return 0;
+}
+
 int tc_status_unfused(uint32_t *out)
 {
     cudaError_t e = cudaMemcpyFromSymbol(out, tc::g_status, sizeof(uint32_t));

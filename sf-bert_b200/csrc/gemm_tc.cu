@@ -270,6 +270,14 @@ int tc_linear(cudaStream_t s, void *out, const void *x, const void *w, const flo
     return check_launch("sfb_linear");
 }
 
+int tc_status_clear_gemm()
+{
+    const uint32_t zero = 0;
+    cudaError_t e = cudaMemcpyToSymbol(tc::g_status, &zero, sizeof(uint32_t));
+    if (e != cudaSuccess) return fail("sfb_device_status_clear: %s", cudaGetErrorString(e));
+    return 0;
+}
+
 int tc_status_gemm(uint32_t *out)
 {
     cudaError_t e = cudaMemcpyFromSymbol(out, tc::g_status, sizeof(uint32_t));

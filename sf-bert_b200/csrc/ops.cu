@@ -105,25 +105,48 @@ extern "C" int sfb_fused_sddmm_softmax(sfb_stream_t stream, const void *nn_lut, 
     return simt_fused_sddmm_softmax(as_stream(stream), nn_lut, a, b, mask, y, ab_dtype, y_dtype, block_size, p, scale);
 }
 
-extern "C" int sfb_fused_attention(sfb_stream_t stream, const void *nn_lut, const void *q, const void *k, const void *v, void *o,
-                                   const void *mask, int dtype, uint32_t block_size, uint32_t blocks, uint32_t batch_dim,
-                                   uint32_t ctx_blks, uint32_t head_dim, uint32_t state_dim, uint32_t lut_heads, uint32_t lut_dim,
-                                   uint32_t mask_heads, float scale, uint32_t max_lut)
+static int fused_attention_common(const char *who, sfb_stream_t stream, const void *nn_lut, const void *q, const void *k, const void *v,
+                                  void *o, const void *mask, int dtype, uint32_t block_size, uint32_t blocks, uint32_t batch_dim,
+                                  uint32_t ctx_blks, uint32_t head_dim, uint32_t state_dim, uint32_t lut_heads, uint32_t lut_dim,
+                                  uint32_t mask_heads, float scale, uint32_t max_lut, uint64_t in_pitch, uint64_t out_pitch)
 {
-    const char *who = "sfb_fused_attention";
-    (void)max_lut;
     SFB_REQUIRE(nn_lut && q && k && v && o, "%s: NULL pointer", who);
     SFB_REQUIRE(valid_dtype(dtype), "%s: unknown dtype %d", who, dtype);
     if (check_common(who, block_size, batch_dim, head_dim, state_dim, lut_heads)) return 1;
     SFB_REQUIRE(mask_heads == 1 || mask_heads == head_dim, "%s: mask_heads=%u must be 1 or head_dim", who, mask_heads);
     SFB_REQUIRE(lut_heads == 1 || lut_dim >= blocks, "%s: lut_dim %u smaller than blocks %u", who, lut_dim, blocks);
+    const uint64_t width = (uint64_t)head_dim * state_dim;
+    SFB_REQUIRE((in_pitch == 0 || in_pitch >= width) && (out_pitch == 0 || out_pitch >= width),
+                "%s: a row pitch smaller than head_dim * state_dim = %llu elements", who, (unsigned long long)width);
+    SFB_REQUIRE(in_pitch < (1ull << 31) && out_pitch < (1ull << 31), "%s: row pitch too large", who);
     if (ctx_blks == 0) { clear_error(); return 0; }
     AttnDims p = {batch_dim, head_dim, state_dim, ctx_blks, ctx_blks, blocks, lut_heads > 1 ? lut_dim + ctx_blks : 0,
-                  mask_heads > 1 ? blocks * block_size : 0};
-    // 16-bit operands with 64x64 blocks and 64-wide heads run on the tensor cores
-    if (tc_fused_attention_supported(dtype, block_size, p, scale, max_lut))
+                  mask_heads > 1 ? blocks * block_size : 0, in_pitch, out_pitch};
+    // 16-bit operands with 64x64 blocks and 64-wide heads run on the tensor cores, when the TMA can address them
+    // (16-byte aligned bases and row pitches); everything else runs on the CUDA cores
+    const bool tma_ok = ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o) & 15) == 0) && in_pitch % 8 == 0 && out_pitch % 8 == 0;
+    if (tma_ok && tc_fused_attention_supported(dtype, block_size, p, scale, max_lut))
         return tc_fused_attention(as_stream(stream), nn_lut, q, k, v, o, mask, dtype, p, scale);
     return simt_fused_attention(as_stream(stream), nn_lut, q, k, v, o, mask, dtype, block_size, p, scale);
+}
+
+extern "C" int sfb_fused_attention(sfb_stream_t stream, const void *nn_lut, const void *q, const void *k, const void *v, void *o,
+                                   const void *mask, int dtype, uint32_t block_size, uint32_t blocks, uint32_t batch_dim,
+                                   uint32_t ctx_blks, uint32_t head_dim, uint32_t state_dim, uint32_t lut_heads, uint32_t lut_dim,
+                                   uint32_t mask_heads, float scale, uint32_t max_lut)
+{
+    return fused_attention_common("sfb_fused_attention", stream, nn_lut, q, k, v, o, mask, dtype, block_size, blocks, batch_dim, ctx_blks,
+                                  head_dim, state_dim, lut_heads, lut_dim, mask_heads, scale, max_lut, 0, 0);
+}
+
+extern "C" int sfb_fused_attention_slice(sfb_stream_t stream, const void *nn_lut, const void *q, const void *k, const void *v, void *o,
+                                         const void *mask, int dtype, uint32_t block_size, uint32_t blocks, uint32_t batch_dim,
+                                         uint32_t ctx_blks, uint32_t head_dim, uint32_t state_dim, uint32_t lut_heads,
+                                         uint32_t lut_dim, uint32_t mask_heads, float scale, uint32_t max_lut, uint64_t in_pitch,
+                                         uint64_t out_pitch)
+{
+    return fused_attention_common("sfb_fused_attention_slice", stream, nn_lut, q, k, v, o, mask, dtype, block_size, blocks, batch_dim,
+                                  ctx_blks, head_dim, state_dim, lut_heads, lut_dim, mask_heads, scale, max_lut, in_pitch, out_pitch);
 }
 
 static int linear_common(const char *who, sfb_stream_t stream, void *out, const void *x, const void *w, const float *bias, uint32_t m,
@@ -196,6 +219,13 @@ extern "C" int sfb_fused_sddmm_softmax_grad(sfb_stream_t stream, const void *nt_
     AttnDims p = {batch_dim, head_dim, state_dim, ctx_blks, ctx_blks, blocks, lut_heads > 1 ? lut_dim : 0, 0};
     SFB_REQUIRE((uint64_t)batch_dim * ctx_blks * 64 < (1ull << 31), "%s: sequence too long for one launch", who);
     return tc_sddmm_softmax_grad(as_stream(stream), nt_lut, dout, v, p_blocks, delta, ds, dtype, p, scale);
+}
+
+extern "C" int sfb_device_status_clear(void)
+{
+    if (tc_status_clear_fused() || tc_status_clear_unfused() || tc_status_clear_gemm()) return 1;
+    clear_error();
+    return 0;
 }
 
 extern "C" int sfb_device_status(uint32_t *status)

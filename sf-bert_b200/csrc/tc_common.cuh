@@ -333,13 +333,14 @@ inline EncodeTiledFn encode_fn()
     return fn;
 }
 
-// [rows, H*64] 16-bit row-major tensor, boxes of box_rows x 64 elements (one head's slice), 128-byte swizzle
-inline int make_map(CUtensorMap *map, const void *base, uint64_t rows, uint32_t H, int is_bf16, uint32_t box_rows)
+// [rows, H*64] 16-bit row-major tensor, boxes of box_rows x 64 elements (one head's slice), 128-byte swizzle; pitch =
+// elements between consecutive rows (0 = H*64; larger when the H heads are a slice of a wider tensor)
+inline int make_map(CUtensorMap *map, const void *base, uint64_t rows, uint32_t H, int is_bf16, uint32_t box_rows, uint64_t pitch = 0)
 {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail("cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[2] = {(cuuint64_t)H * 64, rows};
-    cuuint64_t strides[1] = {(cuuint64_t)H * 64 * 2};
+    cuuint64_t strides[1] = {(cuuint64_t)(pitch ? pitch : (uint64_t)H * 64) * 2};
     cuuint32_t box[2] = {64, box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)base, dims,

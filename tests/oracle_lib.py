@@ -443,6 +443,19 @@ def ref_bias_residual_layernorm(x, bias, resid, gain, beta):
     return out, t2, mean, rstd
 
 
+def assert_close_16bit(got, ref, rel=2e-2, floor_of_rms=0.5):
+    """Element-wise bar for results of 16-bit operands with fp32 accumulation: |got - ref| <= rel * |ref| + floor for every
+    element, floor = rel * floor_of_rms * rms(ref).  The relative part is the stated 2e-2; the floor covers elements that are
+    small only because their terms cancel (their error does not shrink with them: it is the rounding of the probabilities
+    and of the exponentials' 16-bit arguments, about 1.5e-3 of rms(ref) per element, so the floor sits near six sigma)."""
+    got = np.asarray(got, np.float64)
+    ref = np.asarray(ref, np.float64)
+    floor = rel * floor_of_rms * float(np.sqrt(np.mean(ref * ref)))
+    excess = np.abs(got - ref) - (rel * np.abs(ref) + floor)
+    worst = float(excess.max())
+    assert worst <= 0.0, "element-wise 16-bit bar exceeded by %g (floor %g)" % (worst, floor)
+
+
 def blocks_to_dense(blk, nt, nb, bs):
     """[B,H,blocks,bs,bs] block tensor -> dense [B,H,L,L] (zeros elsewhere)."""
     B, H, blocks, _, _ = blk.shape
