@@ -143,6 +143,170 @@ def bind_to_gpu_cpus(index):
     return None
 
 
+
+# ------------------------------------------------------------------------------------------------
+def _load_encoder():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("sfb_encoder", os.path.join(ROOT, "sf-bert_b200", "encoder.py"))
+    enc = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(enc)
+    return enc
+
+
+def measure_encoder_layer(torch, sfb, cfg, steps, flush):
+    """ms per forward of one post-LN encoder layer at the workload's shape on this rank (attention, projections with
+    bias / GELU, bias + residual + LayerNorm all from this library); L2 flushed between timed steps."""
+    enc = _load_encoder()
+    B, H, L, d, bs = cfg["B"], cfg["H"], cfg["L"], cfg["d"], cfg["bs"]
+    tdt = {"f16": torch.float16, "bf16": torch.bfloat16}[cfg["dtype"]]
+    hidden, ffn = H * d, 4 * H * d
+    lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
+    w = enc.EncoderLayerWeights(hidden, ffn, tdt, seed=1)
+    x = torch.randn(B, L, hidden, device="cuda").to(tdt)
+    fn = lambda: enc.encoder_layer(sfb, x, w, lay, H, "post", "tensor")
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b_ in ev:
+        flush.fill_(1)
+        a.record()
+        fn()
+        b_.record()
+    torch.cuda.synchronize()
+    return sum(a.elapsed_time(b_) for a, b_ in ev) / steps, B
+
+
+def measure_encoder_stack(torch, sfb, cfg, steps, layers, rank):
+    """ms per forward of embedding + positions + `layers` post-LN encoder layers at the workload's shape, 1/8 of its
+    batch on this rank (the workload's 8-GPU split), replayed as one CUDA graph."""
+    enc = _load_encoder()
+    B, H, L, d, bs = cfg["B"], cfg["H"], cfg["L"], cfg["d"], cfg["bs"]
+    Bg = B // 8 if B >= 8 and B % 8 == 0 else B
+    tdt = {"f16": torch.float16, "bf16": torch.bfloat16}[cfg["dtype"]]
+    hidden, ffn, vocab = H * d, 4 * H * d, 30522
+    lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), cfg.get("lut_heads", 1), L // bs, bs, **cfg["layout"][1])
+    ws = [enc.EncoderLayerWeights(hidden, ffn, tdt, seed=100 + i) for i in range(layers)]
+    g = torch.Generator(device="cuda").manual_seed(7)
+    table = (0.02 * torch.randn(vocab, hidden, device="cuda", generator=g)).to(tdt)
+    pos = (0.02 * torch.randn(L, hidden, device="cuda", generator=g)).to(tdt)
+    ids = torch.randint(0, vocab, (Bg, L), device="cuda", dtype=torch.int32,
+                        generator=torch.Generator(device="cuda").manual_seed(1234 + rank))
+
+    def forward(tok):
+        x, _ = sfb.embedding(table, tok, pos)
+        for w in ws:
+            x = enc.encoder_layer(sfb, x, w, lay, H, "post", "tensor")
+        return x
+
+    for _ in range(2):
+        forward(ids)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        forward(ids)
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.cuda.graph(graph):
+        forward(ids)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps, Bg
+
+
+def pair_slices(B, H, start, stop):
+    """The (batch, head) pairs [start, stop) (pair = b * H + h) as rectangles (b0, b1, h0, h1) of the [B, L, H, d] tensors."""
+    out = []
+    p = start
+    while p < stop:
+        b, h = divmod(p, H)
+        if h == 0 and stop - p >= H:
+            nb_ = (stop - p) // H
+            out.append((b, b + nb_, 0, H))
+            p += nb_ * H
+        else:
+            h1 = min(H, h + stop - p)
+            out.append((b, b + 1, h, h1))
+            p += h1 - h
+    return out
+
+
+def measure_strong_scaling(torch, dist, sfb, steps, world, rank, chunks=2):
+    """Strong scaling of the `local_bertlarge` workload (B=4, H=16, L=16384: 64 (batch, head) pairs): the pairs are dealt
+    contiguously to the ranks (sharding.partition_pairs), a rank computes its share in place on head slices of the full
+    tensors (sfb_fused_attention_slice) in `chunks` launches, and every chunk's output is all-gathered (NCCL) on a second
+    stream while the next chunk computes.  Returns ms for the share alone, for the gather alone and for both overlapped."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("sfb_sharding", os.path.join(ROOT, "sf-bert_b200", "sharding.py"))
+    sh = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sh)
+    cfg = CONFIGS["local_bertlarge"]
+    B, H, L, d, bs = cfg["B"], cfg["H"], cfg["L"], cfg["d"], cfg["bs"]
+    lay = sfb.BlockLayout.generate(getattr(sfb, cfg["layout"][0]), 1, L // bs, bs, **cfg["layout"][1])
+    gen = torch.Generator(device="cuda").manual_seed(4321)      # the same tensors on every rank
+    q, k, v = (torch.randn(B, L, H, d, device="cuda", generator=gen).to(torch.bfloat16) for _ in range(3))
+    start, stop = sh.partition_pairs(B, H, world, rank)
+    n = stop - start
+    # the share in `chunks` pieces of whole pairs, each piece a few rectangles
+    bounds = [start + (n * c) // chunks for c in range(chunks + 1)]
+    pieces = [pair_slices(B, H, bounds[c], bounds[c + 1]) for c in range(chunks) if bounds[c + 1] > bounds[c]]
+    outs = [[torch.empty(b1 - b0, L, h1 - h0, d, dtype=torch.bfloat16, device="cuda") for (b0, b1, h0, h1) in piece] for piece in pieces]
+    gathered = [[torch.empty((world,) + tuple(o.shape), dtype=o.dtype, device="cuda") for o in po] for po in outs] if world > 1 else None
+    scale = 1.0 / d ** 0.5
+    comm = torch.cuda.Stream()
+
+    def compute(c):
+        for (b0, b1, h0, h1), o in zip(pieces[c], outs[c]):
+            sfb.fused_attention_slice(q[b0:b1, :, h0:h1], k[b0:b1, :, h0:h1], v[b0:b1, :, h0:h1], lay, scale, out=o)
+
+    def gather(c):
+        for o, g_ in zip(outs[c], gathered[c]):
+            dist.all_gather_into_tensor(g_, o)
+
+    def run(do_compute, do_gather):
+        cur = torch.cuda.current_stream()
+        for c in range(len(pieces)):
+            if do_compute:
+                compute(c)
+            if do_gather and world > 1:
+                ev = torch.cuda.Event()
+                ev.record(cur)
+                comm.wait_event(ev)
+                with torch.cuda.stream(comm):
+                    gather(c)
+        if do_gather and world > 1:
+            cur.wait_stream(comm)
+
+    def timed(do_compute, do_gather):
+        for _ in range(3):
+            run(do_compute, do_gather)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            run(do_compute, do_gather)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    ms_share = timed(True, False)
+    ms_gather = timed(False, True) if world > 1 else 0.0
+    ms_both = timed(True, True) if world > 1 else ms_share
+    flops = attention_flops(cfg, lay.blocks)
+    return dict(ms_share=ms_share, ms_gather=ms_gather, ms_both=ms_both, flops=flops, pairs=B * H, pairs_here=n,
+                launches=sum(len(p_) for p_ in pieces), gather_bytes=sum(o.numel() * 2 for po in outs for o in po))
+
 # ------------------------------------------------------------------------------------------------
 def run_ours(args):
     import torch
@@ -231,11 +395,24 @@ def run_ours(args):
         sync_all()
         gather_ms = g0.elapsed_time(g1) / 5
 
+    # the rest of the metric and of the multi-GPU row, as extra keys of the same line (headline workload only)
+    extra = None
+    if args.config == "stride_bertbase" and not args.no_extras:
+        del hq, hk, hv, ho, pipe
+        layer_ms, layer_B = measure_encoder_layer(torch, sfb, cfg, args.steps, flush)
+        stack_ms, stack_B = measure_encoder_stack(torch, sfb, CONFIGS["full_bertlarge"], max(args.steps // 2, 3), args.layers, rank)
+        strong = measure_strong_scaling(torch, dist, sfb, args.steps, world, rank)
+        extra = dict(layer_ms=layer_ms, layer_B=layer_B, stack_ms=stack_ms, stack_B=stack_B, strong=strong)
+
     status = sfb.device_status()
-    t = torch.tensor([ms_total, e2e_ms, gather_ms or 0.0], dtype=torch.float64, device="cuda")
+    vals = [ms_total, e2e_ms, gather_ms or 0.0]
+    if extra:
+        vals += [extra["layer_ms"], extra["stack_ms"], extra["strong"]["ms_share"], extra["strong"]["ms_gather"], extra["strong"]["ms_both"]]
+    t = torch.tensor(vals, dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms, gather_max = (float(x) for x in t.cpu())
+    vals = [float(x) for x in t.cpu()]
+    ms_total, e2e_ms, gather_max = vals[:3]
 
     if rank == 0:
         pk = peaks()
@@ -267,6 +444,22 @@ def run_ours(args):
         }
         if gather_ms is not None:
             line["gather_ms"] = round(gather_max, 4)
+        if extra:
+            layer_ms, stack_ms, share_ms, sgather_ms, both_ms = vals[3:8]
+            st = extra["strong"]
+            line["encoder_layer_seq_s"] = {"value": round(world * extra["layer_B"] / (layer_ms * 1e-3), 1), "unit": "seq/s", "ms_per_layer": round(layer_ms, 4),
+                                           "config": "one post-LN encoder layer at the stride_bertbase shape (B=%d per GPU, L=4096, hidden 768, FFN 3072), all kernels from this library" % extra["layer_B"],
+                                           "scaling": "weak"}
+            line["encoder_stack_seq_s"] = {"value": round(world * extra["stack_B"] / (stack_ms * 1e-3), 1), "unit": "seq/s", "ms_per_forward": round(stack_ms, 4),
+                                           "config": "embedding + %d post-LN layers at the full_bertlarge shape (L=1024, hidden 1024, FFN 4096), %d sequences per GPU, one CUDA graph replay per forward" % (args.layers, extra["stack_B"]),
+                                           "scaling": "weak"}
+            line["strong_scaling"] = {"workload": "local_bertlarge", "pairs": st["pairs"], "pairs_per_rank": st["pairs_here"],
+                                      "ms_share": round(share_ms, 4), "gather_ms": round(sgather_ms, 4), "ms_incl_gather": round(both_ms, 4),
+                                      "value": round(st["flops"] / (share_ms * 1e-3) / 1e12, 2),
+                                      "value_incl_gather": round(st["flops"] / (both_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                                      "how": "the 64 (batch, head) pairs dealt contiguously to the ranks, computed in place on head slices "
+                                             "(sfb_fused_attention_slice) in two chunks; each chunk's output all-gathered on a second stream under the next chunk's compute",
+                                      "gather_bytes_per_rank": st["gather_bytes"], "launches_per_step": st["launches"]}
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_reference_sample(cfg, budget_s=20.0, steps=1)
         print(json.dumps(line), flush=True)
@@ -856,6 +1049,7 @@ if __name__ == "__main__":
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="stride_bertbase", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the encoder-layer / encoder-stack / strong-scaling legs of the default line")
     ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer", "softmax_grad", "spmm_tn", "linear", "embedding", "encoder_stack", "csr_attention", "attention_backward"],
                     help="fused = the headline fused attention; softmax / layernorm = the bandwidth kernels (N=1)")
     ap.add_argument("--projections", default="tensor", choices=["tensor", "library"],

@@ -75,3 +75,26 @@ def test_two_ranks_gather_equals_unsharded(tmp_path, oracle):
     q, k, v = (oracle.fill_normal((B, L, H, d), 70 + i) for i in range(3))
     want = oracle.attention(q, k, v, luts, bs, np.float32(0.2), want=("o",))["o"]
     assert np.array_equal(got, want)
+
+
+def test_pair_slices_cover_a_rank_share_exactly():
+    """bench.py turns a rank's contiguous range of (batch, head) pairs into rectangles of the [B, L, H, d] tensors (the head
+    slices sfb_fused_attention_slice takes): every pair of the range exactly once, for every world size of the scaling run."""
+    import importlib.util
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("sfb_bench", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    spec = importlib.util.spec_from_file_location("sfb_sharding", os.path.join(root, "sf-bert_b200", "sharding.py"))
+    sh = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sh)
+    for B, H in ((4, 16), (3, 5), (1, 7)):
+        for world in (1, 2, 3, 4, 8):
+            seen = []
+            for rank in range(world):
+                start, stop = sh.partition_pairs(B, H, world, rank)
+                for (b0, b1, h0, h1) in bench.pair_slices(B, H, start, stop):
+                    assert 0 <= b0 < b1 <= B and 0 <= h0 < h1 <= H
+                    seen += [b * H + h for b in range(b0, b1) for h in range(h0, h1)]
+            assert sorted(seen) == list(range(B * H)) and len(seen) == B * H
