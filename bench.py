@@ -43,9 +43,9 @@ CONFIGS = {
 }
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the fused kernel, from the ncu capture
-# summarised in profiles/fused_attention_tc_stride_bertbase.md (not measured by this script)
-NCU_TRAFFIC_BYTES = {"stride_bertbase": 184.3e6}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the fused kernel, from one ncu capture of this
+# command line (a profiler cannot run inside the timed region; the line says so in "traffic_source")
+NCU_TRAFFIC_BYTES = {"stride_bertbase": 179.7e6}
 
 
 def peaks():
@@ -431,6 +431,7 @@ def run_ours(args):
                        "sharding": "batch x head, no collective on the data path", "l2": flush.note},
             "roofline": {"bound": "tensor", "achieved": round(per_gpu, 3), "peak": pk["tensor"], "unit": "TFLOP/s",
                          "frac": round(per_gpu / pk["tensor"], 4), "traffic": NCU_TRAFFIC_BYTES.get(args.config),
+                         "traffic_source": "one ncu capture of this command, not this run" if args.config in NCU_TRAFFIC_BYTES else None,
                          "peak_source": pk["source"] + " burst bf16",
                          "frac_of_sustained": round(per_gpu / pk["tensor_sustained"], 4),
                          "min_hbm_bytes": 4 * B * L * H * d * esz,

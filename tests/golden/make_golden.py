@@ -107,7 +107,9 @@ def cpu_reference_backward():
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    # the reference tree: first argument, else SFB_REFERENCE_DIR, else a directory `reference` beside this repository
+    ref = (sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SFB_REFERENCE_DIR")
+           or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference"))
     np.savez_compressed(os.path.join(HERE, "ref_uploads.npz"), **capture(ref))
     np.savez_compressed(os.path.join(HERE, "ref_cpu_attention.npz"), **cpu_reference())
     np.savez_compressed(os.path.join(HERE, "ref_cpu_backward.npz"), **cpu_reference_backward())

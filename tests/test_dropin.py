@@ -8,7 +8,8 @@ import subprocess
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = "/root/reference"
+# the reference tree: SFB_REFERENCE_DIR, else a directory `reference` beside this repository (tests skip when it is absent)
+REF = os.environ.get("SFB_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference")
 DRIVER = os.path.join(ROOT, "tests", "dropin", "driver")
 
 

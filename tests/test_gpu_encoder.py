@@ -61,3 +61,68 @@ def test_encoder_layer(sfb, oracle, order, dtype, bs, tol, proj):
     assert sfb.device_status() == 0
     want = _cpu_layer(oracle, x.float().cpu().numpy(), w, luts, heads, bs, order)
     assert np.abs(y - want).max() <= tol * max(1.0, np.abs(want).max())
+
+
+def _fill_small_params(oracle, w):
+    for name in ("bq", "bk", "bv", "bo", "b1", "b2", "be1", "be2"):
+        getattr(w, name).copy_(torch.from_numpy(oracle.fill_normal(tuple(getattr(w, name).shape), hash(name) % 1000, 0.1)))
+
+
+@pytest.mark.parametrize("name,dtype,L,heads,ffn,kind,kw,dev", [
+    ("bert_base_stride", "f16", 4096, 12, 3072, "stride", dict(band=4, every=8), ("LAYOUT_STRIDE", dict(p0=4, p1=8))),
+    ("bert_large_full", "bf16", 1024, 16, 4096, "full", dict(), ("LAYOUT_FULL", dict())),
+])
+def test_encoder_layer_at_the_benchmark_shapes(sfb, oracle, name, dtype, L, heads, ffn, kind, kw, dev):
+    """One post-LN encoder layer at the two shapes the metric names (hidden 768 / FFN 3072 / L 4096 on the stride layout,
+    hidden 1024 / FFN 4096 / L 1024 on the full layout), every kernel from this library, one sequence, every row checked
+    against the oracle chain in the reference's operator order (transformer_inference_part.cpp:210-239).  The bar is
+    element-wise: 3e-2 of the element plus 3e-2 of the output's root mean square (two 16-bit projections, the attention
+    and two LayerNorms compound their roundings; the LayerNorm output has unit scale)."""
+    enc = _encoder()
+    tdt = {"bf16": torch.bfloat16, "f16": torch.float16}[dtype]
+    hidden, nb = heads * 64, L // 64
+    lay = sfb.BlockLayout.generate(getattr(sfb, dev[0]), 1, nb, 64, **dev[1])
+    luts = oracle.lut_build(oracle.layout(kind, 1, nb, **kw))
+    w = enc.EncoderLayerWeights(hidden, ffn, tdt, seed=11, std=0.03)
+    _fill_small_params(oracle, w)
+    x = torch.from_numpy(oracle.fill_normal((1, L, hidden), 78)).cuda().to(tdt)
+    y = enc.encoder_layer(sfb, x, w, lay, heads, "post", "tensor").float().cpu().numpy()
+    assert sfb.device_status() == 0
+    want = _cpu_layer(oracle, x.float().cpu().numpy(), w, luts, heads, 64, "post")
+    oracle.assert_close_16bit(y, want, rel=3e-2, floor_of_rms=1.0)
+
+
+def test_embedding_two_layers_logits_at_the_bert_large_shape(sfb, oracle):
+    """The stack either side of the attention at the BERT-large shape on one sequence: embedding lookup + positions
+    (embedding.h:5-12, ewops.h:276-282), two post-LN layers, logits over the tied embedding table
+    (transformer_inference_part.cpp:201-209, 241), against the oracle chain."""
+    enc = _encoder()
+    tdt = torch.bfloat16
+    L, heads, hidden, ffn, vocab = 1024, 16, 1024, 4096, 30522
+    vpad = (vocab + 15) // 16 * 16
+    lay = sfb.BlockLayout.generate(sfb.LAYOUT_FULL, 1, L // 64, 64)
+    luts = oracle.lut_build(oracle.layout("full", 1, L // 64))
+    g = torch.Generator(device="cuda").manual_seed(21)
+    table = torch.zeros(vpad, hidden, device="cuda", dtype=tdt)
+    table[:vocab] = (0.05 * torch.randn(vocab, hidden, device="cuda", generator=g)).to(tdt)
+    pos = (0.05 * torch.randn(L, hidden, device="cuda", generator=g)).to(tdt)
+    ids = torch.randint(0, vocab, (1, L), device="cuda", dtype=torch.int32, generator=g)
+    ws = [enc.EncoderLayerWeights(hidden, ffn, tdt, seed=30 + i, std=0.03) for i in range(2)]
+    for w in ws:
+        _fill_small_params(oracle, w)
+    x, bad = sfb.embedding(table, ids, pos)
+    assert int(bad.item()) == 0
+    x0 = x.clone()
+    for w in ws:
+        x = enc.encoder_layer(sfb, x, w, lay, heads, "post", "tensor")
+    logits = sfb.linear_nt(x.view(L, hidden), table).float().cpu().numpy()
+    assert sfb.device_status() == 0
+    f32 = lambda t: t.float().cpu().numpy()
+    h = oracle.embedding(f32(table), ids.cpu().numpy(), f32(pos))
+    np.testing.assert_allclose(f32(x0), h, atol=1e-3, rtol=2.0 ** -8)   # one bf16 rounding of the sum
+    h = f32(x0)
+    for w in ws:
+        h = _cpu_layer(oracle, h, w, luts, heads, 64, "post")
+    oracle.assert_close_16bit(f32(x), h, rel=3e-2, floor_of_rms=1.0)
+    want = (h.reshape(L, hidden).astype(np.float64) @ f32(table).astype(np.float64).T).astype(np.float32)
+    oracle.assert_close_16bit(logits[:, :vocab], want[:, :vocab], rel=3e-2, floor_of_rms=1.0)
