@@ -32,11 +32,12 @@ int tc_fused_attention(cudaStream_t s, const void *nn_lut, const void *q, const 
                        const void *mask, int dtype, const AttnDims &p, float scale);
 int tc_status_fused(uint32_t *out);
 int tc_status_clear_fused();
-bool tc_sddmm_supported(int ab_dtype, uint32_t bs, const AttnDims &p);
+bool tc_sddmm_supported(int ab_dtype, uint32_t bs, const AttnDims &p, const void *a, const void *b, const void *c);
 int tc_sddmm(cudaStream_t s, const void *nt_lut, const void *a, const void *b, void *c, int ab_dtype, int c_dtype, const AttnDims &p);
-bool tc_spmm_supported(int a_dtype, int bc_dtype, uint32_t bs, const AttnDims &p, uint32_t max_lut);
+bool tc_spmm_supported(int a_dtype, int bc_dtype, uint32_t bs, const AttnDims &p, uint32_t max_lut, const void *a, const void *b,
+                       const void *c);
 int tc_spmm(cudaStream_t s, const void *lut, const void *a, const void *b, void *c, int dtype, const AttnDims &p, bool trans);
-bool tc_fused_p_supported(int ab_dtype, uint32_t bs, const AttnDims &p, float scale);
+bool tc_fused_p_supported(int ab_dtype, uint32_t bs, const AttnDims &p, float scale, const void *a, const void *b, const void *y);
 int tc_fused_p(cudaStream_t s, const void *nn_lut, const void *a, const void *b, const void *mask, void *y, int ab_dtype,
                int y_dtype, const AttnDims &p, float scale);
 int tc_sddmm_softmax_grad(cudaStream_t s, const void *nt_lut, const void *dout, const void *v, const void *pblk, const float *delta,

@@ -588,8 +588,11 @@ static bool tc_shape_ok(uint32_t bs, const AttnDims &p, uint32_t max_lut)
            (uint64_t)p.B * p.nb_a * 64 < (1ull << 31) && (uint64_t)p.B * p.H * p.blocks * 64 < (1ull << 31) - 64;
 }
 
-bool tc_sddmm_supported(int ab_dtype, uint32_t bs, const AttnDims &p)
+bool tc_sddmm_supported(int ab_dtype, uint32_t bs, const AttnDims &p, const void *a, const void *b, const void *c)
 {
+    // what the kernel cannot take goes to the CUDA-core kernel instead of failing: unequal block grids, operands the TMA
+    // cannot address (16-byte aligned a, b; 32-byte aligned c)
+    if ((((uintptr_t)a | (uintptr_t)b) & 15) != 0 || ((uintptr_t)c & 31) != 0 || p.nb_a != p.nb_b) return false;
     return (ab_dtype == SFB_BF16 || ab_dtype == SFB_F16) && bs == 64 && p.d == 64 && p.blocks > 0 &&
            (uint64_t)p.B * (p.nb_a > p.nb_b ? p.nb_a : p.nb_b) * 64 < (1ull << 31);
 }
@@ -645,8 +648,9 @@ int tc_sddmm_softmax_grad(cudaStream_t s, const void *nt_lut, const void *dout, 
     return check_launch("sfb_fused_sddmm_softmax_grad");
 }
 
-bool tc_fused_p_supported(int ab_dtype, uint32_t bs, const AttnDims &p, float scale)
+bool tc_fused_p_supported(int ab_dtype, uint32_t bs, const AttnDims &p, float scale, const void *a, const void *b, const void *y)
 {
+    if ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)y) & 31) != 0) return false;     // the CUDA-core kernel takes any alignment
     // the longest row is not an argument of the fused entry points: any row of the block grid must fit the union list
     return (ab_dtype == SFB_BF16 || ab_dtype == SFB_F16) && scale > 0.f && p.blocks > 0 &&
            tc_shape_ok(bs, p, p.nb_a <= tc::kMaxUnion / 2 ? p.nb_a : 0);
@@ -674,8 +678,10 @@ int tc_fused_p(cudaStream_t s, const void *nn_lut, const void *a, const void *b,
     return check_launch("sfb_fused_sddmm_softmax");
 }
 
-bool tc_spmm_supported(int a_dtype, int bc_dtype, uint32_t bs, const AttnDims &p, uint32_t max_lut)
+bool tc_spmm_supported(int a_dtype, int bc_dtype, uint32_t bs, const AttnDims &p, uint32_t max_lut, const void *a, const void *b,
+                       const void *c)
 {
+    if ((((uintptr_t)a | (uintptr_t)b) & 15) != 0 || ((uintptr_t)c & 31) != 0) return false;    // the CUDA-core kernel takes any alignment
     return a_dtype == bc_dtype && (a_dtype == SFB_BF16 || a_dtype == SFB_F16) && p.blocks > 0 && tc_shape_ok(bs, p, max_lut);
 }
 

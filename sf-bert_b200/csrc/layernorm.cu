@@ -192,7 +192,8 @@ extern "C" int sfb_bias_residual_layernorm(sfb_stream_t stream, void *out, void 
 namespace sfb {
 
 template <int DT>
-__global__ void __launch_bounds__(256) bias_gelu_kernel(void *__restrict__ out, const void *__restrict__ x,
+// out may be x itself (the header allows the call in place), so neither carries __restrict__
+__global__ void __launch_bounds__(256) bias_gelu_kernel(void *out, const void *x,
                                                        const float *__restrict__ bias, size_t total, uint32_t n)
 {
     constexpr int N = Vec8<DT>::N;

@@ -26,7 +26,7 @@ extern "C" int sfb_bst_sgemm_nt(sfb_stream_t stream, const void *lut, const void
     SFB_REQUIRE(lut_heads == 1 || lut_dim >= blocks, "%s: lut_dim %u smaller than blocks %u", who, lut_dim, blocks);
     if (blocks == 0) { clear_error(); return 0; }
     AttnDims p = {batch_dim, head_dim, state_dim, ctx_blks_a, ctx_blks_b, blocks, lut_heads > 1 ? lut_dim : 0, 0};
-    if (tc_sddmm_supported(ab_dtype, block_size, p)) return tc_sddmm(as_stream(stream), lut, a, b, c, ab_dtype, c_dtype, p);
+    if (tc_sddmm_supported(ab_dtype, block_size, p, a, b, c)) return tc_sddmm(as_stream(stream), lut, a, b, c, ab_dtype, c_dtype, p);
     return simt_sddmm_nt(as_stream(stream), lut, a, b, c, ab_dtype, c_dtype, block_size, p);
 }
 
@@ -66,7 +66,7 @@ extern "C" int sfb_bst_sgemm_xn(sfb_stream_t stream, const void *lut, const void
     if (ctx_blks_c == 0) { clear_error(); return 0; }
     AttnDims p = {batch_dim, head_dim, state_dim, ctx_blks_c, ctx_blks_b, blocks, lut_heads > 1 ? lut_dim : 0, 0};
     const bool trans = op == SFB_TN_OP;
-    if (tc_spmm_supported(a_dtype, bc_dtype, block_size, p, max_lut)) return tc_spmm(as_stream(stream), lut, a, b, c, a_dtype, p, trans);
+    if (tc_spmm_supported(a_dtype, bc_dtype, block_size, p, max_lut, a, b, c)) return tc_spmm(as_stream(stream), lut, a, b, c, a_dtype, p, trans);
     return simt_spmm_nn(as_stream(stream), lut, a, b, c, a_dtype, bc_dtype, block_size, p, trans);
 }
 
@@ -100,7 +100,7 @@ extern "C" int sfb_fused_sddmm_softmax(sfb_stream_t stream, const void *nn_lut, 
     // the nn_lut of head h starts at h * (lut_dim + ctx_blks_a)  (fusion_blocksparse.h:1245)
     AttnDims p = {batch_dim, head_dim, state_dim, ctx_blks_a, ctx_blks_b, blocks, lut_heads > 1 ? lut_dim + ctx_blks_a : 0,
                   mask_heads > 1 ? blocks * block_size : 0};
-    if (ctx_blks_a == ctx_blks_b && tc_fused_p_supported(ab_dtype, block_size, p, scale))
+    if (ctx_blks_a == ctx_blks_b && tc_fused_p_supported(ab_dtype, block_size, p, scale, a, b, y))
         return tc_fused_p(as_stream(stream), nn_lut, a, b, mask, y, ab_dtype, y_dtype, p, scale);
     return simt_fused_sddmm_softmax(as_stream(stream), nn_lut, a, b, mask, y, ab_dtype, y_dtype, block_size, p, scale);
 }

@@ -100,3 +100,40 @@ def test_second_device_first(sfb, oracle):
     o0 = sfb.fused_attention(q.to("cuda:0"), k.to("cuda:0"), v.to("cuda:0"), lay0, 0.125)
     y0 = sfb.linear(x.to("cuda:0"), w.to("cuda:0"))
     assert torch.equal(o0.cpu(), o1.cpu()) and torch.equal(y0.cpu(), y1.cpu())
+
+
+def test_operands_the_tma_cannot_address_fall_back(sfb):
+    """A score tensor that is 16-byte but not 32-byte aligned (and operands at an odd element) cannot go through the TMA
+    kernels; the same call then runs on the CUDA cores instead of being rejected, with the same result up to rounding."""
+    B, H, L, d = 1, 2, 512, 64
+    lay = sfb.BlockLayout.generate(sfb.LAYOUT_STRIDE, 1, L // 64, 64, p0=3, p1=4)
+    gen = torch.Generator(device="cuda").manual_seed(17)
+    q, k, v = (torch.randn(B, L, H, d, device="cuda", generator=gen).to(torch.bfloat16) for _ in range(3))
+    s_ref = sfb.bst_sgemm_nt(q, k, lay, torch.bfloat16)
+    n = s_ref.numel()
+    buf = torch.empty(n + 8, dtype=torch.bfloat16, device="cuda")
+    s_off = buf[8:].view_as(s_ref)                       # 16 bytes past a 256-byte boundary
+    assert s_off.data_ptr() % 32 == 16
+    p = lambda t: C.c_void_p(t.data_ptr())
+    rc = sfb.lib.sfb_bst_sgemm_nt(C.c_void_p(torch.cuda.current_stream().cuda_stream), p(lay.nt_lut), p(q), p(k), p(s_off), sfb.BF16, sfb.BF16,
+                                  64, lay.blocks, B, lay.nb, lay.nb, H, d, 1, lay.blocks)
+    assert rc == 0, sfb.lib.sfb_last_error()
+    assert float((s_off.float() - s_ref.float()).abs().max()) <= 2.0 ** -7 * float(s_ref.float().abs().max())
+    # fused attention with q two bytes off: CUDA cores, same numbers at the 16-bit bar
+    qb = torch.empty(q.numel() + 8, dtype=torch.bfloat16, device="cuda")
+    q_off = qb[1:1 + q.numel()].view_as(q)
+    q_off.copy_(q)
+    want = sfb.fused_attention(q, k, v, lay, 0.125).float()
+    got = sfb.fused_attention(q_off, k, v, lay, 0.125).float()
+    assert float((got - want).abs().max()) <= 2e-2 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_bias_gelu_in_place(sfb, dtype):
+    gen = torch.Generator(device="cuda").manual_seed(23)
+    x = torch.randn(300, 256, device="cuda", generator=gen).to(dtype)
+    bias = torch.randn(256, device="cuda", generator=gen)
+    want = sfb.bias_gelu(x, bias)
+    y = x.clone()
+    sfb.bias_gelu(y, bias, out=y)
+    assert torch.equal(y, want)
