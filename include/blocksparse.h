@@ -20,6 +20,7 @@ namespace sfb_dropin {
 template <typename T> struct dtype_of;
 template <> struct dtype_of<float> { static const int value = SFB_F32; };
 template <> struct dtype_of<bhalf> { static const int value = SFB_BF16; };
+template <> struct dtype_of<ehalf> { static const int value = SFB_F16; };
 }  // namespace sfb_dropin
 
 /* blocksparse.h:425-432 */
@@ -97,6 +98,40 @@ inline void magicu64(uint d, uint &magic, uint &shift)
     sfb_magicu64(d, &m, &s);
     magic = m;
     shift = s;
+}
+
+/* ---- Additions: 16-bit activations (no counterpart in the reference, whose Q, K, V, O are fp32) ---------------
+ * The same operators with Q, K, V, O as bhalf (bf16) or ehalf (fp16): with block_size 64 and state_dim 64 they run on
+ * the tensor cores.  QT is deduced from the pointers. */
+template <typename QT>
+inline bool bst_sgemm_nt(CUstream stream, const uint2 *lut, const QT *a, const QT *b, bhalf *c, uint block_size, uint blocks,
+                         uint batch_dim, uint ctx_blks_a, uint ctx_blks_b, uint head_dim, uint state_dim, uint lut_heads,
+                         uint lut_dim)
+{
+    return sfb_bst_sgemm_nt(stream, lut, a, b, c, sfb_dropin::dtype_of<QT>::value, SFB_BF16, block_size, blocks, batch_dim,
+                            ctx_blks_a, ctx_blks_b, head_dim, state_dim, lut_heads, lut_dim) == 0;
+}
+
+template <typename PT, typename QT>
+inline bool bst_sgemm_xn(CUstream stream, const uint2 *lut, const PT *a, const QT *b, QT *c, uint block_size, uint blocks,
+                         uint batch_dim, uint ctx_blks_b, uint ctx_blks_c, uint head_dim, uint state_dim, uint lut_heads,
+                         uint lut_dim, uint op, uint magic, uint shift, uint max_lut)
+{
+    return sfb_bst_sgemm_xn(stream, lut, a, b, c, sfb_dropin::dtype_of<PT>::value, sfb_dropin::dtype_of<QT>::value, block_size,
+                            blocks, batch_dim, ctx_blks_b, ctx_blks_c, head_dim, state_dim, lut_heads, lut_dim, op, magic, shift,
+                            max_lut) == 0;
+}
+
+/* One call for what the reference's test programs do inline (stride_fusion_test.cu:77-227): nt_lut, nn_lut, rblk_lut,
+ * nn_max and, when pred >= 0, the element masks in both orders.  Any output pointer may be NULL. */
+inline bool sfb_build_lut(CUstream stream, const uchar *layout, uint heads, uint ctx_blks, uint block_size, uint blocks,
+                          uint2 *nt_lut, uint2 *nn_lut, uint2 *rblk_lut, uint *nn_max, uint *status, int pred, uint ctx,
+                          void *mask_np, void *mask_t)
+{
+    if (sfb_lut_build(stream, layout, heads, ctx_blks, blocks, nt_lut, nn_lut, rblk_lut, nn_max, status) != 0) return false;
+    if (pred >= 0 && (mask_np || mask_t))
+        return sfb_mask_pack(stream, nt_lut, heads, blocks, block_size, pred, ctx, mask_np, mask_t) == 0;
+    return true;
 }
 
 #endif

@@ -104,4 +104,18 @@ bool fusion_attention(CUstream stream, const uint2 *nt_lut, const float *a, cons
                                head_dim, state_dim, lut_heads, lut_dim, mask_heads, scale, max_lut) == 0;
 }
 
+/* ---- Additions: 16-bit activations (no counterpart in the reference) ------------------------------------------
+ * fusion_attention with Q, K, V, O as bhalf (bf16) or ehalf (fp16); with block_size 64 and state_dim 64 this is the
+ * tensor-core kernel.  Mask words are 64-bit for block_size 64 (as fusion_attention2_64 takes them). */
+template <typename T, typename V, typename QT>
+bool fusion_attention(CUstream stream, const uint2 *nt_lut, const QT *a, const QT *b, bhalf *c, const uint2 *nn_lut,
+                      int *rblk_flag, int *rblk_flag1, const void *Mask, float *Max, float *Sum, T *Y, const QT *e, QT *f,
+                      uint block_size, uint blocks, uint batch_dim, uint ctx_blks_a, uint ctx_blks_b, uint ctx_blks_c,
+                      uint head_dim, uint state_dim, uint lut_heads, uint lut_dim, uint mask_heads, float scale, uint max_lut)
+{
+    (void)nt_lut; (void)c; (void)rblk_flag; (void)rblk_flag1; (void)Max; (void)Sum; (void)Y; (void)ctx_blks_b; (void)ctx_blks_c;
+    return sfb_fused_attention(stream, nn_lut, a, b, e, f, Mask, sfb_dropin::dtype_of<QT>::value, block_size, blocks, batch_dim,
+                               ctx_blks_a, head_dim, state_dim, lut_heads, lut_dim, mask_heads, scale, max_lut) == 0;
+}
+
 #endif

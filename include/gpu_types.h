@@ -29,6 +29,14 @@ typedef struct __align__(4) bhalf2 {
     uint x;
 } bhalf2;
 
+/* fp16 storage (the OpenAI code the reference derives from calls it ehalf): an ADDITION, used only by the 16-bit
+ * overloads below the reference's own signatures */
+typedef struct __align__(2) ehalf {
+    __host__ __device__ ehalf() {}
+    __host__ __device__ ehalf(ushort v) : x(v) {}
+    ushort x;
+} ehalf;
+
 #define NT_OP 0
 #define NN_OP 1
 #define TN_OP 2

@@ -7,9 +7,9 @@
 // memory, no waiting on other CTAs (the reference's fused kernels spin on counters in global memory,
 // fusion_blocksparse.h:224-366).  Per key block of a stream:
 //     S  = Q . K^T            tcgen05.mma, A and B from shared memory (TMA, 128-byte swizzle), accumulator in TMEM
-//     P  = exp2(S*c - m)      128 threads, one query row each, straight out of TMEM; the row sum is kept in fp32
-//                             registers; a share of the exponentials runs as a cubic on the FMA pipe because the
-//                             MUFU is the unit that bounds this kernel; P goes back to TMEM as 16-bit pairs
+//     P  = exp2(S*c - m)      128 threads, one query row each, straight out of TMEM (fp32 ex2.approx; the packed
+//                             fp16 form measured slower); the row sum is kept in fp32 registers; P goes back to
+//                             TMEM as 16-bit pairs
 //     O += P . V              tcgen05.mma, P as the A operand from TMEM, V from shared memory as an MN-major operand
 // TMEM per stream (160 columns): two score buffers that overlap by half, S_even = [0,64) and S_odd = [32,96), with
 // P_even = [0,32) and P_odd = [64,96): S(t+1) never touches P(t), so the next scores are produced while the
@@ -25,32 +25,15 @@
 // Every wait is bounded; on a timeout the CTA records a status word and leaves through the common teardown.
 #include "tc_common.cuh"
 
-// every SFB_TC_POLY-th pair of exponentials runs on the FMA pipe (0 = all on the MUFU)
+// every SFB_TC_POLY-th pair of exponentials runs as a cubic on the FMA pipe (0 = all on the MUFU, the default: with
+// every fourth pair moved the kernel was no faster, the MUFU is not what holds it back)
 #ifndef SFB_TC_POLY
 #define SFB_TC_POLY 0
-#endif
-#ifndef SFB_TC_PREFETCH
-#define SFB_TC_PREFETCH 0
-#endif
-#ifndef SFB_TC_DEFER
-#define SFB_TC_DEFER 0
 #endif
 
 namespace sfb {
 
 namespace tc {
-
-#ifdef SFB_TC_TRACE
-// development only: a timeline of stream 0 of CTA 0 (softmax warp 0: slots 0-5, issuer: slots 8-14 of 16 per step)
-__device__ long long g_trace[16 * 256 + 16 * 256];   // second table: per quarter, s_full seen / p_full arrival
-#define TRACE_SM(step, slot) do { if (blockIdx.x == 0 && warp == 0 && lane == 0 && (step) < 256u) g_trace[(step) * 16 + (slot)] = clock64(); } while (0)
-#define TRACE_Q(step, slot) do { if (blockIdx.x == 0 && s == 0 && lane == 0 && (step) < 256u) g_trace[16 * 256 + (step) * 16 + (slot)] = clock64(); } while (0)
-#define TRACE_IS(step, slot) do { if (blockIdx.x == 0 && s == 0 && (step) < 256u) g_trace[(step) * 16 + (slot)] = clock64(); } while (0)
-#else
-#define TRACE_SM(step, slot) do {} while (0)
-#define TRACE_Q(step, slot) do {} while (0)
-#define TRACE_IS(step, slot) do {} while (0)
-#endif
 
 constexpr int kStreams = 3;
 constexpr int kMaxU = 256;                      // key blocks a row pair may touch in this kernel
@@ -215,12 +198,6 @@ __device__ __forceinline__ bool mbar_wait2(uint64_t *bar_a, uint32_t par_a, uint
     const bool a = mbar_try_wait(bar_a, par_a), b = mbar_try_wait(bar_b, par_b);
     if (a && b) return true;
     return (a || bar_wait(bar_a, par_a, abort_flag, code)) && (b || bar_wait(bar_b, par_b, abort_flag, code));
-}
-
-// one look at a barrier for a whole warp with one outcome for all lanes; never suspends the warp
-__device__ __forceinline__ bool warp_test_wait(uint64_t *bar, uint32_t parity)
-{
-    return __all_sync(0xffffffffu, mbar_test_wait(bar, parity));
 }
 
 // The union of the key blocks of block-rows 2*pair and 2*pair+1, built by ONE warp: the upper row's blocks in LUT
@@ -404,11 +381,7 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     UEntry *lists = (UEntry *)(smem + kOffList);
 
     const uint32_t hw_warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef SFB_TC_CTRL_FIRST
-    const uint32_t warp = (hw_warp + 12) % 20;     // role index: the control warps get the lowest hardware warp ids
-#else
     const uint32_t warp = hw_warp;
-#endif
     const uint32_t L = p.nb * 64;
     volatile uint32_t *abort_flag = &sh->abort_flag;
     const uint32_t fmt = BF16 ? 1u : 0u;
@@ -492,18 +465,15 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             auto issue_qk = [&](uint32_t gg) -> bool {
                 const uint32_t b2 = gg & 1;
                 // S(gg) overlaps half of S(gg-1): that one must be in the softmax threads' registers
-                TRACE_IS(gg, 8);
                 if (gg >= 1 ? !mbar_wait2(&st->s_free, (gg - 1) & 1, &st->k_full[b2], (gg >> 1) & 1, abort_flag, 4)
                             : !bar_wait(&st->k_full[b2], (gg >> 1) & 1, abort_flag, 3))
                     return false;
-                TRACE_IS(gg, 10);
                 tcgen05_fence_after();
                 const uint64_t k_desc = smem_desc_sw128(smem_u32(smem + kOffK + (s * 2 + b2) * kTileBytes));
 #pragma unroll
                 for (uint32_t kk = 0; kk < 4; kk++)   // 16 of the 64 head elements per MMA: +32 bytes inside the swizzled row
                     umma_f16(tbase + 32 * b2, q_desc + 2 * kk, k_desc + 2 * kk, idesc_qk, kk);
                 umma_commit(&st->qk_done[b2]);
-                TRACE_IS(gg, 11);
                 return true;
             };
             for (uint32_t k = 0; alive; k++) {
@@ -523,14 +493,7 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                         }
                         // the accumulator still holds the previous item's O until its epilogue has read it
                         if (t == 0 && kq >= 1 && !bar_wait(&st->o_free, (kq - 1) & 1, abort_flag, 11)) { alive = false; break; }
-#ifdef SFB_TC_TRACE
-                        if (!bar_wait(&st->p_full[b2], (gg >> 1) & 1, abort_flag, 5)) { alive = false; break; }
-                        TRACE_IS(gg, 12);
-                        if (!bar_wait(&st->v_full[b2], (gg >> 1) & 1, abort_flag, 5)) { alive = false; break; }
-#else
                         if (!mbar_wait2(&st->p_full[b2], (gg >> 1) & 1, &st->v_full[b2], (gg >> 1) & 1, abort_flag, 5)) { alive = false; break; }
-#endif
-                        TRACE_IS(gg, 13);
                         tcgen05_fence_after();
                         const uint64_t v_desc = smem_desc_sw128(smem_u32(smem + kOffV + (s * 2 + b2) * kTileBytes));
 #pragma unroll
@@ -538,7 +501,6 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                             umma_f16_ts(t_o, tbase + 64 * b2 + 8 * kk, v_desc + 128 * kk, idesc_pv, (t | kk) ? 1u : 0u);
                         umma_commit(&st->pv_done[b2]);
                         if (t + 1 == T) umma_commit(&st->o_final);
-                        TRACE_IS(gg, 14);
                     }
                     g += T;
                     kq++;
@@ -563,10 +525,9 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
         uint32_t g = 0, kq = 0, n_epi = 0;
         bool alive = true;
 
-        // The epilogue of an item: O / row sum -> the stream's staging tile -> (value producer) one TMA store per row pair.
-        // It runs AFTER the first softmax step of the stream's next item: by then the item's last O product has long
-        // completed, so nothing waits for the tensor core, and the next item's first products were not held up.
-        // 16 accumulator columns at a time: the registers of the next step's scores stay live around it.
+        // The epilogue of an item: O / row sum -> the stream's staging tile -> (value producer) one TMA store per row pair,
+        // 16 accumulator columns at a time.  (Running it behind the next item's first softmax step, so that nothing waits
+        // for the item's last O product, was built and measured: slower.)
         auto epilogue = [&](bool has_data, uint32_t e_id, uint64_t l0, uint64_t l1) -> bool {
             const Item e_it = decode_item(e_id, p);
             const uint32_t e_pair = e_it.pair, e_b = e_it.b, e_h = e_it.h;
@@ -624,9 +585,6 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             return true;
         };
 
-        bool pend = false, pre = false;                    // an epilogue is owed / the next step's scores are in registers
-        uint32_t pend_id = 0;
-        uint64_t pend_l0 = 0, pend_l1 = 0;
         uint32_t sr[64];                                   // this row of S(t), fp32 bits
         for (uint32_t k = 0; alive; k++) {
             const uint32_t id = item_id(k, s);
@@ -635,35 +593,19 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             const uint32_t T = st->list_n[k & 1];
             const UEntry *list = lists + (s * 2 + (k & 1)) * kMaxU;
             const uint32_t item_h = HAS_MASK ? decode_item(id, p).h : 0u;
-            if (T == 0) {
-                if (pend && !epilogue(true, pend_id, pend_l0, pend_l1)) break;
-                pend = false;
-                if (!epilogue(false, id, 0ull, 0ull)) break;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&st->list_free[k & 1]);
-                continue;
-            }
             float m_used = -INFINITY;
             uint64_t lacc0 = 0, lacc1 = 0;                 // four partial row sums (two packed pairs)
             for (uint32_t t = 0; t < T; t++) {
                 const uint32_t gg = g + t, b2 = gg & 1;
                 const uint32_t t_s = tbase + 32 * b2, t_p = tbase + 64 * b2;
-                TRACE_SM(gg, 0);
-                if (!pre) {
-                    if (!bar_wait_warp(&st->qk_done[b2], (gg >> 1) & 1, abort_flag, 6)) { alive = false; break; }
-                    TRACE_SM(gg, 1);
-                    tcgen05_fence_after();
-                    TMEM_LD_32((sr), t_s);
-                    TMEM_LD_32((sr + 32), t_s + 32);
-                    tmem_wait_ld();
-                }
-                pre = false;
+                if (!bar_wait_warp(&st->qk_done[b2], (gg >> 1) & 1, abort_flag, 6)) { alive = false; break; }
+                tcgen05_fence_after();
+                TMEM_LD_32((sr), t_s);
+                TMEM_LD_32((sr + 32), t_s + 32);
+                tmem_wait_ld();
                 tcgen05_fence_before();
                 mbar_arrive(&st->s_free);                  // the buffer may be overwritten from here on
-                TRACE_SM(gg, 2);
                 const bool mine = (list[t].col_flags >> (30 + half)) & 1;     // the same for the whole warp
-                // is the next step's S there already?  Then its two halves are fetched while this step's exponentials run
-                bool fetch = false;
                 if (mine) {
                     if (HAS_MASK) {
                         const uint64_t mw = p.mask[(size_t)item_h * p.mask_stride + (size_t)list[t].blk[half] * 64 + (r & 63)];
@@ -711,7 +653,6 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                     }
                     const float neg_m = m_used > -INFINITY ? -m_used : 0.f;
                     const uint64_t nm2 = pk64(neg_m, neg_m);
-                    TRACE_SM(gg, 3);
 #pragma unroll
                     for (int hh = 0; hh < 2; hh++) {
                         uint32_t pk[16];
@@ -720,9 +661,6 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                             const int c = hh * 32 + 2 * j;
                             const uint64_t x = fma2p(pk64(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), sl2, nm2);
                             float e0, e1;
-#if defined(SFB_TC_ABL) && SFB_TC_ABL == 1
-                            up64(x, e0, e1);      // timing experiment only: no exponentials
-#else
                             if (POLY > 0 && (j % (POLY > 0 ? POLY : 1)) == (POLY > 0 ? POLY : 1) - 1) {
                                 exp2_fma_pair(x, e0, e1);
                             } else {
@@ -731,20 +669,11 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                                 e0 = ex2_approx(x0);
                                 e1 = ex2_approx(x1);
                             }
-#endif
                             if (j & 1) lacc1 = add2p(lacc1, pk64(e0, e1));
                             else lacc0 = add2p(lacc0, pk64(e0, e1));
                             pk[j] = pack_pair<BF16>(e0, e1);
                         }
                         TMEM_ST_16(t_p + hh * 16, (pk));
-                        if (hh == 0) {
-                            // the first half of the registers is free: the next step's scores start their way into them
-                            fetch = SFB_TC_PREFETCH && t + 1 < T && warp_test_wait(&st->qk_done[b2 ^ 1], ((gg + 1) >> 1) & 1);
-                            if (fetch) {
-                                tcgen05_fence_after();
-                                TMEM_LD_32((sr), tbase + 32 * (b2 ^ 1));
-                            }
-                        }
                     }
                 } else {
                     uint32_t pk[16];
@@ -752,43 +681,17 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                     for (int j = 0; j < 16; j++) pk[j] = 0u;
                     TMEM_ST_16(t_p, (pk));
                     TMEM_ST_16(t_p + 16, (pk));
-                    fetch = SFB_TC_PREFETCH && t + 1 < T && warp_test_wait(&st->qk_done[b2 ^ 1], ((gg + 1) >> 1) & 1);
-                    if (fetch) {
-                        tcgen05_fence_after();
-                        TMEM_LD_32((sr), tbase + 32 * (b2 ^ 1));
-                    }
                 }
-                if (fetch) TMEM_LD_32((sr + 32), tbase + 32 * (b2 ^ 1) + 32);
-                TRACE_SM(gg, 4);
                 tmem_wait_st();
                 tcgen05_fence_before();
                 mbar_arrive(&st->p_full[b2]);
-                TRACE_SM(gg, 5);
-                TRACE_Q(gg, 4 + quarter);
-                if (fetch) {
-                    // no load is left in flight across the loop's back edge: the registers it fills are read right after
-                    tmem_wait_ld();
-                    pre = true;
-                }
-                if (t == 0 && pend) {
-                    if (!epilogue(true, pend_id, pend_l0, pend_l1)) { alive = false; break; }
-                    pend = false;
-                }
             }
             if (!alive) break;
             g += T;
-            if (SFB_TC_DEFER) {
-                pend = true;
-                pend_id = id;
-                pend_l0 = lacc0;
-                pend_l1 = lacc1;
-            } else if (!epilogue(true, id, lacc0, lacc1)) {
-                break;
-            }
+            if (!epilogue(T > 0, id, lacc0, lacc1)) break;
             __syncwarp();
             if (lane == 0) mbar_arrive(&st->list_free[k & 1]);
         }
-        if (alive && pend) epilogue(true, pend_id, pend_l0, pend_l1);
     }
 
     // ---- teardown (also the way out after a timeout) ----
@@ -859,13 +762,6 @@ int tc_fused_attention(cudaStream_t s, const void *nn_lut, const void *q, const 
     else fused_attention_tc_kernel<false, false, SFB_TC_POLY><<<grid, kThreads, kSmemBytes, s>>>(qm, km, vm, om, prm);
     return check_launch("sfb_fused_attention");
 }
-
-#ifdef SFB_TC_TRACE
-extern "C" int sfb_debug_trace(long long *out, int n)
-{
-    return cudaMemcpyFromSymbol(out, tc::g_trace, sizeof(long long) * n) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 int tc_status_clear_fused()
 {
