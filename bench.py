@@ -860,6 +860,75 @@ def run_encoder_layer(args, sfb, cfg, pk, flush):
         "gpu_launches": args.steps * 4, "clocks": clocks}), flush=True)
 
 
+
+# ------------------------------------------------------------------------------------------------
+def run_dropin(args):
+    """The reference's own call signature on the reference's own micro-benchmark shape (stride_fusion_test.cu:19-24:
+    B=32, H=4, d=128, 32x32 blocks, L=1024, fp32 Q/K/V, its sawtooth "stride" layout): the operators a program that
+    includes include/blocksparse.h / include/fusion_blocksparse.h reaches (their bodies are one-line forwarders to the
+    C ABI entry points called here with the same arguments) timed beside the reference's own unfused GPU operators
+    compiled for sm_100a (oracle/_ref/libsfb_ref_gpu.so) on the same inputs.  fp32 operands run on this library's
+    CUDA-core kernels (tensor-core arithmetic cannot meet fp32 parity); the reference's fused kernels spin on global
+    flags without a bound and are not run."""
+    import torch
+    import __graft_entry__ as ge
+    sfb = ge.load_package()
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as O
+    torch.cuda.set_device(0)
+    B, H, L, d, bs = 32, 4, 1024, 128, 32
+    nb = L // bs
+    lay = sfb.BlockLayout.generate(sfb.LAYOUT_SAWTOOTH, 1, nb, bs, p0=8)
+    gen = torch.Generator(device="cuda").manual_seed(1234)
+    q, k, v = (torch.randn(B, L, H, d, device="cuda", generator=gen) for _ in range(3))
+    scale = 1.0 / d ** 0.5
+    flush = L2Flush(torch, args.l2_flush)
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for a, b_ in ev:
+            flush.fill_(1)
+            a.record()
+            fn()
+            b_.record()
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b_) for a, b_ in ev) / args.steps
+
+    def trio():
+        s_ = sfb.bst_sgemm_nt(q, k, lay, torch.bfloat16)
+        p_ = sfb.masked_softmax(s_, lay, scale, torch.bfloat16)
+        return sfb.bst_sgemm_xn(p_, v, lay)
+
+    ours = {
+        "fusion_attention2<float,float2> (SDDMM + softmax, fp32 P out)": timed(lambda: sfb.fused_sddmm_softmax(q, k, lay, scale, torch.float32)),
+        "bst_sgemm_nt + BlocksparseMaskedSoftmax<bhalf> + bst_sgemm_xn": timed(trio),
+        "fusion_attention (SDDMM + softmax + SpMM in one launch)": timed(lambda: sfb.fused_attention(q, k, v, lay, scale)),
+    }
+    ref_ms = None
+    if O.ref_gpu() is not None:
+        ref = O.RefGpuAttention(O.layout("sawtooth", 1, nb, chunks=8))
+        ref.alloc(q)
+        ref_ms = timed(lambda: ref.launch(q, k, v, scale))
+        got = sfb.fused_attention(q, k, v, lay, scale)
+        err = float((got - ref.o).abs().max() / ref.o.abs().max())
+    flops = 4.0 * bs * bs * d * lay.blocks * B * H
+    best = ours["fusion_attention (SDDMM + softmax + SpMM in one launch)"]
+    print(json.dumps({
+        "metric": "block-sparse attention TFLOP/s on nonzero blocks", "value": round(flops / (best * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(best, 4), "higher_is_better": True,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "reference micro-benchmark shape (stride_fusion_test.cu:19-24)", "B": B, "H": H, "L": L, "d": d, "block": bs,
+                   "layout": "LAYOUT_SAWTOOTH chunks=8", "nnz_blocks_per_head": lay.blocks, "l2": flush.note},
+        "ours_ms": {k_: round(v_, 4) for k_, v_ in ours.items()},
+        "reference_gpu": None if ref_ms is None else {
+            "ms_per_step": round(ref_ms, 4), "value": round(flops / (ref_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+            "what": "reference bst_sgemm_nt + BlocksparseMaskedSoftmax<bhalf> + bst_sgemm_xn(NN) compiled for sm_100a, same inputs",
+            "max_rel_diff_of_O": round(err, 5)},
+        "gpu_launches": args.steps * 5}), flush=True)
+
 # ------------------------------------------------------------------------------------------------
 def cpu_reference_sample(cfg, budget_s, steps):
     """Times the reference's CPU attention operators (multiheadmatmulNT -> softmax -> multiheadmatmulNN,
@@ -1051,7 +1120,7 @@ if __name__ == "__main__":
     ap.add_argument("--config", default="stride_bertbase", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the encoder-layer / encoder-stack / strong-scaling legs of the default line")
-    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer", "softmax_grad", "spmm_tn", "linear", "embedding", "encoder_stack", "csr_attention", "attention_backward"],
+    ap.add_argument("--kernel", default="fused", choices=["fused", "softmax", "layernorm", "sddmm", "spmm", "fused_p", "encoder_layer", "softmax_grad", "spmm_tn", "linear", "embedding", "encoder_stack", "csr_attention", "attention_backward", "dropin"],
                     help="fused = the headline fused attention; softmax / layernorm = the bandwidth kernels (N=1)")
     ap.add_argument("--projections", default="tensor", choices=["tensor", "library"],
                     help="--kernel encoder_layer: the layer's GEMMs on this library's tcgen05 kernel or on the GEMM library")
@@ -1064,6 +1133,8 @@ if __name__ == "__main__":
         run_reference(a)
     elif a.kernel == "encoder_stack":
         run_encoder_stack(a)
+    elif a.kernel == "dropin":
+        run_dropin(a)
     elif a.kernel != "fused":
         run_bandwidth_kernel(a)
     else:

@@ -16,6 +16,53 @@
 
 static float bf(ushort v) { unsigned u = (unsigned)v << 16; float f; memcpy(&f, &u, 4); return f; }
 
+// The additions below the reference's surface: sfb_build_lut (LUTs + masks in one call, on the device) and the 16-bit
+// overload of fusion_attention (bf16 Q, K, V, O; 64x64 blocks, 64-wide heads: the tensor-core kernel), on the all-ones
+// known answer with the causal element mask on the diagonal blocks: every output 1.
+static size_t sixteen_bit_additions()
+{
+    const uint B = 2, H = 3, d = 64, bs = 64, nb = 6, L = nb * bs;
+    std::vector<uchar> lay(nb * nb, 0);
+    uint blocks = 0;
+    for (uint i = 0; i < nb; i++)
+        for (uint j = 0; j <= i; j++) { lay[i * nb + j] = 1; blocks++; }
+    uchar *d_lay;
+    uint2 *nt, *nn, *rblk;
+    uint *nn_max, *status;
+    uint64 *mask_np, *mask_t;
+    cudaMalloc(&d_lay, nb * nb);
+    cudaMemcpy(d_lay, lay.data(), nb * nb, cudaMemcpyHostToDevice);
+    cudaMalloc(&nt, sizeof(uint2) * blocks);
+    cudaMalloc(&nn, sizeof(uint2) * (nb + blocks));
+    cudaMalloc(&rblk, sizeof(uint2) * blocks);
+    cudaMalloc(&nn_max, sizeof(uint));
+    cudaMalloc(&status, sizeof(uint));
+    cudaMemset(status, 0, sizeof(uint));
+    cudaMalloc(&mask_np, sizeof(uint64) * blocks * bs);
+    cudaMalloc(&mask_t, sizeof(uint64) * blocks * bs);
+    bool ok = sfb_build_lut(0, d_lay, 1, nb, bs, blocks, nt, nn, rblk, nn_max, status, SFB_MASK_CAUSAL_DIAG, 0, mask_np, mask_t);
+    uint h_max = 0, h_status = 1;
+    cudaMemcpy(&h_max, nn_max, sizeof(uint), cudaMemcpyDeviceToHost);
+    cudaMemcpy(&h_status, status, sizeof(uint), cudaMemcpyDeviceToHost);
+    const size_t n = (size_t)B * L * H * d;
+    std::vector<bhalf> one(n, bhalf((ushort)0x3f80));    // 1.0 in bf16
+    bhalf *q, *o;
+    cudaMalloc(&q, sizeof(bhalf) * n);
+    cudaMalloc(&o, sizeof(bhalf) * n);
+    cudaMemcpy(q, one.data(), sizeof(bhalf) * n, cudaMemcpyHostToDevice);
+    cudaMemset(o, 0, sizeof(bhalf) * n);
+    ok = ok && fusion_attention<float, float2>(0, nt, q, q, (bhalf *)0, nn, (int *)0, (int *)0, mask_np, (float *)0, (float *)0,
+                                               (float *)0, q, o, bs, blocks, B, nb, nb, nb, H, d, 1, blocks, 1, 0.125f, h_max);
+    uint word = 1;
+    ok = ok && sfb_device_status(&word) == 0;
+    std::vector<bhalf> o_h(n);
+    cudaMemcpy(o_h.data(), o, sizeof(bhalf) * n, cudaMemcpyDeviceToHost);
+    size_t bad = (ok && h_max == nb && h_status == 0 && word == 0) ? 0 : 1;
+    if (bad) printf("16-bit additions: call failed (%s), nn_max %u status %u word %u\n", sfb_last_error(), h_max, h_status, word);
+    for (size_t i = 0; i < n; i++) bad += fabsf(bf(o_h[i].x) - 1.0f) > 1.0f / 128;
+    return bad;
+}
+
 int main()
 {
     const uint batch_dim = 2, heads_ = 4, head_state_ = 128, blk_size_ = 32, seq_len = 320;
@@ -178,6 +225,7 @@ int main()
         bad += fabsf(dk_h[i]) > 0.5f;
         bad += fabsf(dq_h[i]) > 0.5f;
     }
+    bad += sixteen_bit_additions();
     printf(bad ? "FAIL: %zu wrong values\n" : "PASS\n", bad);
     return bad ? 1 : 0;
 }
