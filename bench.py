@@ -239,7 +239,7 @@ def pair_slices(B, H, start, stop):
     return out
 
 
-def measure_strong_scaling(torch, dist, sfb, steps, world, rank, chunks=2):
+def measure_strong_scaling(torch, dist, sfb, steps, world, rank, chunks=None):
     """Strong scaling of the `local_bertlarge` workload (B=4, H=16, L=16384: 64 (batch, head) pairs): the pairs are dealt
     contiguously to the ranks (sharding.partition_pairs), a rank computes its share in place on head slices of the full
     tensors (sfb_fused_attention_slice) in `chunks` launches, and every chunk's output is all-gathered (NCCL) on a second
@@ -255,6 +255,12 @@ def measure_strong_scaling(torch, dist, sfb, steps, world, rank, chunks=2):
     q, k, v = (torch.randn(B, L, H, d, device="cuda", generator=gen).to(torch.bfloat16) for _ in range(3))
     start, stop = sh.partition_pairs(B, H, world, rank)
     n = stop - start
+    if chunks is None:
+        # two chunks (so that a gather can run under the second) only while each still fills the GPU several times over:
+        # the kernel deals whole row pairs to 3 streams on each of 148 SMs, and a launch of about as many pairs as streams
+        # ends with most of them idle
+        row_pairs = (L // bs + 1) // 2
+        chunks = 2 if world > 1 and (n // 2) * row_pairs >= 4 * 3 * 148 else 1
     # the share in `chunks` pieces of whole pairs, each piece a few rectangles
     bounds = [start + (n * c) // chunks for c in range(chunks + 1)]
     pieces = [pair_slices(B, H, bounds[c], bounds[c + 1]) for c in range(chunks) if bounds[c + 1] > bounds[c]]
