@@ -404,7 +404,9 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap pmap, const __grid_constant__
 // Row-pair tiling as the three-stage kernel.  The row's scores are produced twice by the tensor core instead of
 // making a round trip through memory: sweep 1 over the row pair's key blocks keeps the running row max and sum,
 // sweep 2 recomputes S and writes exp2(s*c - max) / sum.  warp 0: TMA (Q once, the K tiles twice); warp 1: MMA;
-// warps 2-5: one query row per thread.
+// warps 2-9: two threads per query row, 32 score columns each.  The two threads of a row keep their own running
+// (max, sum) through sweep 1 and combine them once, between the sweeps, through shared memory: no exchange per step,
+// and twice the warps to hide the TMEM-load -> exponentials -> store chain of a step.
 struct FpParams {
     const uint2 *nn_lut;
     const uint64_t *mask;      // mask_np order, or NULL
@@ -414,9 +416,14 @@ struct FpParams {
     int out_dtype, is_bf16;
 };
 
-constexpr size_t kFpSmem = 1024 + kQBytes + kUStages * kTileBytes + sizeof(UShared);
+constexpr size_t kFpSmem = 1024 + kQBytes + kUStages * kTileBytes + sizeof(UShared) + 256 * sizeof(float2);
+constexpr int kFpThreads = 64 + 256;
+#ifndef SFB_FP_POLY
+#define SFB_FP_POLY 2
+#endif
+constexpr int kFpPoly = SFB_FP_POLY;        // sweep 1: every kFpPoly-th pair of exponentials on the FMA pipe (0 = none)
 
-__global__ void __launch_bounds__(192, 2)
+__global__ void __launch_bounds__(kFpThreads, 3)
 fused_p_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap, const FpParams p)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -424,6 +431,7 @@ fused_p_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     uint8_t *q_tile = smem;
     uint8_t *k_tiles = q_tile + kQBytes;
     UShared *st = (UShared *)(k_tiles + kUStages * kTileBytes);
+    float2 *comb = (float2 *)(st + 1);         // [column half][row]: (max, sum) after sweep 1
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t pair = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
@@ -435,7 +443,8 @@ fused_p_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     if (threadIdx.x == 0) {
         mbar_init(&st->q_full, 1);
         for (int s = 0; s < kUStages; s++) { mbar_init(&st->in_full[s], 1); mbar_init(&st->in_empty[s], 1); }
-        for (int s = 0; s < 2; s++) { mbar_init(&st->s_full[s], 1); mbar_init(&st->s_empty[s], 128); }
+        for (int s = 0; s < 2; s++) { mbar_init(&st->s_full[s], 1); mbar_init(&st->s_empty[s], 256); }
+        mbar_init(&st->o_final, 256);          // here: both halves of every row have published their (max, sum)
         mbar_init(&st->drained, 1);
         st->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -464,7 +473,7 @@ fused_p_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 if (t >= kUStages && !mbar_wait(&st->in_empty[s], ((t / kUStages) - 1) & 1, abort_flag, 41)) break;
                 mbar_expect_tx(&st->in_full[s], kTileBytes);
                 tma_load_2d(smem_u32(k_tiles + s * kTileBytes), &kmap, &st->in_full[s], xq,
-                            (int32_t)(b * L + st->entries[t % T].col * 64));
+                            (int32_t)(b * L + st->entries[t < T ? t : t - T].col * 64));
             }
         }
     } else if (warp == 1) {
@@ -485,7 +494,9 @@ fused_p_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             }
         }
     } else {
-        const uint32_t quarter = warp & 3;
+        const uint32_t quarter = warp & 3;         // the TMEM lanes a warp may read: 32 * (warp % 4)
+        const uint32_t ch = (warp - 2) >> 2;       // which 32 of the 64 score columns
+        const uint32_t cb = ch * 32;
         const uint32_t r = quarter * 32 + lane;
         const uint32_t half = r >> 6;
         const uint32_t lane_field = (quarter * 32) << 16;
@@ -494,46 +505,67 @@ fused_p_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         for (uint32_t t = 0; t < T2; t++) {
             if (!mbar_wait_warp(&st->s_full[t & 1], (t >> 1) & 1, abort_flag, 45)) break;
             tcgen05_fence_after();
-            uint32_t sr[64];
-            TMEM_LD_32((sr), tmem + 64 * (t & 1) + lane_field);
-            TMEM_LD_32((sr + 32), tmem + 64 * (t & 1) + lane_field + 32);
+            uint32_t sr[32];
+            TMEM_LD_32((sr), tmem + 64 * (t & 1) + lane_field + cb);
             tmem_wait_ld();
             tcgen05_fence_before();
             mbar_arrive(&st->s_empty[t & 1]);
 
-            const UnionEntry ent = st->entries[t % T];
-            const bool mine = (ent.flags >> half) & 1;
-            // the row sum is final once sweep 1 is over, whichever block-row owns the union's first and last entries
-            if (t == T) inv = l > 0.f ? 1.f / l : 0.f;
-            if (!mine) continue;
+            if (t == T) {
+                // sweep 1 is over, whichever block-row owns the union's first and last entries: the row's two threads
+                // merge their (max, sum).  A bounded wait on a barrier, not bar.sync: a warp that gave up never arrives.
+                comb[ch * 128 + r] = make_float2(m, l);
+                mbar_arrive(&st->o_final);
+                if (!mbar_wait_warp(&st->o_final, 0, abort_flag, 46)) break;
+                const float2 o = comb[(ch ^ 1) * 128 + r];
+                const float mf = fmaxf(m, o.x);
+                l = (m > -INFINITY ? l * ex2_approx(m - mf) : 0.f) + (o.x > -INFINITY ? o.y * ex2_approx(o.x - mf) : 0.f);
+                m = mf;
+                inv = l > 0.f ? 1.f / l : 0.f;
+            }
+            const UnionEntry *ent = &st->entries[t < T ? t : t - T];     // read in place: a copy indexed by `half` would live in local memory
+            if (!((ent->flags >> half) & 1)) continue;
             if (p.mask) {
-                const uint64_t w = p.mask[(size_t)h * p.mask_stride + (size_t)ent.blk[half] * 64 + (r & 63)];
+                const uint32_t w = (uint32_t)(p.mask[(size_t)h * p.mask_stride + (size_t)ent->blk[half] * 64 + (r & 63)] >> cb);
 #pragma unroll
-                for (int c = 0; c < 64; c++)
+                for (int c = 0; c < 32; c++)
                     if (!((w >> c) & 1)) sr[c] = 0xff800000u;
             }
             if (t < T) {
-                // sweep 1: running max and sum
+                // sweep 1: running max and sum of this thread's columns
                 float mx = -INFINITY;
 #pragma unroll
-                for (int c = 0; c < 64; c++) mx = fmaxf(mx, __uint_as_float(sr[c]));
+                for (int c = 0; c < 32; c++) mx = fmaxf(mx, __uint_as_float(sr[c]));
                 mx *= sl;
                 if (mx > m) {
                     l *= ex2_approx(m - mx);     // 0 while m is still -inf
                     m = mx;
                 }
                 if (m > -INFINITY) {
+                    // only the sum of these exponentials is kept: every kFpPoly-th pair is a cubic on the FMA pipe
+                    // (relative error 1.6e-4), which takes that share of sweep 1 off the MUFU
                     float ps4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                    for (int c = 0; c < 64; c++) ps4[c & 3] += ex2_approx(fmaf(__uint_as_float(sr[c]), sl, -m));
+                    for (int j = 0; j < 16; j++) {
+                        const float x0 = fmaf(__uint_as_float(sr[2 * j]), sl, -m), x1 = fmaf(__uint_as_float(sr[2 * j + 1]), sl, -m);
+                        float e0, e1;
+                        if (kFpPoly > 0 && j % (kFpPoly > 0 ? kFpPoly : 1) == 0) {
+                            exp2_fma_pair(pk64(x0, x1), e0, e1);
+                        } else {
+                            e0 = ex2_approx(x0);
+                            e1 = ex2_approx(x1);
+                        }
+                        ps4[(2 * j) & 3] += e0;
+                        ps4[(2 * j + 1) & 3] += e1;
+                    }
                     l += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
                 }
             } else {
                 // sweep 2: probabilities out
                 const float neg_m = m > -INFINITY ? -m : 0.f;
-                const size_t off = ((((size_t)b * p.H + h) * p.blocks + ent.blk[half]) * 64 + (r & 63)) * 64;
+                const size_t off = ((((size_t)b * p.H + h) * p.blocks + ent->blk[half]) * 64 + (r & 63)) * 64 + cb;
 #pragma unroll
-                for (int c0 = 0; c0 < 64; c0 += 16) {
+                for (int c0 = 0; c0 < 32; c0 += 16) {
                     uint32_t v[16];
 #pragma unroll
                     for (int c = 0; c < 16; c++)
@@ -674,7 +706,7 @@ int tc_fused_p(cudaStream_t s, const void *nn_lut, const void *a, const void *b,
             return fail("sfb_fused_sddmm_softmax: cannot reserve %zu bytes of shared memory", kFpSmem);
         once.mark(dev);
     }
-    fused_p_tc_kernel<<<dim3((p.nb_a + 1) / 2, p.B, p.H), 192, kFpSmem, s>>>(qm, km, prm);
+    fused_p_tc_kernel<<<dim3((p.nb_a + 1) / 2, p.B, p.H), kFpThreads, kFpSmem, s>>>(qm, km, prm);
     return check_launch("sfb_fused_sddmm_softmax");
 }
 

@@ -188,14 +188,59 @@ __device__ __forceinline__ float ex2_approx(float x)
     return y;
 }
 
-// exp2 of two values at once: fp32 pair -> packed fp16 pair -> MUFU on both halves (lo = first value)
-__device__ __forceinline__ uint32_t ex2_pair_f16(float lo, float hi)
+// ---- packed fp32 pairs (one instruction, two lanes) ----
+__device__ __forceinline__ uint64_t pk64(float a, float b)
 {
-    __half2 h = __floats2half2_rn(lo, hi);
-    uint32_t x = *reinterpret_cast<uint32_t *>(&h), y;
-    asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
-    return y;
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
 }
+__device__ __forceinline__ void up64(uint64_t v, float &a, float &b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2p(uint64_t a, uint64_t b, uint64_t c)
+{
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2p(uint64_t a, uint64_t b)
+{
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2p_rm(uint64_t a, uint64_t b)
+{
+    uint64_t d;
+    asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t sub2p(uint64_t a, uint64_t b)
+{
+    uint64_t d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+// exp2 of a pair on the FMA pipe: x = n + f with n = floor(x) taken by a magic-number add that rounds down, a cubic
+// in f on [0, 1) (max relative error 1.6e-4, below half a unit of either 16-bit format P is rounded to), n added
+// into the exponent field.  x <= 0 up to the lazy-max slack, clamped at -120 so that the exponent cannot wrap.
+__device__ __forceinline__ void exp2_fma_pair(uint64_t x, float &e0, float &e1)
+{
+    const uint64_t magic = pk64(12582912.f, 12582912.f);   // 1.5 * 2^23
+    float x0, x1;
+    up64(x, x0, x1);
+    x = pk64(fmaxf(x0, -120.f), fmaxf(x1, -120.f));
+    const uint64_t r = add2p_rm(x, magic);
+    const uint64_t f = sub2p(x, sub2p(r, magic));
+    uint64_t q = fma2p(pk64(0.0790210f, 0.0790210f), f, pk64(0.2249302f, 0.2249302f));
+    q = fma2p(q, f, pk64(0.6960656f, 0.6960656f));
+    q = fma2p(q, f, pk64(1.0f, 1.0f));
+    float q0, q1, r0, r1;
+    up64(q, q0, q1);
+    up64(r, r0, r1);
+    e0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
+    e1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
+}
+
 // packed fp16 pair -> packed bf16 pair (the MMA wants A and B in one format)
 __device__ __forceinline__ uint32_t f16x2_to_bf16x2(uint32_t v)
 {

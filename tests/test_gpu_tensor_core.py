@@ -237,6 +237,30 @@ def test_fused_sddmm_softmax_on_tensor_cores(sfb, oracle, dtype, out, pred, ctx)
     np.testing.assert_allclose(sums, 1.0, atol=1e-3 if out == "f32" else 2e-2)
 
 
+@pytest.mark.parametrize("nb", [9, 40, 41, 48])
+@pytest.mark.parametrize("out", ["f32", "f16", "bf16"])
+def test_fused_sddmm_softmax_row_maximum_grows_along_the_row(sfb, oracle, nb, out):
+    """Keys whose magnitude grows with position: the running row maximum moves at nearly every key block, so the
+    probabilities written early are rescaled by large factors.  Unions of up to 40 key blocks take the single sweep
+    that rescales what it wrote, longer ones the double sweep; both sides of that boundary against the oracle."""
+    B, H, d = 1, 2, 64
+    L = nb * 64
+    lay = sfb.BlockLayout.generate(sfb.LAYOUT_FULL, 1, nb, 64)
+    luts = oracle.lut_build(oracle.layout("full", 1, nb))
+    q, k = (_rand(oracle, (B, L, H, d), 1300 + i, "bf16") for i in range(2))
+    ramp = (0.25 + 3.0 * torch.arange(L, device=k.device, dtype=torch.float32) / L).view(1, L, 1, 1)
+    k = (k.float() * ramp).to(torch.bfloat16)
+    qn, kn = q.float().cpu().numpy(), k.float().cpu().numpy()
+    ref = oracle.attention(qn, kn, kn, luts, 64, np.float32(0.125), want=("p",))["p"]
+    odt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[out]
+    p = sfb.fused_sddmm_softmax(q, k, lay, 0.125, odt).float().cpu().numpy()
+    assert sfb.device_status() == 0
+    tol = 2e-3 if out == "f32" else REL
+    assert np.abs(p - ref).max() <= tol * ref.max()
+    sums = oracle.blocks_to_dense(p, luts["nt"], nb, 64).sum(-1)
+    np.testing.assert_allclose(sums, 1.0, atol=1e-3 if out == "f32" else 2e-2)
+
+
 @pytest.mark.parametrize("case", ["lower_interior_subset", "upper_empty", "lower_in_the_middle_only"])
 @pytest.mark.parametrize("op", ["probabilities", "attention"])
 def test_row_pair_ownership_of_union_entries(sfb, oracle, case, op):
