@@ -1145,3 +1145,11 @@ if __name__ == "__main__":
         run_bandwidth_kernel(a)
     else:
         run_ours(a)
+    if a.impl != "reference":
+        # a kernel that gave up on a bounded wait leaves its code in the library's status word: the numbers above are
+        # then not measurements, and the run says so with its exit code (every rank looks at its own device)
+        import __graft_entry__ as ge
+        status = ge.load_package().device_status()
+        if status:
+            print("bench.py: device status word 0x%08x (a kernel gave up on a bounded wait): results invalid" % status, file=sys.stderr)
+            sys.exit(3)
