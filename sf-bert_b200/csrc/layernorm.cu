@@ -8,6 +8,14 @@ namespace sfb {
 template <int DT> struct Vec8;
 template <> struct Vec8<SFB_F32> {
     static constexpr int N = 4;  // elements per 16-byte access
+    static __device__ __forceinline__ void decode(float (&v)[4], const uint4 &u)
+    {
+        v[0] = __uint_as_float(u.x); v[1] = __uint_as_float(u.y); v[2] = __uint_as_float(u.z); v[3] = __uint_as_float(u.w);
+    }
+    static __device__ __forceinline__ uint4 encode(const float (&v)[4])
+    {
+        return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+    }
     static __device__ __forceinline__ void load(float (&v)[4], const void *p, size_t i)
     {
         float4 t = *(const float4 *)((const float *)p + i);
@@ -20,6 +28,25 @@ template <> struct Vec8<SFB_F32> {
 };
 template <> struct Vec8<SFB_BF16> {
     static constexpr int N = 8;
+    static __device__ __forceinline__ void decode(float (&v)[8], const uint4 &u)
+    {
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            v[2 * t] = __uint_as_float(w[t] << 16);
+            v[2 * t + 1] = __uint_as_float(w[t] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ uint4 encode(const float (&v)[8])
+    {
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * t], v[2 * t + 1]);
+            w[t] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
     static __device__ __forceinline__ void load(float (&v)[8], const void *p, size_t i)
     {
         uint4 u = *(const uint4 *)((const uint16_t *)p + i);
@@ -43,6 +70,26 @@ template <> struct Vec8<SFB_BF16> {
 };
 template <> struct Vec8<SFB_F16> {
     static constexpr int N = 8;
+    static __device__ __forceinline__ void decode(float (&v)[8], const uint4 &u)
+    {
+        uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            float2 f = __half22float2(*reinterpret_cast<__half2 *>(&w[t]));
+            v[2 * t] = f.x;
+            v[2 * t + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ uint4 encode(const float (&v)[8])
+    {
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            __half2 h = __floats2half2_rn(v[2 * t], v[2 * t + 1]);
+            w[t] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
     static __device__ __forceinline__ void load(float (&v)[8], const void *p, size_t i)
     {
         uint4 u = *(const uint4 *)((const uint16_t *)p + i);
@@ -66,74 +113,118 @@ template <> struct Vec8<SFB_F16> {
     }
 };
 
-// CHUNKS 16-byte accesses per lane: hidden <= 32 * CHUNKS * N.  One warp per row, ROWS_PER_CTA warps.
-template <int DT, int CHUNKS>
-__global__ void __launch_bounds__(256) bias_residual_layernorm_kernel(void *__restrict__ out, void *__restrict__ sum_out,
+// streamed once: 16 bytes that bypass L1 on the way in, and leave L2 first on the way out
+__device__ __forceinline__ uint4 ld_stream16(const void *p)
+{
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_stream16(void *p, const uint4 &v)
+{
+    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// CHUNKS 16-byte accesses per lane: hidden <= 32 * CHUNKS * N.  One warp per row, 8 warps per CTA, a fixed grid of
+// warps striding over the rows.  bias, gain and beta sit in shared memory as fp32 (read once per CTA; from global
+// memory they were three times the row's own bytes through L1 for every row).  All of a row's loads are issued before
+// anything waits for one of them; with PREFETCH the next row's loads are issued before this row's arithmetic.
+// A row is read once, by the warp that later writes it, so out (or sum_out) may be x or resid themselves.
+template <int DT, int CHUNKS, bool HAS_RESID, bool PREFETCH>
+__global__ void __launch_bounds__(256) bias_residual_layernorm_kernel(void *out, void *sum_out,
                                                                      float *__restrict__ mean, float *__restrict__ rstd,
-                                                                     const void *__restrict__ x, const float *__restrict__ bias,
-                                                                     const void *__restrict__ resid, const float *__restrict__ gain,
+                                                                     const void *x, const float *__restrict__ bias,
+                                                                     const void *resid, const float *__restrict__ gain,
                                                                      const float *__restrict__ beta, uint32_t m, uint32_t hidden)
 {
     constexpr int N = Vec8<DT>::N;
+    constexpr int ESZ = 16 / N;
+    extern __shared__ __align__(16) float prm[];           // [bias | gain | beta][hidden]
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t warps = gridDim.x * (blockDim.x >> 5);
-    // a fixed grid of warps strides over the rows
-    for (uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < m; row += warps) {
-    const size_t base = (size_t)row * hidden;
-    float v[CHUNKS][N];
-    float s = 0.f, s2 = 0.f;
+    const uint8_t *xb = (const uint8_t *)x, *rb = (const uint8_t *)resid;
+    uint4 xr[CHUNKS], rr[CHUNKS];
+    auto issue = [&](uint32_t row) {
+        const size_t base = (size_t)row * hidden;
 #pragma unroll
-    for (int c = 0; c < CHUNKS; c++) {
-        const uint32_t col = (c * 32 + lane) * N;
-        if (col < hidden) {
-            Vec8<DT>::load(v[c], x, base + col);
-            if (bias) {
+        for (int c = 0; c < CHUNKS; c++) {
+            const uint32_t col = (c * 32 + lane) * N;
+            if (col < hidden) {
+                xr[c] = ld_stream16(xb + (base + col) * ESZ);
+                if (HAS_RESID) rr[c] = ld_stream16(rb + (base + col) * ESZ);
+            }
+        }
+    };
+    uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (PREFETCH && row < m) issue(row);                   // the first row is on its way while the parameters are staged
+    for (uint32_t i = threadIdx.x; i < hidden; i += blockDim.x) {
+        prm[i] = bias ? bias[i] : 0.f;
+        prm[hidden + i] = gain[i];
+        prm[2 * hidden + i] = beta[i];
+    }
+    __syncthreads();
+    for (; row < m; row += warps) {
+        const size_t base = (size_t)row * hidden;
+        if (!PREFETCH) issue(row);
+        float v[CHUNKS][N];
+        float s = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int c = 0; c < CHUNKS; c++) {
+            const uint32_t col = (c * 32 + lane) * N;
+            if (col < hidden) {
+                Vec8<DT>::decode(v[c], xr[c]);
 #pragma unroll
                 for (int t = 0; t < N; t += 4) {
-                    float4 bb = __ldg((const float4 *)(bias + col + t));
+                    const float4 bb = *(const float4 *)(prm + col + t);
                     v[c][t] += bb.x; v[c][t + 1] += bb.y; v[c][t + 2] += bb.z; v[c][t + 3] += bb.w;
                 }
-            }
-            if (resid) {
-                float r[N];
-                Vec8<DT>::load(r, resid, base + col);
+                if (HAS_RESID) {
+                    float r[N];
+                    Vec8<DT>::decode(r, rr[c]);
 #pragma unroll
-                for (int t = 0; t < N; t++) v[c][t] = r[t] + v[c][t];
-            }
-            if (sum_out) Vec8<DT>::store(sum_out, base + col, v[c]);
-#pragma unroll
-            for (int t = 0; t < N; t++) {
-                s += v[c][t];
-                s2 = fmaf(v[c][t], v[c][t], s2);
+                    for (int t = 0; t < N; t++) v[c][t] = r[t] + v[c][t];
+                }
             }
         }
-    }
-    s = warp_sum(s);
-    s2 = warp_sum(s2);
-    const float mu = s / (float)hidden;
-    // var = E[x^2] - mean^2 with eps inside the root (layernorm.h:28-30)
-    const float rs = rsqrtf(fmaxf(s2 / (float)hidden - mu * mu, 0.f) + 1e-5f);
-    if (lane == 0) {
-        if (mean) mean[row] = mu;
-        if (rstd) rstd[row] = rs;
-    }
+        if (PREFETCH && row + warps < m) issue(row + warps);     // the raw words are decoded: their registers take the next row
 #pragma unroll
-    for (int c = 0; c < CHUNKS; c++) {
-        const uint32_t col = (c * 32 + lane) * N;
-        if (col < hidden) {
-            float y[N];
+        for (int c = 0; c < CHUNKS; c++) {
+            const uint32_t col = (c * 32 + lane) * N;
+            if (col < hidden) {
+                if (sum_out) st_stream16((uint8_t *)sum_out + (base + col) * ESZ, Vec8<DT>::encode(v[c]));
 #pragma unroll
-            for (int t = 0; t < N; t += 4) {
-                float4 g = __ldg((const float4 *)(gain + col + t));
-                float4 be = __ldg((const float4 *)(beta + col + t));
-                y[t] = (v[c][t] - mu) * rs * g.x + be.x;
-                y[t + 1] = (v[c][t + 1] - mu) * rs * g.y + be.y;
-                y[t + 2] = (v[c][t + 2] - mu) * rs * g.z + be.z;
-                y[t + 3] = (v[c][t + 3] - mu) * rs * g.w + be.w;
+                for (int t = 0; t < N; t++) {
+                    s += v[c][t];
+                    s2 = fmaf(v[c][t], v[c][t], s2);
+                }
             }
-            Vec8<DT>::store(out, base + col, y);
         }
-    }
+        s = warp_sum(s);
+        s2 = warp_sum(s2);
+        const float mu = s / (float)hidden;
+        // var = E[x^2] - mean^2 with eps inside the root (layernorm.h:28-30)
+        const float rs = rsqrtf(fmaxf(s2 / (float)hidden - mu * mu, 0.f) + 1e-5f);
+        if (lane == 0) {
+            if (mean) mean[row] = mu;
+            if (rstd) rstd[row] = rs;
+        }
+#pragma unroll
+        for (int c = 0; c < CHUNKS; c++) {
+            const uint32_t col = (c * 32 + lane) * N;
+            if (col < hidden) {
+                float y[N];
+#pragma unroll
+                for (int t = 0; t < N; t += 4) {
+                    const float4 g = *(const float4 *)(prm + hidden + col + t);
+                    const float4 be = *(const float4 *)(prm + 2 * hidden + col + t);
+                    y[t] = (v[c][t] - mu) * rs * g.x + be.x;
+                    y[t + 1] = (v[c][t + 1] - mu) * rs * g.y + be.y;
+                    y[t + 2] = (v[c][t + 2] - mu) * rs * g.z + be.z;
+                    y[t + 3] = (v[c][t + 3] - mu) * rs * g.w + be.w;
+                }
+                st_stream16((uint8_t *)out + (base + col) * ESZ, Vec8<DT>::encode(y));
+            }
+        }
     }
 }
 
@@ -145,14 +236,30 @@ static int launch_ln(cudaStream_t s, void *out, void *sum_out, float *mean, floa
     const uint32_t per_chunk = 32 * N;
     const uint32_t chunks = (hidden + per_chunk - 1) / per_chunk;
     const uint32_t rows_per_cta = 8;
-    // at most the CTAs that are resident at once (four per SM at 61 registers); the warps loop over the remaining
-    // rows.  Measured against 16 per SM and against one row per warp: 0.66 / 0.62 / 0.59 of copy bandwidth.
-    uint32_t ctas = (m + rows_per_cta - 1) / rows_per_cta;
-    if (ctas > 148 * 4) ctas = 148 * 4;
-    dim3 grid(ctas);
-#define LN_CASE(C)                                                                                                   \
-    bias_residual_layernorm_kernel<DT, C><<<grid, 32 * rows_per_cta, 0, s>>>(out, sum_out, mean, rstd, x, bias, resid, \
-                                                                             gain, beta, m, hidden)
+    // the grid is the CTAs that are resident at once (a second wave of CTAs would start while the first one's warps
+    // are still striding: measured 0.62 against 0.66 of copy bandwidth); the warps loop over the remaining rows
+    const uint32_t want = (m + rows_per_cta - 1) / rows_per_cta;
+    const size_t smem = 3 * (size_t)hidden * sizeof(float);
+    const int sms = device_sm_count(current_device());
+    SFB_REQUIRE(sms > 0, "sfb_bias_residual_layernorm: cannot query the device");
+#ifndef SFB_LN_PREFETCH
+#define SFB_LN_PREFETCH true
+#endif
+#define LN_LAUNCH(C, R)                                                                                                        \
+    do {                                                                                                                       \
+        auto kern = bias_residual_layernorm_kernel<DT, C, R, SFB_LN_PREFETCH>;                                                 \
+        int per_sm = 0;                                                                                                        \
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 32 * rows_per_cta, smem) != cudaSuccess || per_sm < 1) \
+            per_sm = 1;                                                                                                        \
+        const uint32_t resident = (uint32_t)per_sm * (uint32_t)sms;                                                            \
+        kern<<<want < resident ? want : resident, 32 * rows_per_cta, smem, s>>>(out, sum_out, mean, rstd, x, bias, resid, gain, \
+                                                                                beta, m, hidden);                              \
+    } while (0)
+#define LN_CASE(C)                                                                                                             \
+    do {                                                                                                                       \
+        if (resid) LN_LAUNCH(C, true);                                                                                         \
+        else LN_LAUNCH(C, false);                                                                                              \
+    } while (0)
     if (chunks <= 1) LN_CASE(1);
     else if (chunks <= 2) LN_CASE(2);
     else if (chunks <= 3) LN_CASE(3);
@@ -161,6 +268,7 @@ static int launch_ln(cudaStream_t s, void *out, void *sum_out, float *mean, floa
     else if (chunks <= 8) LN_CASE(8);
     else if (chunks <= 16) LN_CASE(16);
     else return fail("sfb_bias_residual_layernorm: hidden %u too large (max %u)", hidden, 16 * per_chunk);
+#undef LN_LAUNCH
 #undef LN_CASE
     return check_launch("sfb_bias_residual_layernorm");
 }
