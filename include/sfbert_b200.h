@@ -215,6 +215,7 @@ int sfb_device_status_clear(void);
 /* out = LayerNorm(resid + (x + bias)) * gain + beta over rows of `hidden` elements; also writes
  * the pre-norm sum (sum_out), mean and rstd when those are not NULL.  bias and resid may be NULL.
  * dtype is the type of x, resid, out and sum_out; bias, gain, beta, mean, rstd are fp32.
+ * out (or sum_out) may be x or resid: a row is read completely before it is written.
  * Replaces tensor_add_vector_gpu + tensor_add_tensor_gpu + layernorm_gpu
  * (cuda_kernels.h:459-469, :449-457, :334-372; call site transformer_attention_optimize.cu:763-771). */
 int sfb_bias_residual_layernorm(sfb_stream_t stream, void *out, void *sum_out, float *mean,

@@ -251,7 +251,7 @@ def embedding(table, ids, pos=None):
     vocab, hidden = table.shape
     assert ids.dtype == torch.int32 and ids.is_contiguous() and table.is_contiguous()
     out = torch.empty(B, L, hidden, dtype=table.dtype, device=table.device)
-    bad = torch.zeros(1, dtype=torch.int32, device=table.device)
+    bad = torch.empty(1, dtype=torch.int32, device=table.device)      # the call zeroes it on the stream
     _check(lib.sfb_embedding(_stream(), _p(out), _p(table), _p(ids), _p(pos), B, L, hidden, vocab, dtype_tag(table), _p(bad)))
     return out, bad
 
@@ -390,11 +390,11 @@ def fused_attention_slice(q, k, v, lay, scale=None, use_mask=False, out=None):
     return o
 
 
-def bias_residual_layernorm(x, bias, resid, gain, beta, want_sum=False):
+def bias_residual_layernorm(x, bias, resid, gain, beta, want_sum=False, out=None):
     """LayerNorm(resid + (x + bias)) (tensor_add_vector_gpu + tensor_add_tensor_gpu + layernorm_gpu,
-    cuda_kernels.h:459,449,334).  Returns (out, sum or None, mean, rstd)."""
+    cuda_kernels.h:459,449,334).  Returns (out, sum or None, mean, rstd); out may be x or resid."""
     m, hidden = x.shape
-    out = torch.empty_like(x)
+    out = torch.empty_like(x) if out is None else out
     summed = torch.empty_like(x) if want_sum else None
     mean = torch.empty(m, dtype=torch.float32, device=x.device)
     rstd = torch.empty(m, dtype=torch.float32, device=x.device)

@@ -162,10 +162,14 @@ __device__ __forceinline__ float ex2_fast(float x)
 // lane in flight) and stay in registers: one pass over HBM, one exponential per element.
 // NB == 0: rows of any length.  Pass 1 finds the row maximum, pass 2 the sum of exponentials, pass 3 writes;
 // passes 2 and 3 re-read scores this CTA has just pulled through L2.
-// SPLIT > 1: the block-row is shared by SPLIT CTAs of BS/SPLIT query rows each (more registers per thread for the
-// register-resident variant of longer rows).
+// SPLIT > 1: the block-row is shared by SPLIT CTAs of BS/SPLIT query rows each.  Registers decide how many of the
+// register-resident CTAs an SM holds, and small CTAs fill what the register file leaves: with loads of some CTAs in
+// flight while others compute and store, the 12- and 16-block rows run at the speed of a copy (0.98 of it; a CTA per
+// whole block-row, one per SM, reached 0.6-0.7).
+// The second launch bound asks for the number of CTAs per SM that the variant's registers allow anyway (it keeps the
+// compiler from spending registers the occupancy needs).
 template <int BS, int X_DT, int Y_DT, int NB, int SPLIT>
-__global__ void __launch_bounds__(BS * BS / 8 / SPLIT) softmax_kernel(const uint2 *__restrict__ lut,
+__global__ void __launch_bounds__(BS * BS / 8 / SPLIT, (NB > 0 && SPLIT > 1 && BS == 64 && X_DT != SFB_F32) ? (NB <= 12 ? 6 : NB <= 18 ? 5 : 4) : 1) softmax_kernel(const uint2 *__restrict__ lut,
                                                                 const typename MaskWord<BS>::type *__restrict__ mask,
                                                                 const void *__restrict__ X, void *__restrict__ Y, AttnDims p,
                                                                 float scale_log2e, int rescale_in_place)
@@ -741,23 +745,39 @@ int simt_softmax(cudaStream_t s, const void *lut, const void *mask, const void *
                  uint32_t bs, const AttnDims &p, float scale, uint32_t max_lut)
 {
     const float sl = scale * LOG2E_F;
-    // rows that just fill 4, 8 or 16 blocks (the caller's max_lut says so) stay in registers; 0 = unknown, stream.
-    // Measured: a register tile with spare slots (12 blocks in 16, 17 in 32 with half-size CTAs) is slower here than
-    // streaming -- 3.9 against 4.9 TB/s on 12-block rows, 2.6 against 4.4 on 17-block rows -- unlike in the gradient.
+    // The caller's max_lut (0 = unknown) picks the variant.  16-bit scores: rows of up to 20 blocks stay in registers,
+    // one pass over HBM; from 9 blocks up a CTA takes a quarter of the block-row's query rows.  Longer or unknown rows
+    // are streamed: three sweeps, the second and third over lines the CTA has just pulled through L2.  Measured and not
+    // kept for rows of 17-32 blocks: two groups of lanes per query row, each holding every other block (0.68 of copy
+    // bandwidth on 17-block rows against 0.77 with 20 slots per lane).
     const int inplace = max_lut != 0 && max_lut <= 12;   // streamed short rows: unnormalised values wait in L2 for the rescale
-    const int nb = (max_lut >= 3 && max_lut <= 4) ? 4 : (max_lut >= 7 && max_lut <= 8) ? 8 : (max_lut >= 14 && max_lut <= 16) ? 16 : 0;
+    int nb = 0;   // block slots of the register tile, 0 = stream
+    if (x_dtype == SFB_BF16)
+        nb = max_lut == 0 ? 0 : max_lut <= 4 ? 4 : max_lut <= 8 ? 8 : max_lut <= 12 ? 12 : max_lut <= 16 ? 16 : max_lut <= 18 ? 18 : max_lut <= 20 ? 20 : 0;
+    else
+        nb = (max_lut >= 3 && max_lut <= 4) ? 4 : (max_lut >= 7 && max_lut <= 8) ? 8 : (max_lut >= 14 && max_lut <= 16) ? 16 : 0;
 #define SM_LAUNCH(XD, NBV, SPL)                                                                                        \
     DISPATCH_DT(y_dtype, YD, {                                                                                         \
         softmax_kernel<BS, XD, YD, NBV, SPL><<<dim3(p.nb_a * SPL, p.B, p.H), BS * BS / 8 / SPL, 0, s>>>(             \
             (const uint2 *)lut, (const W *)mask, x, y, p, sl, inplace);                                                \
     })
-#define SM_BY_NB(XD)                                                                                                   \
-    if (nb == 4) { SM_LAUNCH(XD, 4, 1) } else if (nb == 8) { SM_LAUNCH(XD, 8, 1) } else if (nb == 16) { SM_LAUNCH(XD, 16, 1) } else { SM_LAUNCH(XD, 0, 1) }
     DISPATCH_BS(bs, {
         typedef typename MaskWord<BS>::type W;
-        if (x_dtype == SFB_BF16) { SM_BY_NB(SFB_BF16) } else { SM_BY_NB(SFB_F32) }
+        if (x_dtype == SFB_BF16) {
+            if (nb == 4) { SM_LAUNCH(SFB_BF16, 4, 1) }
+            else if (nb == 8) { SM_LAUNCH(SFB_BF16, 8, 1) }
+            else if (nb == 12) { SM_LAUNCH(SFB_BF16, 12, 4) }
+            else if (nb == 16) { SM_LAUNCH(SFB_BF16, 16, 4) }
+            else if (nb == 18) { SM_LAUNCH(SFB_BF16, 18, 4) }
+            else if (nb == 20) { SM_LAUNCH(SFB_BF16, 20, 4) }
+            else { SM_LAUNCH(SFB_BF16, 0, 1) }
+        } else {
+            if (nb == 4) { SM_LAUNCH(SFB_F32, 4, 1) }
+            else if (nb == 8) { SM_LAUNCH(SFB_F32, 8, 1) }
+            else if (nb == 16) { SM_LAUNCH(SFB_F32, 16, 1) }
+            else { SM_LAUNCH(SFB_F32, 0, 1) }
+        }
     })
-#undef SM_BY_NB
 #undef SM_LAUNCH
     return check_launch("sfb_masked_softmax");
 }

@@ -319,37 +319,59 @@ __global__ void __launch_bounds__(256) bias_gelu_kernel(void *out, const void *x
     }
 }
 
-// Embedding lookup + positional add: out[token, :] = table[ids[token], :] + pos[token % seq_len, :].  One 16-byte
-// access per thread and step; a warp covers 512 contiguous bytes of one row.  An id outside [0, vocab) gives a row of
-// zeros (plus pos) and is counted in *bad_ids -- no out-of-bounds read.
+// Embedding lookup + positional add: out[b, l, :] = table[ids[b, l], :] + pos[l, :].  A thread owns one 16-byte piece
+// (l, col) of the position table for a run of batch elements: the position piece is read once and stays in registers,
+// so per output row only the table row comes in and the output row goes out (with a piece per token the positions
+// crossed from L2 to the SMs once per token: a third of all the bytes the kernel moved).  kEmbUnroll batch elements are
+// in flight per step, their ids requested one step ahead.  A warp covers 512 contiguous bytes of a row.  An id outside
+// [0, vocab) gives a row of zeros (plus pos) and is counted in *bad_ids -- no out-of-bounds read.
+constexpr int kEmbUnroll = 4;
 template <int DT>
 __global__ void __launch_bounds__(256) embedding_kernel(void *__restrict__ out, const void *__restrict__ table,
-                                                       const int32_t *__restrict__ ids, const void *__restrict__ pos, size_t tokens,
-                                                       uint32_t seq_len, uint32_t hidden, uint32_t vocab, uint32_t *bad_ids)
+                                                       const int32_t *__restrict__ ids, const void *__restrict__ pos, uint32_t batch,
+                                                       uint32_t per_cta_y, uint32_t seq_len, uint32_t hidden, uint32_t vocab,
+                                                       uint32_t *bad_ids)
 {
-    constexpr int N = Vec8<DT>::N;
-    const uint32_t per_row = hidden / N;                       // 16-byte pieces per row
-    const size_t total = tokens * per_row, stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const size_t tok = i / per_row;
-        const uint32_t col = (uint32_t)(i % per_row) * N;
-        const int32_t id = __ldg(ids + tok);
-        const bool ok = id >= 0 && (uint32_t)id < vocab;
-        float v[N];
-        if (ok) {
-            Vec8<DT>::load(v, table, (size_t)id * hidden + col);
-        } else {
+    constexpr int N = Vec8<DT>::N, U = kEmbUnroll;
+    constexpr int ESZ = 16 / N;
+    const uint32_t per_row = hidden / N;                                   // 16-byte pieces per row
+    const uint32_t piece = blockIdx.x * blockDim.x + threadIdx.x;          // < seq_len * per_row < 2^32 (checked by the host)
+    if (piece >= seq_len * per_row) return;
+    const uint32_t l = piece / per_row, col = (piece - l * per_row) * N;
+    const uint32_t b_begin = blockIdx.y * per_cta_y, b_end = min(batch, b_begin + per_cta_y);
+    const uint8_t *tb = (const uint8_t *)table;
+    float q[N];
 #pragma unroll
-            for (int t = 0; t < N; t++) v[t] = 0.f;
-            if (col == 0 && bad_ids) atomicAdd(bad_ids, 1u);
-        }
-        if (pos) {
-            float q[N];
-            Vec8<DT>::load(q, pos, (size_t)(tok % seq_len) * hidden + col);
+    for (int t = 0; t < N; t++) q[t] = 0.f;
+    if (pos) Vec8<DT>::decode(q, __ldg((const uint4 *)((const uint8_t *)pos + ((size_t)l * hidden + col) * ESZ)));
+    auto fetch_ids = [&](uint32_t b0, int32_t (&id)[U]) {
 #pragma unroll
-            for (int t = 0; t < N; t++) v[t] += q[t];
+        for (int u = 0; u < U; u++) id[u] = b0 + u < b_end ? __ldg(ids + (size_t)(b0 + u) * seq_len + l) : -1;
+    };
+    int32_t id[U], id_next[U];
+    if (b_begin < b_end) fetch_ids(b_begin, id);
+    for (uint32_t b0 = b_begin; b0 < b_end; b0 += U) {
+        uint4 tv[U];
+        bool ok[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            ok[u] = id[u] >= 0 && (uint32_t)id[u] < vocab;
+            tv[u] = make_uint4(0u, 0u, 0u, 0u);                            // all-zero bits decode to 0 in every type
+            if (ok[u]) tv[u] = __ldg((const uint4 *)(tb + ((size_t)id[u] * hidden + col) * ESZ));
         }
-        Vec8<DT>::store(out, tok * hidden + col, v);
+        if (b0 + U < b_end) fetch_ids(b0 + U, id_next);
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            if (b0 + u < b_end) {
+                if (!ok[u] && col == 0 && bad_ids) atomicAdd(bad_ids, 1u);
+                float v[N];
+                Vec8<DT>::decode(v, tv[u]);
+#pragma unroll
+                for (int t = 0; t < N; t++) v[t] += q[t];
+                st_stream16((uint8_t *)out + (((size_t)(b0 + u) * seq_len + l) * hidden + col) * ESZ, Vec8<DT>::encode(v));
+            }
+            id[u] = id_next[u];
+        }
     }
 }
 
@@ -388,15 +410,24 @@ int rowdot(cudaStream_t s, float *out, const void *a, const void *b, size_t rows
 int embedding_lookup(cudaStream_t s, void *out, const void *table, const int32_t *ids, const void *pos, uint32_t batch,
                      uint32_t seq_len, uint32_t hidden, uint32_t vocab, int dtype, uint32_t *bad_ids)
 {
-    const size_t tokens = (size_t)batch * seq_len;
     const int per = dtype == SFB_F32 ? 4 : 8;
     if (hidden % per) return fail("sfb_embedding: hidden=%u must be a multiple of %d for this type", hidden, per);
     if (bad_ids) cudaMemsetAsync(bad_ids, 0, sizeof(uint32_t), s);
-    size_t ctas = (tokens * (hidden / per) + 255) / 256;
-    if (ctas > 148 * 16) ctas = 148 * 16;
-    if (dtype == SFB_F32) embedding_kernel<SFB_F32><<<(unsigned)ctas, 256, 0, s>>>(out, table, ids, pos, tokens, seq_len, hidden, vocab, bad_ids);
-    else if (dtype == SFB_BF16) embedding_kernel<SFB_BF16><<<(unsigned)ctas, 256, 0, s>>>(out, table, ids, pos, tokens, seq_len, hidden, vocab, bad_ids);
-    else embedding_kernel<SFB_F16><<<(unsigned)ctas, 256, 0, s>>>(out, table, ids, pos, tokens, seq_len, hidden, vocab, bad_ids);
+    const size_t pieces = (size_t)seq_len * (hidden / per);                 // one thread per 16-byte piece of a position row
+    if (pieces >= (1ull << 32)) return fail("sfb_embedding: seq_len * hidden too large");
+    const int sms = device_sm_count(current_device());
+    if (sms <= 0) return fail("sfb_embedding: cannot query the device");
+    // short sequences: the batch is split over gridDim.y until the grid has about eight CTAs per SM
+    const size_t ctas_x = (pieces + 255) / 256;
+    uint32_t split = (uint32_t)(((size_t)sms * 8 + ctas_x - 1) / ctas_x);
+    if (split > batch) split = batch;
+    if (split > 65535u) split = 65535u;
+    if (split < 1) split = 1;
+    const uint32_t per_y = (batch + split - 1) / split;
+    const dim3 grid((unsigned)ctas_x, (batch + per_y - 1) / per_y);
+    if (dtype == SFB_F32) embedding_kernel<SFB_F32><<<grid, 256, 0, s>>>(out, table, ids, pos, batch, per_y, seq_len, hidden, vocab, bad_ids);
+    else if (dtype == SFB_BF16) embedding_kernel<SFB_BF16><<<grid, 256, 0, s>>>(out, table, ids, pos, batch, per_y, seq_len, hidden, vocab, bad_ids);
+    else embedding_kernel<SFB_F16><<<grid, 256, 0, s>>>(out, table, ids, pos, batch, per_y, seq_len, hidden, vocab, bad_ids);
     return check_launch("sfb_embedding");
 }
 

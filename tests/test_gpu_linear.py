@@ -97,6 +97,24 @@ def test_embedding_bit_exact(sfb, oracle, dtype, hidden):
     assert torch.equal(plain, table[ids.long()])
 
 
+@pytest.mark.parametrize("B,L,hidden", [(37, 8, 64), (5, 2, 1024), (130, 33, 128), (1, 4096, 768)])
+def test_embedding_batch_runs(sfb, B, L, hidden):
+    """A thread keeps one piece of a position row for a run of batch elements; short sequences split the batch over
+    the grid.  Batches that are no multiple of the run length or of the steps inside it, and a batch of one."""
+    gen = torch.Generator(device="cuda").manual_seed(31)
+    vocab = 1000
+    table = torch.randn(vocab, hidden, device="cuda", generator=gen).to(torch.bfloat16)
+    pos = torch.randn(L, hidden, device="cuda", generator=gen).to(torch.bfloat16)
+    ids = torch.randint(0, vocab, (B, L), device="cuda", generator=gen, dtype=torch.int32)
+    ids[B // 2, L // 2] = vocab + 3          # one id outside the table: zeros + position, counted once
+    out, bad = sfb.embedding(table, ids, pos)
+    assert int(bad.item()) == 1
+    rows = table[ids.clamp(0, vocab - 1).long()].float()
+    rows[B // 2, L // 2] = 0.0
+    want = (rows + pos.float().unsqueeze(0)).to(torch.bfloat16)
+    assert torch.equal(out, want)
+
+
 def test_embedding_ids_outside_the_table_are_counted_not_read(sfb):
     table = torch.ones(10, 16, device="cuda", dtype=torch.bfloat16)
     ids = torch.tensor([[0, 9, 10, -1, 5]], dtype=torch.int32, device="cuda")

@@ -137,3 +137,19 @@ def test_bias_gelu_in_place(sfb, dtype):
     y = x.clone()
     sfb.bias_gelu(y, bias, out=y)
     assert torch.equal(y, want)
+
+
+@pytest.mark.parametrize("dtype,hidden", [(torch.float32, 256), (torch.bfloat16, 768), (torch.float16, 1024)])
+@pytest.mark.parametrize("target", ["x", "resid"])
+def test_layernorm_in_place(sfb, dtype, hidden, target):
+    """out may be x or resid themselves: a row is read completely before the warp that owns it writes it."""
+    gen = torch.Generator(device="cuda").manual_seed(29)
+    m = 5000          # more rows than resident warps: every warp also prefetches rows it writes later
+    x, resid = (torch.randn(m, hidden, device="cuda", generator=gen).to(dtype) for _ in range(2))
+    bias, gain, beta = (torch.randn(hidden, device="cuda", generator=gen) for _ in range(3))
+    want, _, mean, rstd = sfb.bias_residual_layernorm(x, bias, resid, gain, beta)
+    xs, rs = x.clone(), resid.clone()
+    dst = xs if target == "x" else rs
+    got, _, mean2, rstd2 = sfb.bias_residual_layernorm(xs, bias, rs, gain, beta, out=dst)
+    assert got.data_ptr() == dst.data_ptr()
+    assert torch.equal(got, want) and torch.equal(mean, mean2) and torch.equal(rstd, rstd2)
