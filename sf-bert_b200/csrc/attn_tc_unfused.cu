@@ -544,32 +544,48 @@ fused_p_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 if (m > -INFINITY) {
                     // only the sum of these exponentials is kept: every kFpPoly-th pair is a cubic on the FMA pipe
                     // (relative error 1.6e-4), which takes that share of sweep 1 off the MUFU
-                    float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+                    uint64_t acc0 = 0ull, acc1 = 0ull;          // four partial sums as two packed pairs
+                    const uint64_t sl2 = pk64(sl, sl), nm2 = pk64(-m, -m);
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
-                        const float x0 = fmaf(__uint_as_float(sr[2 * j]), sl, -m), x1 = fmaf(__uint_as_float(sr[2 * j + 1]), sl, -m);
+                        const uint64_t x = fma2p(pk64(__uint_as_float(sr[2 * j]), __uint_as_float(sr[2 * j + 1])), sl2, nm2);
                         float e0, e1;
                         if (kFpPoly > 0 && j % (kFpPoly > 0 ? kFpPoly : 1) == 0) {
-                            exp2_fma_pair(pk64(x0, x1), e0, e1);
+                            exp2_fma_pair(x, e0, e1);
                         } else {
+                            float x0, x1;
+                            up64(x, x0, x1);
                             e0 = ex2_approx(x0);
                             e1 = ex2_approx(x1);
                         }
-                        ps4[(2 * j) & 3] += e0;
-                        ps4[(2 * j + 1) & 3] += e1;
+                        if (j & 1) acc1 = add2p(acc1, pk64(e0, e1));
+                        else acc0 = add2p(acc0, pk64(e0, e1));
                     }
+                    float ps4[4];
+                    up64(acc0, ps4[0], ps4[1]);
+                    up64(acc1, ps4[2], ps4[3]);
                     l += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
                 }
             } else {
                 // sweep 2: probabilities out
                 const float neg_m = m > -INFINITY ? -m : 0.f;
                 const size_t off = ((((size_t)b * p.H + h) * p.blocks + ent->blk[half]) * 64 + (r & 63)) * 64 + cb;
+                // a row with nothing visible has only -inf scores: every exponential is 0 and so is 0 * inv
+                const uint64_t sl2 = pk64(sl, sl), nm2 = pk64(neg_m, neg_m), inv2 = pk64(inv, inv);
 #pragma unroll
                 for (int c0 = 0; c0 < 32; c0 += 16) {
                     uint32_t v[16];
 #pragma unroll
-                    for (int c = 0; c < 16; c++)
-                        v[c] = __float_as_uint(inv > 0.f ? ex2_approx(fmaf(__uint_as_float(sr[c0 + c]), sl, neg_m)) * inv : 0.f);
+                    for (int c = 0; c < 16; c += 2) {
+                        const uint64_t x = fma2p(pk64(__uint_as_float(sr[c0 + c]), __uint_as_float(sr[c0 + c + 1])), sl2, nm2);
+                        float x0, x1;
+                        up64(x, x0, x1);
+                        const uint64_t y = mul2p(pk64(ex2_approx(x0), ex2_approx(x1)), inv2);
+                        float y0, y1;
+                        up64(y, y0, y1);
+                        v[c] = __float_as_uint(y0);
+                        v[c + 1] = __float_as_uint(y1);
+                    }
                     store_row16(p.Y, off, v, p.out_dtype, c0);
                 }
             }

@@ -214,6 +214,12 @@ __device__ __forceinline__ uint64_t add2p_rm(uint64_t a, uint64_t b)
     asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
+__device__ __forceinline__ uint64_t mul2p(uint64_t a, uint64_t b)
+{
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ uint64_t sub2p(uint64_t a, uint64_t b)
 {
     uint64_t d;
