@@ -598,7 +598,7 @@ def run_encoder_stack(args):
             "tflops_per_gpu": round(flops / (ms * 1e-3) / 1e12, 1),
             "e2e": {"value": round(world * Bg / (e2e_ms * 1e-3), 2), "unit": "seq/s", "ms_per_step": round(e2e_ms, 4),
                     "h2d_bytes_per_step": Bg * L * 4, "d2h_bytes_per_step": Bg * L * hidden * table.element_size()},
-            "gpu_launches": args.steps * (1 + args.layers * (9 if proj == "tensor" else 4)), "clocks": clocks, "device_status": status,
+            "gpu_launches": args.steps * (1 + args.layers * (7 if proj == "tensor" else 4)), "clocks": clocks, "device_status": status,   # this library's kernels per layer: QKV product, attention, 3 more products, 2 LayerNorms
         }
         if world > 1:
             line["gather_ms"] = round(gather_ms, 4)
@@ -863,7 +863,7 @@ def run_encoder_layer(args, sfb, cfg, pk, flush):
                    "projections": "sfb_linear (tcgen05, bias/GELU in the epilogue)" if proj == "tensor" else "torch.matmul (cuBLAS)",
                    "l2": flush.note},
         "tflops_total": round((gemm_flops + attn_flops) / (ms * 1e-3) / 1e12, 1),
-        "gpu_launches": args.steps * 4, "clocks": clocks}), flush=True)
+        "gpu_launches": args.steps * (7 if proj == "tensor" else 4), "clocks": clocks}), flush=True)
 
 
 

@@ -25,6 +25,14 @@ class EncoderLayerWeights:
         self.b1 = z(ffn)
         self.g1, self.g2 = (torch.ones(hidden, device=device, dtype=torch.float32) for _ in range(2))
         self.be1, self.be2 = z(hidden), z(hidden)
+        self._qkv = None
+
+    def fused_qkv(self):
+        """[hidden, 3 * hidden] weight and [3 * hidden] bias of the three projections side by side (built on first use
+        from wq, wk, wv, which stay the layer's parameters)."""
+        if self._qkv is None:
+            self._qkv = (torch.cat([self.wq, self.wk, self.wv], dim=1).contiguous(), torch.cat([self.bq, self.bk, self.bv]).contiguous())
+        return self._qkv
 
 
 def encoder_layer(sfb, x, w, lay, heads, ln_order="post", projections="library"):
@@ -60,17 +68,19 @@ def encoder_layer(sfb, x, w, lay, heads, ln_order="post", projections="library")
 
 def _encoder_layer_tensor(sfb, x2d, w, lay, heads, ln_order, scale):
     """The same layer with every projection on sfb.linear: biases and the GELU ride in the GEMM epilogues, so the
-    layer is 3 + 1 + 2 projections, the attention and two LayerNorm launches."""
+    layer is 1 + 1 + 2 projections, the attention and two LayerNorm launches."""
     m, hidden = x2d.shape
     d = hidden // heads
     L = lay.nb * lay.block_size
     B = m // L
 
     def attn(h2d):
-        q = sfb.linear(h2d, w.wq, w.bq).view(B, L, heads, d)
-        k = sfb.linear(h2d, w.wk, w.bk).view(B, L, heads, d)
-        v = sfb.linear(h2d, w.wv, w.bv).view(B, L, heads, d)
-        return sfb.fused_attention(q, k, v, lay, scale).view(m, hidden)
+        # one product for the three projections (the activations are read once, and three times the column tiles fill
+        # the last wave of the GEMM's grid better); the attention reads Q, K and V in place as column slices of the
+        # [m, 3 * hidden] result, rows 3 * hidden elements apart
+        wqkv, bqkv = w.fused_qkv()
+        qkv = sfb.linear(h2d, wqkv, bqkv).view(B, L, 3, heads, d)
+        return sfb.fused_attention_slice(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], lay, scale).view(m, hidden)
 
     if ln_order == "pre":
         h, _, _, _ = sfb.bias_residual_layernorm(x2d, None, None, w.g1, w.be1)
