@@ -51,6 +51,49 @@ __device__ __forceinline__ float gelu_ref(float t)
     return __fdividef(t, 1.f + __expf(-1.702f * t));
 }
 
+// One thread's share of a 128-row accumulator: row `row` of the output, 128 columns from n0 on, read from TMEM at
+// tcol 32 columns at a time (the next 32 travel while these are written), bias and activation applied, 32-byte stores.
+__device__ __forceinline__ void drain_rows(const GParams &p, uint32_t tcol, uint32_t row, uint32_t n0)
+{
+    const bool row_ok = row < p.M;
+    const size_t off = (size_t)row * p.N + n0;
+    uint32_t v[2][32];
+    TMEM_LD_32((v[0]), tcol);
+#pragma unroll
+    for (uint32_t c = 0; c < 4; c++) {
+        const uint32_t c0 = c * 32;
+        tmem_wait_ld();
+        if (c + 1 < 4) TMEM_LD_32((v[(c + 1) & 1]), tcol + c0 + 32);
+        uint32_t(&cur)[32] = v[c & 1];
+#pragma unroll
+        for (uint32_t q = 0; q < 2; q++) {
+            const uint32_t col = n0 + c0 + q * 16;
+            if (row_ok && col < p.N) {      // N is a multiple of 16: a group of 16 is inside or outside as a whole
+                float x[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) x[j] = __uint_as_float(cur[q * 16 + j]);
+                if (p.bias) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const float4 bb = __ldg((const float4 *)(p.bias + col) + j);   // the same address in every lane: one broadcast
+                        x[4 * j] += bb.x; x[4 * j + 1] += bb.y; x[4 * j + 2] += bb.z; x[4 * j + 3] += bb.w;
+                    }
+                }
+                if (p.act == 1) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) x[j] = gelu_ref(x[j]);
+                }
+                uint32_t w[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) w[j] = pack2(x[2 * j], x[2 * j + 1], p.is_bf16);
+                asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"((uint16_t *)p.out + off + c0 + q * 16),
+                             "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                             : "memory");
+            }
+        }
+    }
+}
+
 template <int MT>
 __global__ void __launch_bounds__(320, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const GParams p)
@@ -158,44 +201,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
 #pragma unroll 1
             for (uint32_t mt = 0; mt < MT; mt++) {
             const uint32_t m0 = (t % p.tiles_m) * (MT * kGBM) + mt * kGBM;
-            const bool row_ok = m0 + r < p.M;
-            const size_t off = (size_t)(m0 + r) * p.N + n0;
-            const uint32_t tcol = tmem + (buf * MT + mt) * kGBN + chalf * 128 + lane_field;
-            uint32_t v[2][32];
-            TMEM_LD_32((v[0]), tcol);
-#pragma unroll
-            for (uint32_t c = 0; c < 4; c++) {
-                const uint32_t c0 = c * 32;
-                tmem_wait_ld();
-                if (c + 1 < 4) TMEM_LD_32((v[(c + 1) & 1]), tcol + c0 + 32);   // the next 32 columns travel while these are written
-                uint32_t(&cur)[32] = v[c & 1];
-#pragma unroll
-                for (uint32_t q = 0; q < 2; q++) {
-                    const uint32_t col = n0 + c0 + q * 16;
-                    if (row_ok && col < p.N) {      // N is a multiple of 16: a group of 16 is inside or outside as a whole
-                        float x[16];
-#pragma unroll
-                        for (int j = 0; j < 16; j++) x[j] = __uint_as_float(cur[q * 16 + j]);
-                        if (p.bias) {
-#pragma unroll
-                            for (int j = 0; j < 4; j++) {
-                                const float4 bb = __ldg((const float4 *)(p.bias + col) + j);   // the same address in every lane: one broadcast
-                                x[4 * j] += bb.x; x[4 * j + 1] += bb.y; x[4 * j + 2] += bb.z; x[4 * j + 3] += bb.w;
-                            }
-                        }
-                        if (p.act == 1) {
-#pragma unroll
-                            for (int j = 0; j < 16; j++) x[j] = gelu_ref(x[j]);
-                        }
-                        uint32_t w[8];
-#pragma unroll
-                        for (int j = 0; j < 8; j++) w[j] = pack2(x[2 * j], x[2 * j + 1], p.is_bf16);
-                        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"((uint16_t *)p.out + off + c0 + q * 16),
-                                     "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
-                                     : "memory");
-                    }
-                }
-            }
+            drain_rows(p, tmem + (buf * MT + mt) * kGBN + chalf * 128 + lane_field, m0 + r, n0);
             }
             tcgen05_fence_before();
             mbar_arrive(&st->acc_empty[buf]);
@@ -220,6 +226,211 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
         __syncwarp();
         tcgen05_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// ---- the same product on CTA pairs ------------------------------------------------------------------------
+// With one CTA per tile the kernel above is bound by shared-memory bandwidth: an M128 N256 K16 MMA reads 4 KB of A and
+// 8 KB of B from shared memory in its 128 cycles while the TMA writes the next stage at the same rate -- more than
+// the 128 bytes per clock an SM's shared memory moves, which is where its 61 % tensor-pipe activity comes from.
+// Here the two CTAs of a cluster (the two SMs of a TPC) share a 256 x 256 tile: each loads its own 128 rows of x and
+// only HALF of the w tile (128 of the 256 columns), and one thread of the even CTA issues tcgen05.mma.cta_group::2
+// (M 256), which reads A and its half of B from each CTA's own shared memory and writes each CTA's 128 rows of the
+// accumulator into that CTA's TMEM.  Per CTA and MMA: 4 KB + 4 KB read, and stages of 32 KB instead of 48.
+//   * Both producers signal the even CTA's `full` barrier (it expects the bytes of both); the commit after a stage's
+//     MMAs arrives on the `empty` barrier of both CTAs, the commit after a tile on both `acc_full` barriers.
+//   * Each CTA drains its own 128 rows; its epilogue warps arrive on the even CTA's `acc_empty` barrier.
+//   * No load is a multicast: each CTA fetches what it multiplies.
+#ifndef SFB_GEMM_PAIRS
+#define SFB_GEMM_PAIRS 1
+#endif
+constexpr bool kUsePairs = SFB_GEMM_PAIRS != 0;
+constexpr uint32_t kPStages = 6;
+constexpr uint32_t kPABytes = kGBM * kGBK * 2;            // 16 KB: this CTA's 128 rows of x
+constexpr uint32_t kPBBytes = kGBK * (kGBN / 2) * 2;      // 16 KB: this CTA's 128 columns of w
+constexpr uint32_t kPStageBytes = kPABytes + kPBBytes;
+constexpr size_t kPSmem = 1024 + kPStages * kPStageBytes + 256;
+
+struct PShared {
+    uint64_t full[kPStages], empty[kPStages], acc_full[2], acc_empty[2], drained;
+    uint32_t tmem_base, abort_flag;
+};
+static_assert(sizeof(PShared) <= 256, "PShared outgrew its slot");
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the address, in the cluster's shared window, of this CTA's shared-memory address `addr` in CTA `rank`
+__device__ __forceinline__ uint32_t mapa_rank(uint32_t addr, uint32_t rank)
+{
+    uint32_t d;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(d) : "r"(addr), "r"(rank));
+    return d;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// a tile into this CTA's shared memory, its bytes counted on a barrier that may live in the other CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster_addr, int32_t x, int32_t y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrives on the barrier at this offset in both CTAs of the pair once the MMAs issued so far have completed
+__device__ __forceinline__ void umma_commit_pair(uint64_t *bar)
+{
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+                 "h"(both)
+                 : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
+linear_tc_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const GParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *tiles = smem;                                   // stage s: A (16 KB) then this CTA's half of B (16 KB)
+    PShared *st = (PShared *)(tiles + kPStages * kPStageBytes);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();                 // 0: issues the MMAs of the pair
+    const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    volatile uint32_t *abort_flag = &st->abort_flag;
+    const uint32_t fmt = p.is_bf16 ? 1u : 0u;
+    const uint32_t n_tiles = p.tiles_m * p.tiles_n;          // tiles of 256 x 256
+    const uint32_t kblocks = (p.K + kGBK - 1) / kGBK;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kPStages; s++) { mbar_init(&st->full[s], 1); mbar_init(&st->empty[s], 1); }
+        for (int s = 0; s < 2; s++) { mbar_init(&st->acc_full[s], 1); mbar_init(&st->acc_empty[s], 16); }   // 8 epilogue warps of each CTA
+        mbar_init(&st->drained, 1);
+        st->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&st->tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                      // both CTAs' barriers exist before anything signals across
+    tcgen05_fence_after();
+    const uint32_t tmem = st->tmem_base;
+
+    if (warp == 0) {
+        // ===== TMA producer (both CTAs): own rows of x, own half of the w tile; bytes counted on the even CTA's barrier =====
+        if (lane == 0) {
+            uint32_t g = 0;
+            for (uint32_t t = pair; t < n_tiles; t += pairs) {
+                const int32_t m0 = (int32_t)((t % p.tiles_m) * 256 + rank * kGBM);
+                const int32_t n0 = (int32_t)((t / p.tiles_m) * kGBN + rank * (kGBN / 2));
+                bool alive = true;
+                for (uint32_t kb = 0; kb < kblocks; kb++, g++) {
+                    const uint32_t s = g % kPStages;
+                    if (g >= kPStages && !mbar_wait(&st->empty[s], ((g / kPStages) - 1) & 1, abort_flag, 51)) { alive = false; break; }
+                    const uint32_t base = smem_u32(tiles + s * kPStageBytes);
+                    const uint32_t bar = mapa_rank(smem_u32(&st->full[s]), 0);
+                    if (rank == 0) mbar_expect_tx(&st->full[s], 2 * kPStageBytes);   // both CTAs' bytes; boxes beyond the tensor arrive as zeros and still count
+                    tma_load_2d_pair(base, &amap, bar, (int32_t)(kb * kGBK), m0);
+                    if (p.w_transposed) {
+                        tma_load_2d_pair(base + kPABytes, &bmap, bar, (int32_t)(kb * kGBK), n0);      // 128 rows of w, 64 of k
+                    } else {
+#pragma unroll
+                        for (uint32_t j = 0; j < 2; j++)
+                            tma_load_2d_pair(base + kPABytes + j * kTileBytes, &bmap, bar, n0 + (int32_t)(j * 64), (int32_t)(kb * kGBK));
+                    }
+                }
+                if (!alive) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer: one thread of the even CTA for the pair =====
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = instr_desc(fmt, fmt, 256, kGBN, p.w_transposed ? 0 : 1);
+            const uint32_t b_step = p.w_transposed ? 2u : 128u;
+            uint32_t g = 0, i = 0;
+            for (uint32_t t = pair; t < n_tiles; t += pairs, i++) {
+                const uint32_t buf = i & 1;
+                bool alive = true;
+                if (i >= 2 && !mbar_wait(&st->acc_empty[buf], ((i >> 1) - 1) & 1, abort_flag, 52)) break;
+                tcgen05_fence_after();
+                for (uint32_t kb = 0; kb < kblocks; kb++, g++) {
+                    const uint32_t s = g % kPStages;
+                    if (!mbar_wait(&st->full[s], (g / kPStages) & 1, abort_flag, 53)) { alive = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t base = smem_u32(tiles + s * kPStageBytes);
+                    const uint64_t a_desc = smem_desc_sw128(base);
+                    const uint64_t b_desc = p.w_transposed ? smem_desc_sw128(base + kPABytes) : smem_desc_sw128(base + kPABytes, kTileBytes);
+#pragma unroll
+                    for (uint32_t kk = 0; kk < 4; kk++)
+                        umma_f16_pair(tmem + buf * kGBN, a_desc + 2 * kk, b_desc + b_step * kk, idesc, (kb | kk) ? 1u : 0u);
+                    umma_commit_pair(&st->empty[s]);
+                }
+                if (!alive) break;
+                umma_commit_pair(&st->acc_full[buf]);
+            }
+        }
+    } else {
+        // ===== epilogue (both CTAs): this CTA's 128 rows of the tile, as in the single-CTA kernel =====
+        const uint32_t quarter = warp & 3;
+        const uint32_t chalf = (warp - 2) >> 2;
+        const uint32_t r = quarter * 32 + lane;
+        const uint32_t lane_field = (quarter * 32) << 16;
+        const uint32_t acc_empty0[2] = {mapa_rank(smem_u32(&st->acc_empty[0]), 0), mapa_rank(smem_u32(&st->acc_empty[1]), 0)};
+        uint32_t i = 0;
+        for (uint32_t t = pair; t < n_tiles; t += pairs, i++) {
+            const uint32_t buf = i & 1;
+            const uint32_t n0 = (t / p.tiles_m) * kGBN + chalf * 128;
+            const uint32_t m0 = (t % p.tiles_m) * 256 + rank * kGBM;
+            if (!mbar_wait_warp(&st->acc_full[buf], (i >> 1) & 1, abort_flag, 54)) break;
+            tcgen05_fence_after();
+            drain_rows(p, tmem + buf * kGBN + chalf * 128 + lane_field, m0 + r, n0);
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(buf ? acc_empty0[1] : acc_empty0[0]);
+        }
+    }
+
+    // ---- teardown (also the way out after a timeout) ----
+    tcgen05_fence_before();
+    __syncthreads();
+    if (st->abort_flag) {
+        if (warp == 1 && lane == 0 && rank == 0) {
+            asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&st->drained)) : "memory");
+            for (uint32_t k = 0; k < kWaitLimit && !mbar_try_wait(&st->drained, 0); k++) {}
+        }
+        if (warp == 0 && lane == 0) {
+            const uint64_t t0 = clock64();
+            while (clock64() - t0 < 2000000ull) {}
+        }
+        __syncthreads();
+    }
+    cluster_sync_all();      // neither CTA leaves, nor frees its TMEM, while the other may still read its shared memory or signal it
+    if (warp == 0) {
+        __syncwarp();
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
 }
 
@@ -259,8 +470,24 @@ int tc_linear(cudaStream_t s, void *out, const void *x, const void *w, const flo
             return fail("sfb_linear: cannot reserve %zu bytes of shared memory", GCfg<1>::smem);
         once.mark(dev);
     }
-    // long-k products are bound by what travels from L2: 256-row tiles, as long as they still fill the SMs twice over
     const uint32_t tiles_n = (n + kGBN - 1) / kGBN;
+    // CTA pairs on 256 x 256 tiles whenever there is at least one tile per pair of SMs
+    const uint32_t pair_tiles = ((m + 255) / 256) * tiles_n;
+    if (kUsePairs && sms >= 2 && pair_tiles >= (uint32_t)(sms / 2)) {
+        CUtensorMap bp;
+        if (w_transposed ? make_map_2d(&bp, w, n, k, is_bf16, kGBN / 2) : make_map_2d(&bp, w, k, n, is_bf16, kGBK)) return 1;
+        static DeviceOnce once_pair;
+        if (!once_pair.done(dev)) {
+            if (cudaFuncSetAttribute(linear_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPSmem) != cudaSuccess)
+                return fail("sfb_linear: cannot reserve %zu bytes of shared memory", kPSmem);
+            once_pair.mark(dev);
+        }
+        GParams prm = {out, bias, m, n, k, (m + 255) / 256, tiles_n, is_bf16, act, w_transposed ? 1 : 0};
+        const uint32_t pairs = pair_tiles < (uint32_t)(sms / 2) ? pair_tiles : (uint32_t)(sms / 2);
+        linear_tc_pair_kernel<<<2 * pairs, 320, kPSmem, s>>>(am, bp, prm);
+        return check_launch("sfb_linear");
+    }
+    // long-k products are bound by what travels from L2: 256-row tiles, as long as they still fill the SMs twice over
     const int mt = (k >= 2048 && (uint64_t)((m + 255) / 256) * tiles_n >= 2ull * sms) ? 2 : 1;
     GParams prm = {out, bias, m, n, k, (m + mt * kGBM - 1) / (mt * kGBM), tiles_n, is_bf16, act, w_transposed ? 1 : 0};
     const uint32_t tiles = prm.tiles_m * prm.tiles_n;

@@ -51,6 +51,29 @@ def test_linear_more_tiles_than_sms_and_batched_input(sfb, oracle):
     assert float((got.view(-1, n).float() - full).abs().max()) <= 2e-2 * float(full.abs().max())
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("m,n,k,act,transposed", [
+    (19000, 256, 64, 0, False),      # one k-block, one column tile, every pair of CTAs busy
+    (2500, 2320, 200, 1, False),     # ragged in m (last 256-row tile: 196 rows), n (16 columns into the last tile) and k
+    (4096, 768, 3072, 0, False),     # 48 k-blocks: the stage ring wraps eight times per tile
+    (2304, 4000, 512, 1, True),      # w as [n, k]; the odd CTA's half of the last column tile lies beyond n
+    (129, 19200, 128, 0, True),      # a single row into the second CTA's half
+])
+def test_linear_on_cta_pairs(sfb, dtype, m, n, k, act, transposed):
+    """Shapes with at least one 256 x 256 tile per pair of SMs take the two-CTA kernel: against a float32 product on
+    the device (the oracle checks the same entry point on small shapes above)."""
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    x = torch.randn(m, k, device="cuda", generator=gen).to(TD[dtype])
+    w = (0.05 * torch.randn(k, n, device="cuda", generator=gen)).to(TD[dtype])
+    b = torch.randn(n, device="cuda", generator=gen)
+    got = sfb.linear_nt(x, w.t().contiguous(), b, act) if transposed else sfb.linear(x, w, b, act)
+    assert sfb.device_status() == 0
+    t = x.float() @ w.float() + b
+    want = t * torch.sigmoid(1.702 * t) if act else t
+    assert got.shape == (m, n)
+    assert float((got.float() - want).abs().max()) <= 2e-2 * float(want.abs().max())
+
+
 def test_linear_rejects_what_it_cannot_do(sfb):
     x = torch.zeros(16, 64, device="cuda")
     w = torch.zeros(64, 64, device="cuda")
