@@ -465,7 +465,7 @@ def run_ours(args):
                                       "value": round(st["flops"] / (share_ms * 1e-3) / 1e12, 2),
                                       "value_incl_gather": round(st["flops"] / (both_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
                                       "how": "the 64 (batch, head) pairs dealt contiguously to the ranks, computed in place on head slices "
-                                             "(sfb_fused_attention_slice) in two chunks; each chunk's output all-gathered on a second stream under the next chunk's compute",
+                                             "(sfb_fused_attention_slice) in %d launch(es) per step; with two, the first chunk's output is all-gathered on a second stream under the second chunk's compute" % st["launches"],
                                       "gather_bytes_per_rank": st["gather_bytes"], "launches_per_step": st["launches"]}
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_reference_sample(cfg, budget_s=20.0, steps=1)
