@@ -47,8 +47,13 @@ struct GParams {
 
 __device__ __forceinline__ float gelu_ref(float t)
 {
-    // x * sigmoid(1.702 x), the reference's GELU (gelu_gpu_v2, cuda_kernels.h:561-581)
-    return __fdividef(t, 1.f + __expf(-1.702f * t));
+    // x * sigmoid(1.702 x), the reference's GELU (gelu_gpu_v2, cuda_kernels.h:561-581), as
+    // 0.5 x tanh(0.851 x) + 0.5 x: one MUFU operation per element instead of an exponential and a reciprocal
+    // (tanh.approx: relative error about 2^-11, below half a unit of the 16-bit output)
+    float th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.851f * t));
+    const float h = 0.5f * t;
+    return fmaf(h, th, h);
 }
 
 // One thread's share of a 128-row accumulator: row `row` of the output, 128 columns from n0 on, read from TMEM at
