@@ -58,6 +58,8 @@ def test_linear_more_tiles_than_sms_and_batched_input(sfb, oracle):
     (4096, 768, 3072, 0, False),     # 48 k-blocks: the stage ring wraps eight times per tile
     (2304, 4000, 512, 1, True),      # w as [n, k]; the odd CTA's half of the last column tile lies beyond n
     (129, 19200, 128, 0, True),      # a single row into the second CTA's half
+    (8192, 768, 256, 0, True),
+    (8192, 752, 200, 1, True),       # ragged n (the last tile's second half has 112 of its 128 columns) and k
 ])
 def test_linear_on_cta_pairs(sfb, dtype, m, n, k, act, transposed):
     """Shapes with at least one 256 x 256 tile per pair of SMs take the two-CTA kernel: against a float32 product on
