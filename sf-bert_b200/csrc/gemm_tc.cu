@@ -490,7 +490,8 @@ int tc_linear(cudaStream_t s, void *out, const void *x, const void *w, const flo
         GParams prm = {out, bias, m, n, k, (m + 255) / 256, tiles_n, is_bf16, act, w_transposed ? 1 : 0};
         const uint32_t pairs = pair_tiles < (uint32_t)(sms / 2) ? pair_tiles : (uint32_t)(sms / 2);
         linear_tc_pair_kernel<<<2 * pairs, 320, kPSmem, s>>>(am, bp, prm);
-        return check_launch("sfb_linear");
+        // a device or a partition that cannot place the clusters refuses the launch: the single-CTA kernel takes over
+        if (cudaGetLastError() == cudaSuccess) { clear_error(); return 0; }
     }
     // long-k products are bound by what travels from L2: 256-row tiles, as long as they still fill the SMs twice over
     const int mt = (k >= 2048 && (uint64_t)((m + 255) / 256) * tiles_n >= 2ull * sms) ? 2 : 1;
