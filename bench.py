@@ -125,13 +125,20 @@ def attention_flops(cfg, blocks):
 
 
 def bind_to_gpu_cpus(index):
-    """With several ranks on one host, run this process (and first-touch its pinned buffers) on the CPUs next to its GPU:
-    the end-to-end figure moves 150 MB per step from host memory, and a buffer on the far socket halves that rate.
-    Only this process's own CPU affinity changes.  Returns the number of CPUs bound to, or None."""
+    """Run this process (and first-touch its pinned buffers) on the CPUs next to its GPU: the end-to-end figure moves
+    150 MB per step from host memory, and a buffer on the far socket halves that rate.  Only this process's own CPU
+    affinity changes (the caller puts it back before the CPU baseline, which wants every core).  The GPU is looked up
+    by its PCI address, which is the same whatever subset of the host's GPUs this process sees.  Returns the number of
+    CPUs bound to, or None."""
     try:
         import pynvml
+        import torch
         pynvml.nvmlInit()
-        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        pr = torch.cuda.get_device_properties(index)
+        try:
+            h = pynvml.nvmlDeviceGetHandleByPciBusId("%08x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id))
+        except Exception:
+            h = pynvml.nvmlDeviceGetHandleByIndex(index)
         words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
         cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
         cpus &= os.sched_getaffinity(0)
@@ -324,7 +331,8 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    near = bind_to_gpu_cpus(local) if world > 1 else None
+    all_cpus = os.sched_getaffinity(0)
+    near = bind_to_gpu_cpus(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg = CONFIGS[args.config]
@@ -468,6 +476,7 @@ def run_ours(args):
                                              "(sfb_fused_attention_slice) in %d launch(es) per step; with two, the first chunk's output is all-gathered on a second stream under the second chunk's compute" % st["launches"],
                                       "gather_bytes_per_rank": st["gather_bytes"], "launches_per_step": st["launches"]}
         if world == 1 and not args.no_cpu:
+            os.sched_setaffinity(0, all_cpus)      # the reference's CPU path is timed on every core
             line["cpu_baseline"] = cpu_reference_sample(cfg, budget_s=20.0, steps=1)
         print(json.dumps(line), flush=True)
     if world > 1:
