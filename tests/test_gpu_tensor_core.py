@@ -214,6 +214,25 @@ def test_unfused_pipeline_16bit_full_size(sfb, oracle):
     assert float((o - fused).abs().max()) <= 2 * REL * float(fused.abs().max())
 
 
+@pytest.mark.parametrize("heads", [1, 37, 148, 213, 226, 300])
+def test_fused_attention_item_dealing(sfb, heads):
+    """Every row pair of every (batch, head) is computed exactly once whichever way the launch deals its items to the
+    CTAs' streams: fewer items than SMs, fewer than streams, just under and just over four rounds of items (where the
+    order of dealing changes), and more.  Against the three unfused operators on the same inputs."""
+    B, L, d = 1, 1024, 64                 # 8 row pairs per head
+    lay = sfb.BlockLayout.generate(sfb.LAYOUT_STRIDE, 1, L // 64, 64, p0=3, p1=4)
+    gen = torch.Generator(device="cuda").manual_seed(500 + heads)
+    q, k, v = (torch.randn(B, L, heads, d, device="cuda", generator=gen).to(torch.bfloat16) for _ in range(3))
+    o = torch.full((B, L, heads, d), float("nan"), device="cuda", dtype=torch.bfloat16)
+    sfb.fused_attention(q, k, v, lay, 0.125, out=o)
+    assert sfb.device_status() == 0
+    s = sfb.bst_sgemm_nt(q, k, lay, torch.bfloat16)
+    p = sfb.masked_softmax(s, lay, 0.125, torch.bfloat16)
+    ref = sfb.bst_sgemm_xn(p, v, lay).float()
+    assert bool(torch.isfinite(o.float()).all())
+    assert float((o.float() - ref).abs().max()) <= 2 * REL * float(ref.abs().max())
+
+
 @pytest.mark.parametrize("dtype,out", [("bf16", "f32"), ("f16", "f16"), ("bf16", "bf16")])
 @pytest.mark.parametrize("pred,ctx", [(None, 0), ("MASK_CAUSAL_DIAG", 0), ("MASK_LOCAL", 100)])
 def test_fused_sddmm_softmax_on_tensor_cores(sfb, oracle, dtype, out, pred, ctx):
