@@ -99,6 +99,64 @@ __device__ __forceinline__ void drain_rows(const GParams &p, uint32_t tcol, uint
     }
 }
 
+// The same share of an accumulator, leaving through shared memory: the warp's 32 rows x 64 columns are packed into a
+// staging tile in the tensor map's 128-byte swizzle (16-byte chunk c of row r at chunk c ^ (r % 8)) and one lane hands
+// the tile to the TMA, twice per 128 columns.  The writes reach memory as whole 128-byte rows instead of 32 bytes per
+// thread and instruction, and the storing threads are free as soon as the tile is in shared memory.
+// row0 = first of the warp's 32 rows, n0 = first of its 128 columns.
+__device__ __forceinline__ void drain_rows_staged(const GParams &p, const CUtensorMap *omap, uint32_t tcol, uint8_t *stage, uint32_t row0,
+                                                  uint32_t n0, uint32_t lane)
+{
+    uint8_t *srow = stage + lane * 128;
+    uint32_t v[2][32];
+    TMEM_LD_32((v[0]), tcol);
+#pragma unroll
+    for (uint32_t c = 0; c < 4; c++) {
+        const uint32_t c0 = c * 32;
+        tmem_wait_ld();
+        if (c + 1 < 4) TMEM_LD_32((v[(c + 1) & 1]), tcol + c0 + 32);
+        if ((c & 1) == 0) {
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the store that used the tile has read it
+            __syncwarp();
+        }
+        uint32_t(&cur)[32] = v[c & 1];
+#pragma unroll
+        for (uint32_t q = 0; q < 2; q++) {
+            const uint32_t col = n0 + c0 + q * 16;
+            float x[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) x[j] = __uint_as_float(cur[q * 16 + j]);
+            if (p.bias && col < p.N) {      // N is a multiple of 16: a group of 16 is inside or outside as a whole
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float4 bb = __ldg((const float4 *)(p.bias + col) + j);
+                    x[4 * j] += bb.x; x[4 * j + 1] += bb.y; x[4 * j + 2] += bb.z; x[4 * j + 3] += bb.w;
+                }
+            }
+            if (p.act == 1) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) x[j] = gelu_ref(x[j]);
+            }
+            uint32_t w[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) w[j] = pack2(x[2 * j], x[2 * j + 1], p.is_bf16);
+            const uint32_t ch = ((c & 1) * 32 + q * 16) >> 3;     // 16-byte chunk of the 128-byte row
+            *(uint4 *)(srow + ((ch ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            *(uint4 *)(srow + (((ch + 1) ^ (lane & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+        if (c & 1) {
+            fence_proxy_async();
+            __syncwarp();
+            const uint32_t col0 = n0 + (c0 - 32);
+            if (lane == 0 && col0 < p.N && row0 < p.M) {      // rows and columns of the box beyond the tensor are not written
+                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                             ::"l"((uint64_t)omap), "r"(smem_u32(stage)), "r"((int32_t)col0), "r"((int32_t)row0) : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+        }
+    }
+}
+
 template <int MT>
 __global__ void __launch_bounds__(320, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const GParams p)
@@ -244,17 +302,19 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
 // accumulator into that CTA's TMEM.  Per CTA and MMA: 4 KB + 4 KB read, and stages of 32 KB instead of 48.
 //   * Both producers signal the even CTA's `full` barrier (it expects the bytes of both); the commit after a stage's
 //     MMAs arrives on the `empty` barrier of both CTAs, the commit after a tile on both `acc_full` barriers.
-//   * Each CTA drains its own 128 rows; its epilogue warps arrive on the even CTA's `acc_empty` barrier.
+//   * Each CTA drains its own 128 rows (through per-warp staging tiles and TMA stores); its epilogue warps arrive on
+//     the even CTA's `acc_empty` barrier.
 //   * No load is a multicast: each CTA fetches what it multiplies.
 #ifndef SFB_GEMM_PAIRS
 #define SFB_GEMM_PAIRS 1
 #endif
 constexpr bool kUsePairs = SFB_GEMM_PAIRS != 0;
 constexpr uint32_t kPStages = 6;
+constexpr uint32_t kPStagingBytes = 8 * 32 * 128;     // one 32-row x 64-column tile per epilogue warp
 constexpr uint32_t kPABytes = kGBM * kGBK * 2;            // 16 KB: this CTA's 128 rows of x
 constexpr uint32_t kPBBytes = kGBK * (kGBN / 2) * 2;      // 16 KB: this CTA's 128 columns of w
 constexpr uint32_t kPStageBytes = kPABytes + kPBBytes;
-constexpr size_t kPSmem = 1024 + kPStages * kPStageBytes + 256;
+constexpr size_t kPSmem = 1024 + kPStages * kPStageBytes + kPStagingBytes + 256;
 
 struct PShared {
     uint64_t full[kPStages], empty[kPStages], acc_full[2], acc_empty[2], drained;
@@ -310,12 +370,14 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t *bar)
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
-linear_tc_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const GParams p)
+linear_tc_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap,
+                      const __grid_constant__ CUtensorMap omap, const GParams p)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *tiles = smem;                                   // stage s: A (16 KB) then this CTA's half of B (16 KB)
-    PShared *st = (PShared *)(tiles + kPStages * kPStageBytes);
+    uint8_t *staging = tiles + kPStages * kPStageBytes;      // the epilogue warps' output tiles (4 KB each)
+    PShared *st = (PShared *)(staging + kPStagingBytes);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();                 // 0: issues the MMAs of the pair
@@ -397,10 +459,10 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_con
             }
         }
     } else {
-        // ===== epilogue (both CTAs): this CTA's 128 rows of the tile, as in the single-CTA kernel =====
+        // ===== epilogue (both CTAs): this CTA's 128 rows of the tile; a warp takes 32 rows and 128 columns and stores them
+        // through its own staging tile =====
         const uint32_t quarter = warp & 3;
         const uint32_t chalf = (warp - 2) >> 2;
-        const uint32_t r = quarter * 32 + lane;
         const uint32_t lane_field = (quarter * 32) << 16;
         const uint32_t acc_empty0[2] = {mapa_rank(smem_u32(&st->acc_empty[0]), 0), mapa_rank(smem_u32(&st->acc_empty[1]), 0)};
         uint32_t i = 0;
@@ -410,11 +472,12 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_con
             const uint32_t m0 = (t % p.tiles_m) * 256 + rank * kGBM;
             if (!mbar_wait_warp(&st->acc_full[buf], (i >> 1) & 1, abort_flag, 54)) break;
             tcgen05_fence_after();
-            drain_rows(p, tmem + buf * kGBN + chalf * 128 + lane_field, m0 + r, n0);
+            drain_rows_staged(p, &omap, tmem + buf * kGBN + chalf * 128 + lane_field, staging + (warp - 2) * 4096, m0 + quarter * 32, n0, lane);
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(buf ? acc_empty0[1] : acc_empty0[0]);
         }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the last tile has left shared memory
     }
 
     // ---- teardown (also the way out after a timeout) ----
@@ -487,9 +550,11 @@ int tc_linear(cudaStream_t s, void *out, const void *x, const void *w, const flo
                 return fail("sfb_linear: cannot reserve %zu bytes of shared memory", kPSmem);
             once_pair.mark(dev);
         }
+        CUtensorMap om;      // out as [m, n], boxes of 32 rows x 64 columns for the epilogue's stores
+        if (make_map_2d(&om, out, m, n, is_bf16, 32)) return 1;
         GParams prm = {out, bias, m, n, k, (m + 255) / 256, tiles_n, is_bf16, act, w_transposed ? 1 : 0};
         const uint32_t pairs = pair_tiles < (uint32_t)(sms / 2) ? pair_tiles : (uint32_t)(sms / 2);
-        linear_tc_pair_kernel<<<2 * pairs, 320, kPSmem, s>>>(am, bp, prm);
+        linear_tc_pair_kernel<<<2 * pairs, 320, kPSmem, s>>>(am, bp, om, prm);
         // a device or a partition that cannot place the clusters refuses the launch: the single-CTA kernel takes over
         if (cudaGetLastError() == cudaSuccess) { clear_error(); return 0; }
     }
