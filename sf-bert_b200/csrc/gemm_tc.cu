@@ -43,7 +43,20 @@ struct GParams {
     uint32_t M, N, K, tiles_m, tiles_n;
     int is_bf16, act;
     int w_transposed;   // w is [n, k] row-major (out = x . w^T, the tied-embedding logits): its tile is a K-major B operand
+    uint32_t band;      // CTA-pair kernel: column tiles per band of the tile order (tile_coords)
 };
+
+// Tile t of the CTA-pair kernel -> (row tile, column tile).  The tiles run band by band, a band being `band` column
+// tiles wide, row tile by row tile inside it: the pairs that work at the same time then spread over `band` different
+// w tiles and a stripe of x tiles, instead of all asking the same few L2 slices for one w tile at once.
+__device__ __forceinline__ void tile_coords(const GParams &p, uint32_t t, uint32_t &tm, uint32_t &tn)
+{
+    const uint32_t per_band = p.tiles_m * p.band;
+    const uint32_t b = t / per_band, rem = t - b * per_band;
+    const uint32_t width = min(p.band, p.tiles_n - b * p.band);    // the last band may be narrower
+    tm = rem / width;
+    tn = b * p.band + (rem - tm * width);
+}
 
 __device__ __forceinline__ float gelu_ref(float t)
 {
@@ -309,6 +322,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
 #define SFB_GEMM_PAIRS 1
 #endif
 constexpr bool kUsePairs = SFB_GEMM_PAIRS != 0;
+#ifndef SFB_GEMM_BAND
+#define SFB_GEMM_BAND 4
+#endif
+constexpr uint32_t kPBand = SFB_GEMM_BAND;
 constexpr uint32_t kPStages = 6;
 constexpr uint32_t kPStagingBytes = 8 * 32 * 128;     // one 32-row x 64-column tile per epilogue warp
 constexpr uint32_t kPABytes = kGBM * kGBK * 2;            // 16 KB: this CTA's 128 rows of x
@@ -410,8 +427,10 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_con
         if (lane == 0) {
             uint32_t g = 0;
             for (uint32_t t = pair; t < n_tiles; t += pairs) {
-                const int32_t m0 = (int32_t)((t % p.tiles_m) * 256 + rank * kGBM);
-                const int32_t n0 = (int32_t)((t / p.tiles_m) * kGBN + rank * (kGBN / 2));
+                uint32_t tm, tn;
+                tile_coords(p, t, tm, tn);
+                const int32_t m0 = (int32_t)(tm * 256 + rank * kGBM);
+                const int32_t n0 = (int32_t)(tn * kGBN + rank * (kGBN / 2));
                 bool alive = true;
                 for (uint32_t kb = 0; kb < kblocks; kb++, g++) {
                     const uint32_t s = g % kPStages;
@@ -468,8 +487,10 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_con
         uint32_t i = 0;
         for (uint32_t t = pair; t < n_tiles; t += pairs, i++) {
             const uint32_t buf = i & 1;
-            const uint32_t n0 = (t / p.tiles_m) * kGBN + chalf * 128;
-            const uint32_t m0 = (t % p.tiles_m) * 256 + rank * kGBM;
+            uint32_t tm, tn;
+            tile_coords(p, t, tm, tn);
+            const uint32_t n0 = tn * kGBN + chalf * 128;
+            const uint32_t m0 = tm * 256 + rank * kGBM;
             if (!mbar_wait_warp(&st->acc_full[buf], (i >> 1) & 1, abort_flag, 54)) break;
             tcgen05_fence_after();
             drain_rows_staged(p, &omap, tmem + buf * kGBN + chalf * 128 + lane_field, staging + (warp - 2) * 4096, m0 + quarter * 32, n0, lane);
@@ -552,7 +573,7 @@ int tc_linear(cudaStream_t s, void *out, const void *x, const void *w, const flo
         }
         CUtensorMap om;      // out as [m, n], boxes of 32 rows x 64 columns for the epilogue's stores
         if (make_map_2d(&om, out, m, n, is_bf16, 32)) return 1;
-        GParams prm = {out, bias, m, n, k, (m + 255) / 256, tiles_n, is_bf16, act, w_transposed ? 1 : 0};
+        GParams prm = {out, bias, m, n, k, (m + 255) / 256, tiles_n, is_bf16, act, w_transposed ? 1 : 0, tiles_n < kPBand ? tiles_n : kPBand};
         const uint32_t pairs = pair_tiles < (uint32_t)(sms / 2) ? pair_tiles : (uint32_t)(sms / 2);
         linear_tc_pair_kernel<<<2 * pairs, 320, kPSmem, s>>>(am, bp, om, prm);
         // a device or a partition that cannot place the clusters refuses the launch: the single-CTA kernel takes over
@@ -560,7 +581,7 @@ int tc_linear(cudaStream_t s, void *out, const void *x, const void *w, const flo
     }
     // long-k products are bound by what travels from L2: 256-row tiles, as long as they still fill the SMs twice over
     const int mt = (k >= 2048 && (uint64_t)((m + 255) / 256) * tiles_n >= 2ull * sms) ? 2 : 1;
-    GParams prm = {out, bias, m, n, k, (m + mt * kGBM - 1) / (mt * kGBM), tiles_n, is_bf16, act, w_transposed ? 1 : 0};
+    GParams prm = {out, bias, m, n, k, (m + mt * kGBM - 1) / (mt * kGBM), tiles_n, is_bf16, act, w_transposed ? 1 : 0, 1};
     const uint32_t tiles = prm.tiles_m * prm.tiles_n;
     const uint32_t grid = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
     if (mt == 2) linear_tc_kernel<2><<<grid, 320, GCfg<2>::smem, s>>>(am, bm, prm);
