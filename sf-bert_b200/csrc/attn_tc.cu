@@ -337,6 +337,8 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     SharedState *sh = (SharedState *)(smem + kOffState);
     UEntry *lists = (UEntry *)(smem + kOffList);
+    grid_dependency_wait();        // Q, K, V come from the kernel before this one
+    grid_launch_dependents();
 
     const uint32_t hw_warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t warp = hw_warp;
@@ -715,10 +717,11 @@ int tc_fused_attention(cudaStream_t s, const void *nn_lut, const void *q, const 
     // one CTA per SM, three streams each; fewer CTAs only when there are fewer items than SMs (few rounds) or than streams
     const uint64_t want = prm.cta_first ? n_items : (n_items + kStreams - 1) / kStreams;
     const dim3 grid((unsigned)(want < (uint64_t)sms ? want : (uint64_t)sms));
-    if (mask && is_bf16) fused_attention_tc_kernel<true, true, SFB_TC_POLY><<<grid, kThreads, kSmemBytes, s>>>(qm, km, vm, om, prm);
-    else if (mask) fused_attention_tc_kernel<true, false, SFB_TC_POLY><<<grid, kThreads, kSmemBytes, s>>>(qm, km, vm, om, prm);
-    else if (is_bf16) fused_attention_tc_kernel<false, true, SFB_TC_POLY><<<grid, kThreads, kSmemBytes, s>>>(qm, km, vm, om, prm);
-    else fused_attention_tc_kernel<false, false, SFB_TC_POLY><<<grid, kThreads, kSmemBytes, s>>>(qm, km, vm, om, prm);
+    const dim3 block(kThreads);
+    if (mask && is_bf16) launch_overlapped(fused_attention_tc_kernel<true, true, SFB_TC_POLY>, grid, block, kSmemBytes, s, qm, km, vm, om, prm);
+    else if (mask) launch_overlapped(fused_attention_tc_kernel<true, false, SFB_TC_POLY>, grid, block, kSmemBytes, s, qm, km, vm, om, prm);
+    else if (is_bf16) launch_overlapped(fused_attention_tc_kernel<false, true, SFB_TC_POLY>, grid, block, kSmemBytes, s, qm, km, vm, om, prm);
+    else launch_overlapped(fused_attention_tc_kernel<false, false, SFB_TC_POLY>, grid, block, kSmemBytes, s, qm, km, vm, om, prm);
     return check_launch("sfb_fused_attention");
 }
 

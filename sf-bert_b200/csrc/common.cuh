@@ -36,6 +36,31 @@ struct DeviceOnce {
     void mark(int dev) { if (dev >= 0 && dev < 64) mask.fetch_or(1ull << dev, std::memory_order_release); }
 };
 
+// ---- launches that may overlap the end of the kernel before them ---------------------------------
+// A kernel launched with launch_overlapped() may have its CTAs placed while the previous kernel of the stream is
+// still draining (programmatic dependent launch): its launch latency and set-up then hide under that tail.  Such a
+// kernel calls grid_dependency_wait() before it touches global memory -- the call returns once the previous kernel has
+// completed and its writes are visible -- and grid_launch_dependents() right after, which lets the kernel after IT be
+// placed as soon as SMs become free.  Both are no-ops in a kernel launched the plain way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // ---- device: element conversion -------------------------------------------------------------
 // fp32 -> bf16 bits the way the reference stores S and P (ew_op_gpu.h:241-253): add half a bf16
 // ulp of the magnitude, round toward zero, keep the upper 16 bits.

@@ -182,6 +182,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
     uint8_t *tiles = smem;                                   // stage s: A (16 KB) then B (32 KB)
     GShared *st = (GShared *)(tiles + kGStages * kGStageBytes);
 
+    grid_dependency_wait();
+    grid_launch_dependents();
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile uint32_t *abort_flag = &st->abort_flag;
     const uint32_t fmt = p.is_bf16 ? 1u : 0u;
@@ -397,6 +399,8 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_con
     uint8_t *staging = tiles + kPStages * kPStageBytes;      // the epilogue warps' output tiles (4 KB each)
     PShared *st = (PShared *)(staging + kPStagingBytes);
 
+    grid_dependency_wait();
+    grid_launch_dependents();
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();                 // 0: issues the MMAs of the pair
     const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
@@ -576,7 +580,7 @@ int tc_linear(cudaStream_t s, void *out, const void *x, const void *w, const flo
         if (make_map_2d(&om, out, m, n, is_bf16, 32)) return 1;
         GParams prm = {out, bias, m, n, k, (m + 255) / 256, tiles_n, is_bf16, act, w_transposed ? 1 : 0, tiles_n < kPBand ? tiles_n : kPBand};
         const uint32_t pairs = pair_tiles < (uint32_t)(sms / 2) ? pair_tiles : (uint32_t)(sms / 2);
-        linear_tc_pair_kernel<<<2 * pairs, 320, kPSmem, s>>>(am, bp, om, prm);
+        launch_overlapped(linear_tc_pair_kernel, dim3(2 * pairs), dim3(320), kPSmem, s, am, bp, om, prm);
         // a device or a partition that cannot place the clusters refuses the launch: the single-CTA kernel takes over
         if (cudaGetLastError() == cudaSuccess) { clear_error(); return 0; }
     }
@@ -585,8 +589,8 @@ int tc_linear(cudaStream_t s, void *out, const void *x, const void *w, const flo
     GParams prm = {out, bias, m, n, k, (m + mt * kGBM - 1) / (mt * kGBM), tiles_n, is_bf16, act, w_transposed ? 1 : 0, 1};
     const uint32_t tiles = prm.tiles_m * prm.tiles_n;
     const uint32_t grid = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
-    if (mt == 2) linear_tc_kernel<2><<<grid, 320, GCfg<2>::smem, s>>>(am, bm, prm);
-    else linear_tc_kernel<1><<<grid, 320, GCfg<1>::smem, s>>>(am, bm, prm);
+    if (mt == 2) launch_overlapped(linear_tc_kernel<2>, dim3(grid), dim3(320), GCfg<2>::smem, s, am, bm, prm);
+    else launch_overlapped(linear_tc_kernel<1>, dim3(grid), dim3(320), GCfg<1>::smem, s, am, bm, prm);
     return check_launch("sfb_linear");
 }
 

@@ -140,6 +140,8 @@ __global__ void __launch_bounds__(256) bias_residual_layernorm_kernel(void *out,
     constexpr int N = Vec8<DT>::N;
     constexpr int ESZ = 16 / N;
     extern __shared__ __align__(16) float prm[];           // [bias | gain | beta][hidden]
+    grid_dependency_wait();
+    grid_launch_dependents();
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t warps = gridDim.x * (blockDim.x >> 5);
     const uint8_t *xb = (const uint8_t *)x, *rb = (const uint8_t *)resid;
@@ -252,8 +254,8 @@ static int launch_ln(cudaStream_t s, void *out, void *sum_out, float *mean, floa
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 32 * rows_per_cta, smem) != cudaSuccess || per_sm < 1) \
             per_sm = 1;                                                                                                        \
         const uint32_t resident = (uint32_t)per_sm * (uint32_t)sms;                                                            \
-        kern<<<want < resident ? want : resident, 32 * rows_per_cta, smem, s>>>(out, sum_out, mean, rstd, x, bias, resid, gain, \
-                                                                                beta, m, hidden);                              \
+        launch_overlapped(kern, dim3(want < resident ? want : resident), dim3(32 * rows_per_cta), smem, s, out, sum_out, mean, rstd, x, \
+                          bias, resid, gain, beta, m, hidden);                                                                 \
     } while (0)
 #define LN_CASE(C)                                                                                                             \
     do {                                                                                                                       \
