@@ -337,8 +337,6 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     SharedState *sh = (SharedState *)(smem + kOffState);
     UEntry *lists = (UEntry *)(smem + kOffList);
-    grid_dependency_wait();        // Q, K, V come from the kernel before this one
-    grid_launch_dependents();
 
     const uint32_t hw_warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t warp = hw_warp;
@@ -379,6 +377,10 @@ fused_attention_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem = sh->tmem_base;
+    // barriers and TMEM are set up; nothing of global memory has been read yet.  Launched as a programmatic dependent,
+    // the kernel waits here for the kernel before it (the projection that writes Q, K, V) to complete
+    grid_dependency_wait();
+    grid_launch_dependents();
 
     if (warp >= 16) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");

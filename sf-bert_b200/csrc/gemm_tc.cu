@@ -182,8 +182,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
     uint8_t *tiles = smem;                                   // stage s: A (16 KB) then B (32 KB)
     GShared *st = (GShared *)(tiles + kGStages * kGStageBytes);
 
-    grid_dependency_wait();
-    grid_launch_dependents();
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile uint32_t *abort_flag = &st->abort_flag;
     const uint32_t fmt = p.is_bf16 ? 1u : 0u;
@@ -206,6 +204,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem = st->tmem_base;
+    grid_dependency_wait();        // set-up done; x (and a w or bias written on the device) come from kernels before this one
+    grid_launch_dependents();
 
     if (warp == 0) {
         // ===== TMA producer =====
@@ -399,8 +399,6 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_con
     uint8_t *staging = tiles + kPStages * kPStageBytes;      // the epilogue warps' output tiles (4 KB each)
     PShared *st = (PShared *)(staging + kPStagingBytes);
 
-    grid_dependency_wait();
-    grid_launch_dependents();
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();                 // 0: issues the MMAs of the pair
     const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
@@ -426,6 +424,8 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_con
     cluster_sync_all();                                      // both CTAs' barriers exist before anything signals across
     tcgen05_fence_after();
     const uint32_t tmem = st->tmem_base;
+    grid_dependency_wait();        // set-up done; nothing of global memory has been read yet
+    grid_launch_dependents();
 
     if (warp == 0) {
         // ===== TMA producer (both CTAs): own rows of x, own half of the w tile; bytes counted on the even CTA's barrier =====
