@@ -230,6 +230,100 @@ __global__ void __launch_bounds__(256) bias_residual_layernorm_kernel(void *out,
     }
 }
 
+// Few rows (every row can be in flight at once): two warps per row, each holding half of it, four rows per CTA, one
+// pass and no loop.  Half the registers per thread of the kernel above, so twice the rows are resident; the two halves'
+// sums meet in shared memory.  bias, gain and beta come through L1 (the streamed rows bypass it).
+template <int DT, int HCHUNKS, bool HAS_RESID>
+__global__ void __launch_bounds__(256) bias_residual_layernorm_split_kernel(void *out, void *sum_out, float *__restrict__ mean,
+                                                                           float *__restrict__ rstd, const void *x,
+                                                                           const float *__restrict__ bias, const void *resid,
+                                                                           const float *__restrict__ gain, const float *__restrict__ beta,
+                                                                           uint32_t m, uint32_t hidden)
+{
+    constexpr int N = Vec8<DT>::N;
+    constexpr int ESZ = 16 / N;
+    __shared__ float2 part[8];
+    grid_dependency_wait();
+    grid_launch_dependents();
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t row = blockIdx.x * 4 + (warp >> 1), half = warp & 1;
+    const bool live = row < m;
+    const size_t base = (size_t)row * hidden;
+    const uint8_t *xb = (const uint8_t *)x, *rb = (const uint8_t *)resid;
+    uint4 xr[HCHUNKS], rr[HCHUNKS];
+#pragma unroll
+    for (int c = 0; c < HCHUNKS; c++) {
+        const uint32_t col = ((half * HCHUNKS + c) * 32 + lane) * N;
+        if (live && col < hidden) {
+            xr[c] = ld_stream16(xb + (base + col) * ESZ);
+            if (HAS_RESID) rr[c] = ld_stream16(rb + (base + col) * ESZ);
+        }
+    }
+    float v[HCHUNKS][N];
+    float s = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < HCHUNKS; c++) {
+        const uint32_t col = ((half * HCHUNKS + c) * 32 + lane) * N;
+        if (live && col < hidden) {
+            Vec8<DT>::decode(v[c], xr[c]);
+            if (bias) {
+#pragma unroll
+                for (int t = 0; t < N; t += 4) {
+                    const float4 bb = __ldg((const float4 *)(bias + col + t));
+                    v[c][t] += bb.x; v[c][t + 1] += bb.y; v[c][t + 2] += bb.z; v[c][t + 3] += bb.w;
+                }
+            }
+            if (HAS_RESID) {
+                float r[N];
+                Vec8<DT>::decode(r, rr[c]);
+#pragma unroll
+                for (int t = 0; t < N; t++) v[c][t] = r[t] + v[c][t];
+            }
+            if (sum_out) st_stream16((uint8_t *)sum_out + (base + col) * ESZ, Vec8<DT>::encode(v[c]));
+#pragma unroll
+            for (int t = 0; t < N; t++) {
+                s += v[c][t];
+                s2 = fmaf(v[c][t], v[c][t], s2);
+            }
+        }
+    }
+    s = warp_sum(s);
+    s2 = warp_sum(s2);
+    if (lane == 0) part[warp] = make_float2(s, s2);
+    __syncthreads();
+    const float2 other = part[warp ^ 1];
+    s += other.x;
+    s2 += other.y;
+    const float mu = s / (float)hidden;
+    const float rs = rsqrtf(fmaxf(s2 / (float)hidden - mu * mu, 0.f) + 1e-5f);
+    if (live && lane == 0 && half == 0) {
+        if (mean) mean[row] = mu;
+        if (rstd) rstd[row] = rs;
+    }
+#pragma unroll
+    for (int c = 0; c < HCHUNKS; c++) {
+        const uint32_t col = ((half * HCHUNKS + c) * 32 + lane) * N;
+        if (live && col < hidden) {
+            float y[N];
+#pragma unroll
+            for (int t = 0; t < N; t += 4) {
+                const float4 g = __ldg((const float4 *)(gain + col + t));
+                const float4 be = __ldg((const float4 *)(beta + col + t));
+                y[t] = (v[c][t] - mu) * rs * g.x + be.x;
+                y[t + 1] = (v[c][t + 1] - mu) * rs * g.y + be.y;
+                y[t + 2] = (v[c][t + 2] - mu) * rs * g.z + be.z;
+                y[t + 3] = (v[c][t + 3] - mu) * rs * g.w + be.w;
+            }
+            st_stream16((uint8_t *)out + (base + col) * ESZ, Vec8<DT>::encode(y));
+        }
+    }
+}
+
+#ifndef SFB_LN_SPLIT
+#define SFB_LN_SPLIT 1
+#endif
+constexpr bool kLnSplit = SFB_LN_SPLIT != 0;
+
 template <int DT>
 static int launch_ln(cudaStream_t s, void *out, void *sum_out, float *mean, float *rstd, const void *x, const float *bias,
                      const void *resid, const float *gain, const float *beta, uint32_t m, uint32_t hidden)
@@ -262,6 +356,27 @@ static int launch_ln(cudaStream_t s, void *out, void *sum_out, float *mean, floa
         if (resid) LN_LAUNCH(C, true);                                                                                         \
         else LN_LAUNCH(C, false);                                                                                              \
     } while (0)
+    // few rows (at most two waves of these CTAs): every row at once, two warps each, four rows per CTA
+#define LN_SPLIT(H, R)                                                                                                         \
+    do {                                                                                                                       \
+        auto kern = bias_residual_layernorm_split_kernel<DT, H, R>;                                                            \
+        launch_overlapped(kern, dim3((m + 3) / 4), dim3(256), 0, s, out, sum_out, mean, rstd, x, bias, resid, gain, beta, m, hidden); \
+        return check_launch("sfb_bias_residual_layernorm");                                                                    \
+    } while (0)
+#define LN_SPLIT_CASE(H)                                                                                                       \
+    do {                                                                                                                       \
+        if (resid) LN_SPLIT(H, true);                                                                                          \
+        else LN_SPLIT(H, false);                                                                                               \
+    } while (0)
+    if (kLnSplit && chunks >= 2 && chunks <= 8 && (uint64_t)m <= 8ull * 8 * (uint64_t)sms) {
+        const uint32_t hc = (chunks + 1) / 2;
+        if (hc == 1) LN_SPLIT_CASE(1);
+        else if (hc == 2) LN_SPLIT_CASE(2);
+        else if (hc == 3) LN_SPLIT_CASE(3);
+        else LN_SPLIT_CASE(4);
+    }
+#undef LN_SPLIT_CASE
+#undef LN_SPLIT
     if (chunks <= 1) LN_CASE(1);
     else if (chunks <= 2) LN_CASE(2);
     else if (chunks <= 3) LN_CASE(3);
