@@ -58,7 +58,14 @@ static inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid,
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e != cudaSuccess) {
+        // a driver or a capture mode that refuses the attribute: the same launch, fully serialised
+        (void)cudaGetLastError();
+        cfg.numAttrs = 0;
+        e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    }
+    return e;
 }
 
 // ---- device: element conversion -------------------------------------------------------------
