@@ -323,6 +323,10 @@ __global__ void __launch_bounds__(256) bias_residual_layernorm_split_kernel(void
 #define SFB_LN_SPLIT 1
 #endif
 constexpr bool kLnSplit = SFB_LN_SPLIT != 0;
+#ifndef SFB_LN_SPLIT_ROWS
+#define SFB_LN_SPLIT_ROWS 64
+#endif
+constexpr uint64_t kLnSplitRows = SFB_LN_SPLIT_ROWS;   // rows per SM up to which a launch takes the two-warps-per-row kernel
 
 template <int DT>
 static int launch_ln(cudaStream_t s, void *out, void *sum_out, float *mean, float *rstd, const void *x, const float *bias,
@@ -368,7 +372,7 @@ static int launch_ln(cudaStream_t s, void *out, void *sum_out, float *mean, floa
         if (resid) LN_SPLIT(H, true);                                                                                          \
         else LN_SPLIT(H, false);                                                                                               \
     } while (0)
-    if (kLnSplit && chunks >= 2 && chunks <= 8 && (uint64_t)m <= 8ull * 8 * (uint64_t)sms) {
+    if (kLnSplit && chunks >= 2 && chunks <= 8 && (uint64_t)m <= kLnSplitRows * (uint64_t)sms) {
         const uint32_t hc = (chunks + 1) / 2;
         if (hc == 1) LN_SPLIT_CASE(1);
         else if (hc == 2) LN_SPLIT_CASE(2);
