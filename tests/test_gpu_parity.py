@@ -314,3 +314,48 @@ def test_bias_gelu(sfb, oracle, dtype, m, n):
     got = sfb.bias_gelu(x, b).float().cpu().numpy()
     tol = 2e-6 if dtype == "f32" else 2e-2
     assert np.abs(got - want).max() <= tol * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("bs", [32, 64])
+@pytest.mark.parametrize("longest", [1, 4, 5, 8, 9, 12, 13, 16, 17, 18, 19, 20, 21, 33])
+def test_masked_softmax_every_row_length_variant(sfb, oracle, bs, longest):
+    """Rows of 1 .. `longest` kept blocks in one layout: the caller's max_lut picks the softmax variant (rows held in
+    registers in 4, 8, 12, 16, 18 or 20 block slots, whole or quarter block-rows per CTA, or streamed beyond that), and
+    every variant must give the same probabilities: bf16 scores against a float64 softmax of the same values, bf16 and
+    fp32 outputs, with and without an element mask."""
+    nb = 36
+    rng = np.random.default_rng(700 + longest)
+    layout = np.zeros((1, nb, nb), np.uint8)
+    for i in range(nb):
+        n = longest if i == nb // 2 else 1 + (i * 7) % longest
+        layout[0, i, rng.choice(nb, size=n, replace=False)] = 1
+    lay = sfb.BlockLayout(torch.from_numpy(layout).cuda(), bs)
+    luts = oracle.lut_build(layout)
+    assert int(lay.nn_max) == longest
+    B, H = 2, 3
+    gen = torch.Generator(device="cuda").manual_seed(41)
+    s = (3.0 * torch.randn(B, H, luts["blocks"], bs, bs, device="cuda", generator=gen)).to(torch.bfloat16)
+    sn = s.float().cpu().numpy().astype(np.float64)
+    nt = luts["nt"][0]
+    for use_mask in (False, True):
+        keep = np.ones((luts["blocks"], bs, bs), bool)
+        if use_mask:
+            lay.pack_mask(sfb.MASK_CAUSAL_DIAG, 0)
+            for kblk in range(luts["blocks"]):
+                if nt[kblk][0] == nt[kblk][1]:
+                    keep[kblk] = np.tril(np.ones((bs, bs), bool))
+        ref = np.zeros_like(sn)
+        for i in range(nb):
+            ids = [kblk for kblk in range(luts["blocks"]) if nt[kblk][0] == i]
+            x = np.concatenate([np.where(keep[kblk], sn[:, :, kblk] * 0.125, -np.inf) for kblk in ids], axis=-1)
+            mx = x.max(-1, keepdims=True)
+            e = np.exp(x - np.where(np.isfinite(mx), mx, 0.0))
+            den = e.sum(-1, keepdims=True)
+            pr = np.where(den > 0, e / np.where(den > 0, den, 1.0), 0.0)
+            for j, kblk in enumerate(ids):
+                ref[:, :, kblk] = pr[..., j * bs:(j + 1) * bs]
+        p32 = sfb.masked_softmax(s, lay, 0.125, torch.float32, use_mask=use_mask).cpu().numpy()
+        np.testing.assert_allclose(p32, ref, rtol=0, atol=3e-6)
+        p16 = sfb.masked_softmax(s, lay, 0.125, torch.bfloat16, use_mask=use_mask).float().cpu().numpy()
+        assert np.abs(p16 - ref).max() <= 2.0 ** -8
+
