@@ -153,3 +153,29 @@ def test_layernorm_in_place(sfb, dtype, hidden, target):
     got, _, mean2, rstd2 = sfb.bias_residual_layernorm(xs, bias, rs, gain, beta, out=dst)
     assert got.data_ptr() == dst.data_ptr()
     assert torch.equal(got, want) and torch.equal(mean, mean2) and torch.equal(rstd, rstd2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("hidden", [264, 520, 768, 1000, 1024, 1544, 2048])
+@pytest.mark.parametrize("m,with_resid", [(1, True), (5, False), (1001, True), (20000, True)])
+def test_layernorm_few_and_many_rows(sfb, dtype, hidden, m, with_resid):
+    """Launches of few rows take the kernel with two warps per row, larger ones the persistent one-warp-per-row kernel;
+    row lengths that do not fill the last 16-byte chunk of a lane, one row, and a row count that is no multiple of the
+    rows per CTA.  Against a float64 LayerNorm of the same inputs (E[x^2] - mean^2, eps 1e-5 inside the root)."""
+    gen = torch.Generator(device="cuda").manual_seed(hidden + m)
+    x = torch.randn(m, hidden, device="cuda", generator=gen).to(dtype)
+    resid = torch.randn(m, hidden, device="cuda", generator=gen).to(dtype) if with_resid else None
+    bias, gain, beta = (torch.randn(hidden, device="cuda", generator=gen) for _ in range(3))
+    out, summed, mean, rstd = sfb.bias_residual_layernorm(x, bias, resid, gain, beta, want_sum=True)
+    t = x.double() + bias.double()
+    if with_resid:
+        t = t + resid.double()
+    mu = t.mean(-1, keepdim=True)
+    var = (t * t).mean(-1, keepdim=True) - mu * mu
+    want = (t - mu) / torch.sqrt(var.clamp_min(0) + 1e-5) * gain.double() + beta.double()
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    assert float((out.double() - want).abs().max()) <= tol * float(want.abs().max())
+    assert float((summed.double() - t).abs().max()) <= (1e-6 if dtype == torch.float32 else 2e-2) * float(t.abs().max())
+    assert float((mean.double() - mu.squeeze(-1)).abs().max()) <= 1e-5
+    assert float((rstd.double() * torch.sqrt(var.clamp_min(0) + 1e-5).squeeze(-1) - 1).abs().max()) <= 1e-4
+
